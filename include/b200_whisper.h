@@ -1,0 +1,140 @@
+/*
+ * b200_whisper.h - C ABI of the sm_100a kernels behind the ggml backend plugin (libggml-b200.so).
+ *
+ * Two libraries:
+ *   libb200_kernels.so  exports every b200_* function below (plain pointers and sizes, no ggml types).
+ *   libggml-b200.so     exports ggml_backend_init / ggml_backend_score, the entry points that ggml's
+ *                       dynamic loader binds (ggml/src/ggml-backend-impl.h:215-218, looked up by
+ *                       ggml/src/ggml-backend-reg.cpp:236-253).  Its graph_compute maps every node of a
+ *                       whisper graph onto the functions declared here.
+ *
+ * Every function returns 0 on success or a cudaError_t value (B200_ERR_* for argument errors).  Device
+ * pointers are plain CUDA device pointers on the current device.  `stream` is a cudaStream_t passed
+ * as void* (NULL = legacy default stream).  Nothing here synchronises the stream.
+ *
+ * Arithmetic contract: each kernel reproduces the operation order of the AVX2/FMA/F16C build of the
+ * reference CPU backend (lane-wise partial sums, FMA placement, F16 round trips), so results are
+ * expected to be bit-identical to it, not merely close.
+ */
+#ifndef B200_WHISPER_H
+#define B200_WHISPER_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_ERR_ARG      10001   /* unsupported shape / type / alignment */
+#define B200_ERR_NO_DEVICE 10002  /* no CUDA device: the library never falls back to the CPU */
+
+/* ggml type ids used at this boundary (ggml/include/ggml.h:354-387) */
+#define B200_TYPE_F32  0
+#define B200_TYPE_F16  1
+#define B200_TYPE_Q5_0 6
+#define B200_TYPE_Q8_0 8
+#define B200_TYPE_I32  26
+
+/* ---- block formats ---------------------------------------------------------------------------
+ * ggml stores 32 weights per block: block_q5_0 = {f16 d; u8 qh[4]; u8 qs[16]} (22 B),
+ * block_q8_0 = {f16 d; i8 qs[32]} (34 B)  (ggml/src/ggml-common.h:187-214).  Neither size allows
+ * aligned vector loads, so device memory holds the same bytes as three (two) planes of one tensor:
+ *   Q5_0: qs[nb][16] | qh[nb] (u32) | d[nb] (f16)         Q8_0: qs[nb][32] | d[nb] (f16)
+ * Total size is unchanged (22*nb / 34*nb bytes).  These run on the host and allocate nothing. */
+int b200_blocks_to_planes(int type, const void * blocks, void * planes, int64_t nb_total,
+                          int64_t nb_first, int64_t nb_count);   /* replaces nothing: layout helper */
+int b200_planes_to_blocks(int type, const void * planes, void * blocks, int64_t nb_total,
+                          int64_t nb_first, int64_t nb_count);
+
+/* dequantize_row_q5_0 / dequantize_row_q8_0 (ggml/src/ggml-quants.c:296-320, 349-362) on planes. */
+int b200_dequantize(int type, const void * planes, int64_t nb_total, int64_t nb_first, int64_t nb_count,
+                    float * out, void * stream);
+
+/* quantize_row_q8_0, AVX2 variant (ggml/src/ggml-cpu/ggml-cpu-quants.c:808-866): rows of f32 ->
+ * int8 qs[n_rows][k] and the f16-rounded scale widened to f32, d[n_rows][k/32]. */
+int b200_quantize_q8_0(const float * x, int64_t n_rows, int64_t k, int64_t row_stride_bytes,
+                       int8_t * qs, float * d, void * stream);
+
+/* ggml_compute_forward_mul_mat for Q5_0 / Q8_0 weights (ggml/src/ggml-cpu/ggml-cpu.c:1266-1458 with
+ * ggml_vec_dot_q5_0_q8_0 / ggml_vec_dot_q8_0_q8_0, ggml-cpu-quants.c:3076-3100, 3869-3886):
+ * dst[n*dst_stride + m] = sum_k W[m][k] * X[n][k], activations already quantised by
+ * b200_quantize_q8_0.  w_planes covers the WHOLE weight tensor (nb_total blocks). */
+int b200_mul_mat_q(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                   const int8_t * xq, const float * xd, int64_t N,
+                   float * dst, int64_t dst_stride, void * stream);
+
+/* Same contract for 1..8 activation columns given as f32 (row stride in bytes): quantisation of the
+ * activations is fused, no scratch is needed.  The batch-1 / beam decode path. */
+int b200_mul_mat_vec_q(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                       const float * x, int64_t x_stride_bytes, int64_t N,
+                       float * dst, int64_t dst_stride, void * stream);
+
+/* mul_mat with F16 src0 (ggml_vec_dot_f16, ggml/src/ggml-cpu/vec.cpp:128-167): src1 is f32 (rounded
+ * to f16 first, ggml-cpu.c:1329-1362) or f16.  Strides in bytes; src0 [K, M, ne02, ne03],
+ * src1 [K, N, ne12, ne13] with ne12 % ne02 == 0, dst f32 contiguous [M, N, ne12, ne13]. */
+int b200_mul_mat_f16(const void * src0, const int64_t * ne0, const int64_t * nb0,
+                     const void * src1, int src1_type, const int64_t * ne1, const int64_t * nb1,
+                     float * dst, const int64_t * nbd, void * stream);
+
+/* ggml_compute_forward_flash_attn_ext_f16 (ggml/src/ggml-cpu/ops.cpp:6638-6851) for head size 64,
+ * F16 K/V, optional F16 mask; the running F16 accumulator and its rounding order are kept.
+ * q f32 [64, n_q, n_head] (strides nbq1, nbq2 bytes), k/v f16 [64, n_kv, n_head], mask f16
+ * [n_kv, >=n_q] or NULL, dst f32 [64, n_head, n_q] contiguous. */
+int b200_flash_attn_ext(const float * q, int64_t nbq1, int64_t nbq2,
+                        const void * k, int64_t nbk1, int64_t nbk2,
+                        const void * v, int64_t nbv1, int64_t nbv2,
+                        const void * mask, int64_t nbm1,
+                        float * dst, int64_t n_q, int64_t n_kv, int64_t n_head, float scale, void * stream);
+
+/* ggml_compute_forward_norm_f32 (ops.cpp:3109-3158): rows of ne00 f32, row strides in bytes. */
+int b200_norm(const float * x, float * y, int64_t ne00, int64_t ne01, int64_t ne02, int64_t ne03,
+              const int64_t * nbx, const int64_t * nby, float eps, void * stream);
+
+/* ADD (op 0) / MUL (op 1) with ggml broadcasting of src1 (ggml/src/ggml-cpu/binary-ops.cpp:50-137). */
+int b200_binary(int op, const float * a, const int64_t * nea, const int64_t * nba,
+                const float * b, const int64_t * neb, const int64_t * nbb,
+                float * dst, const int64_t * nbd, void * stream);
+
+/* SCALE (ops.cpp:3840) and GELU via the F16 lookup table (vec.h:443-457) on contiguous f32. */
+int b200_scale(const float * x, float * y, int64_t n, float s, void * stream);
+int b200_gelu(const float * x, float * y, int64_t n, void * stream);
+
+/* CPY / DUP / CONT (ops.cpp:26-1183): f32->f32, f32->f16, f16->f16, f16->f32, any strides,
+ * same element count, element order = row-major over ne. */
+int b200_cpy(const void * src, int src_type, const int64_t * nes, const int64_t * nbs,
+             void * dst, int dst_type, const int64_t * ned, const int64_t * nbd, void * stream);
+
+/* GET_ROWS (ops.cpp:4146-4313): rows selected by i32 ids from a Q5_0/Q8_0 (planes), F16 or F32
+ * table [ne00, n_table_rows] -> f32 [ne00, n_ids] contiguous. */
+int b200_get_rows(int type, const void * table, int64_t nb_total_or_row_stride, int64_t ne00,
+                  const int32_t * ids, int64_t n_ids, float * dst, void * stream);
+
+/* IM2COL 1-D, F16 output (ops.cpp:5784-5855): x f32 [IW, IC] (row stride bytes) ->
+ * dst f16 [IC*KW, OW]. */
+int b200_im2col_1d_f16(const float * x, int64_t x_stride_bytes, int64_t IW, int64_t IC, int64_t KW,
+                       int64_t OW, int s0, int p0, int d0, void * dst, void * stream);
+
+/* SOFT_MAX with optional mask and scale (ops.cpp:4641-4737, max_bias = 0): rows of ne00 f32. */
+int b200_soft_max(const float * x, const void * mask, int mask_type, int64_t mask_nb1, int64_t mask_ne1,
+                  float * y, int64_t ne00, int64_t nrows, int64_t ne01, float scale, void * stream);
+
+/* CONCAT along dim (ops.cpp:2403-2604), f32, contiguous dst. */
+int b200_concat(const float * a, const int64_t * nea, const int64_t * nba,
+                const float * b, const int64_t * neb, const int64_t * nbb,
+                float * dst, const int64_t * ned, const int64_t * nbd, int dim, void * stream);
+
+/* log_mel_spectrogram (src/whisper.cpp:3008-3271): 16 kHz mono f32 PCM -> log-mel [n_mel][n_len]
+ * on the device; out_host receives n_mel*n_len floats (n_len = (n_samples + 480000 padding)/160).
+ * The result feeds whisper_set_mel_with_state (include/whisper.h:278-293). */
+int b200_log_mel(int device, const float * pcm_host, int64_t n_samples, const float * filters_host,
+                 int n_mel, float * out_host, int64_t out_capacity, int * n_len, int * n_len_org);
+
+/* Library info: number of kernel launches issued so far by this process (all entry points). */
+int64_t b200_launch_count(void);
+const char * b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200_WHISPER_H */

@@ -1,0 +1,75 @@
+"""Whole-path parity through whisper.h: the same synthetic model file and clip run on the reference CPU
+backend (use_gpu=false) and on the B200 plugin (use_gpu=true), flash_attn flag alike on both sides.
+
+Gates (from the north star): encoder output relative L2 <= 1e-3; teacher-forced logits max relative
+error <= 1e-2; greedy token ids identical except where the reference's top-2 margin is below 1e-3.
+"""
+import os
+
+import numpy as np
+import pytest
+
+import ref_ops as R
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not R.have_ref(), reason="reference build (oracle/_ref) missing")]
+
+ENC_TOL = 1e-3
+LOGIT_TOL = 1e-2
+MARGIN = 1e-3
+
+
+def rel_l2(a, b):
+    return float(np.linalg.norm(a.astype(np.float64) - b.astype(np.float64)) / np.linalg.norm(a.astype(np.float64)))
+
+
+def run_pair(pkg, model_dir, arch, wtype, flash, n_new=32, seed=1):
+    path = os.path.join(model_dir, f"{arch}-{wtype}.bin")
+    if not os.path.exists(path):
+        pkg.synth.write_model(path, arch, wtype, seed=0)
+    pcm = pkg.synth.pcm_f32(pkg.synth.make_clip(seed))
+    out = {}
+    cpu = pkg.Whisper(path, use_gpu=False, flash_attn=flash, probe=True)
+    mel = cpu.pcm_to_mel(pcm)[:, :3000].copy()
+    for name, w in (("cpu", cpu), ("gpu", None)):
+        if w is None:
+            w = pkg.Whisper(path, use_gpu=True, flash_attn=flash, probe=True)
+        w.set_mel(mel)
+        enc = w.encode()
+        force = out["cpu"]["tokens"] if name == "gpu" else None
+        toks, margins, logits = w.greedy(n_new, force=force, want_logits=True)
+        out[name] = dict(enc=enc, tokens=toks, margins=margins, logits=logits)
+        if name == "gpu":   # free-running ids as well
+            w.set_mel(mel)
+            out[name]["free_tokens"] = w.greedy(n_new)[0]
+        w.close()
+    return out
+
+
+def check(out, what):
+    e = rel_l2(out["cpu"]["enc"], out["gpu"]["enc"])
+    same = float((out["cpu"]["enc"] == out["gpu"]["enc"]).mean())
+    lc, lg = out["cpu"]["logits"].astype(np.float64), out["gpu"]["logits"].astype(np.float64)
+    lerr = float(np.abs(lc - lg).max() / np.abs(lc).max())
+    print(f"{what}: encoder rel-L2 {e:.3e} (bit-identical fraction {same:.4f}); logits max-rel {lerr:.3e}; "
+          f"bit-identical logits fraction {float((lc == lg).mean()):.4f}")
+    assert e <= ENC_TOL, f"{what}: encoder rel-L2 {e}"
+    assert lerr <= LOGIT_TOL, f"{what}: logits max-rel {lerr}"
+    for name in ("tokens", "free_tokens"):
+        diff = np.flatnonzero(out["cpu"]["tokens"] != out["gpu"][name])
+        if name == "free_tokens" and diff.size:
+            diff = diff[:1]   # after the first divergence the histories differ; only that step is comparable
+        assert all(out["cpu"]["margins"][i] < MARGIN for i in diff), f"{what}: {name} differ at {diff} with margins {out['cpu']['margins'][diff]}"
+
+
+@pytest.mark.parametrize("wtype", ["f16", "q5_0", "q8_0"])
+def test_tiny_flash(pkg, model_dir, wtype):
+    check(run_pair(pkg, model_dir, "tiny", wtype, True), f"tiny {wtype} flash_attn")
+
+
+@pytest.mark.parametrize("wtype", ["f16", "q5_0"])
+def test_tiny_no_flash(pkg, model_dir, wtype):
+    check(run_pair(pkg, model_dir, "tiny", wtype, False), f"tiny {wtype} no flash_attn")
+
+
+def test_base_q5_0_flash(pkg, model_dir):
+    check(run_pair(pkg, model_dir, "base", "q5_0", True, n_new=16), "base q5_0 flash_attn")

@@ -1,0 +1,603 @@
+// ggml backend plugin for NVIDIA B200 (sm_100a).
+//
+// Implements the five interface tables of ggml/src/ggml-backend-impl.h (reg :191-201, device :137-179,
+// buffer type :17-29, buffer :41-58, backend :87-117) and exports ggml_backend_init/ggml_backend_score
+// (:215-218), so that an unmodified whisper.cpp picks it up through ggml_backend_load() and runs
+// whisper_encode / whisper_decode / whisper_full on it.  Every node of the whisper graphs is executed
+// by a kernel of libb200_kernels.so (include/b200_whisper.h); supports_op is exactly the set of nodes
+// graph_compute can run, there is no host fallback inside this file.
+#include "ggml.h"
+#include "ggml-backend.h"
+#include "ggml-backend-impl.h"
+#include "b200_whisper.h"
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#define B200_MAX_DEVICES 16
+
+static bool cuda_ok(cudaError_t e, const char * what) {
+    if (e == cudaSuccess) return true;
+    fprintf(stderr, "ggml-b200: %s failed: %s\n", what, cudaGetErrorString(e));
+    return false;
+}
+
+static bool is_quant(enum ggml_type t) { return t == GGML_TYPE_Q5_0 || t == GGML_TYPE_Q8_0; }
+
+// ---------------------------------------------------------------------------------------------
+// statistics (exposed through get_proc_address for tests and the benchmark)
+// ---------------------------------------------------------------------------------------------
+static std::atomic<int64_t> g_nodes_computed{0};    // non-view nodes executed by this backend
+static std::atomic<int64_t> g_graphs_computed{0};
+static std::atomic<int64_t> g_h2d_bytes{0};
+static std::atomic<int64_t> g_d2h_bytes{0};
+
+extern "C" {
+int64_t b200_stat_nodes(void)   { return g_nodes_computed.load(); }
+int64_t b200_stat_graphs(void)  { return g_graphs_computed.load(); }
+int64_t b200_stat_h2d(void)     { return g_h2d_bytes.load(); }
+int64_t b200_stat_d2h(void)     { return g_d2h_bytes.load(); }
+}
+
+// ---------------------------------------------------------------------------------------------
+// buffer
+// ---------------------------------------------------------------------------------------------
+struct b200_buffer_ctx {
+    int    device;
+    void * base;
+};
+
+static void b200_buffer_free(ggml_backend_buffer_t buffer) {
+    b200_buffer_ctx * ctx = (b200_buffer_ctx *) buffer->context;
+    cudaSetDevice(ctx->device);
+    cudaFree(ctx->base);
+    delete ctx;
+}
+
+static void * b200_buffer_get_base(ggml_backend_buffer_t buffer) {
+    return ((b200_buffer_ctx *) buffer->context)->base;
+}
+
+static void b200_buffer_memset_tensor(ggml_backend_buffer_t buffer, struct ggml_tensor * tensor, uint8_t value, size_t offset, size_t size) {
+    b200_buffer_ctx * ctx = (b200_buffer_ctx *) buffer->context;
+    cudaSetDevice(ctx->device);
+    cuda_ok(cudaMemsetAsync((char *) tensor->data + offset, value, size, cudaStreamPerThread), "memset_tensor");
+    cuda_ok(cudaStreamSynchronize(cudaStreamPerThread), "memset_tensor sync");
+}
+
+// Block-quantised tensors live in device memory as planes (see b200_whisper.h); set/get translate.
+static void b200_buffer_set_tensor(ggml_backend_buffer_t buffer, struct ggml_tensor * tensor, const void * data, size_t offset, size_t size) {
+    b200_buffer_ctx * ctx = (b200_buffer_ctx *) buffer->context;
+    cudaSetDevice(ctx->device);
+    g_h2d_bytes += (int64_t) size;
+    if (is_quant(tensor->type)) {
+        const size_t  bs = ggml_type_size(tensor->type);
+        const int64_t nb_total = (int64_t) (ggml_nbytes(tensor) / bs);
+        GGML_ASSERT(tensor->view_src == nullptr && "ggml-b200: views of block-quantised tensors are not supported");
+        GGML_ASSERT(offset % bs == 0 && size % bs == 0);
+        const int64_t first = (int64_t) (offset / bs), count = (int64_t) (size / bs);
+        // repack into a host image of the touched plane ranges, then copy each range
+        const size_t qsz = tensor->type == GGML_TYPE_Q5_0 ? 16 : 32;
+        std::vector<uint8_t> qs(count * qsz), qh(tensor->type == GGML_TYPE_Q5_0 ? count * 4 : 0), d(count * 2);
+        const uint8_t * src = (const uint8_t *) data;
+        for (int64_t i = 0; i < count; ++i) {
+            const uint8_t * b = src + bs * i;
+            memcpy(&d[2 * i], b, 2);
+            if (tensor->type == GGML_TYPE_Q5_0) {
+                memcpy(&qh[4 * i], b + 2, 4);
+                memcpy(&qs[16 * i], b + 6, 16);
+            } else {
+                memcpy(&qs[32 * i], b + 2, 32);
+            }
+        }
+        char * base = (char *) tensor->data;
+        cudaStream_t st = cudaStreamPerThread;
+        bool ok = cuda_ok(cudaMemcpyAsync(base + qsz * first, qs.data(), qs.size(), cudaMemcpyHostToDevice, st), "set_tensor qs");
+        if (tensor->type == GGML_TYPE_Q5_0) {
+            ok = ok && cuda_ok(cudaMemcpyAsync(base + 16 * nb_total + 4 * first, qh.data(), qh.size(), cudaMemcpyHostToDevice, st), "set_tensor qh");
+            ok = ok && cuda_ok(cudaMemcpyAsync(base + 20 * nb_total + 2 * first, d.data(), d.size(), cudaMemcpyHostToDevice, st), "set_tensor d");
+        } else {
+            ok = ok && cuda_ok(cudaMemcpyAsync(base + 32 * nb_total + 2 * first, d.data(), d.size(), cudaMemcpyHostToDevice, st), "set_tensor d");
+        }
+        cuda_ok(cudaStreamSynchronize(st), "set_tensor sync");
+        GGML_ASSERT(ok);
+        return;
+    }
+    bool ok = cuda_ok(cudaMemcpyAsync((char *) tensor->data + offset, data, size, cudaMemcpyHostToDevice, cudaStreamPerThread), "set_tensor");
+    ok = ok && cuda_ok(cudaStreamSynchronize(cudaStreamPerThread), "set_tensor sync");
+    GGML_ASSERT(ok);
+}
+
+static void b200_buffer_get_tensor(ggml_backend_buffer_t buffer, const struct ggml_tensor * tensor, void * data, size_t offset, size_t size) {
+    b200_buffer_ctx * ctx = (b200_buffer_ctx *) buffer->context;
+    cudaSetDevice(ctx->device);
+    g_d2h_bytes += (int64_t) size;
+    if (is_quant(tensor->type)) {
+        const size_t  bs = ggml_type_size(tensor->type);
+        const int64_t nb_total = (int64_t) (ggml_nbytes(tensor) / bs);
+        GGML_ASSERT(tensor->view_src == nullptr);
+        GGML_ASSERT(offset % bs == 0 && size % bs == 0);
+        const int64_t first = (int64_t) (offset / bs), count = (int64_t) (size / bs);
+        const size_t qsz = tensor->type == GGML_TYPE_Q5_0 ? 16 : 32;
+        std::vector<uint8_t> qs(count * qsz), qh(tensor->type == GGML_TYPE_Q5_0 ? count * 4 : 0), d(count * 2);
+        const char * base = (const char *) tensor->data;
+        cudaStream_t st = cudaStreamPerThread;
+        bool ok = cuda_ok(cudaMemcpyAsync(qs.data(), base + qsz * first, qs.size(), cudaMemcpyDeviceToHost, st), "get_tensor qs");
+        if (tensor->type == GGML_TYPE_Q5_0) {
+            ok = ok && cuda_ok(cudaMemcpyAsync(qh.data(), base + 16 * nb_total + 4 * first, qh.size(), cudaMemcpyDeviceToHost, st), "get_tensor qh");
+            ok = ok && cuda_ok(cudaMemcpyAsync(d.data(), base + 20 * nb_total + 2 * first, d.size(), cudaMemcpyDeviceToHost, st), "get_tensor d");
+        } else {
+            ok = ok && cuda_ok(cudaMemcpyAsync(d.data(), base + 32 * nb_total + 2 * first, d.size(), cudaMemcpyDeviceToHost, st), "get_tensor d");
+        }
+        ok = ok && cuda_ok(cudaStreamSynchronize(st), "get_tensor sync");
+        GGML_ASSERT(ok);
+        uint8_t * dst = (uint8_t *) data;
+        for (int64_t i = 0; i < count; ++i) {
+            uint8_t * b = dst + bs * i;
+            memcpy(b, &d[2 * i], 2);
+            if (tensor->type == GGML_TYPE_Q5_0) {
+                memcpy(b + 2, &qh[4 * i], 4);
+                memcpy(b + 6, &qs[16 * i], 16);
+            } else {
+                memcpy(b + 2, &qs[32 * i], 32);
+            }
+        }
+        return;
+    }
+    bool ok = cuda_ok(cudaMemcpyAsync(data, (const char *) tensor->data + offset, size, cudaMemcpyDeviceToHost, cudaStreamPerThread), "get_tensor");
+    ok = ok && cuda_ok(cudaStreamSynchronize(cudaStreamPerThread), "get_tensor sync");
+    GGML_ASSERT(ok);
+}
+
+static void b200_buffer_clear(ggml_backend_buffer_t buffer, uint8_t value) {
+    b200_buffer_ctx * ctx = (b200_buffer_ctx *) buffer->context;
+    cudaSetDevice(ctx->device);
+    cuda_ok(cudaMemsetAsync(ctx->base, value, buffer->size, cudaStreamPerThread), "clear");
+    cuda_ok(cudaStreamSynchronize(cudaStreamPerThread), "clear sync");
+}
+
+static const struct ggml_backend_buffer_i b200_buffer_iface = {
+    /* .free_buffer   = */ b200_buffer_free,
+    /* .get_base      = */ b200_buffer_get_base,
+    /* .init_tensor   = */ nullptr,
+    /* .memset_tensor = */ b200_buffer_memset_tensor,
+    /* .set_tensor    = */ b200_buffer_set_tensor,
+    /* .get_tensor    = */ b200_buffer_get_tensor,
+    /* .cpy_tensor    = */ nullptr,
+    /* .clear         = */ b200_buffer_clear,
+    /* .reset         = */ nullptr,
+};
+
+// ---------------------------------------------------------------------------------------------
+// buffer type (one per device)
+// ---------------------------------------------------------------------------------------------
+struct b200_device_ctx {
+    int         device;
+    std::string name;
+    std::string description;
+    struct ggml_backend_buffer_type buft;
+    std::string buft_name;
+};
+
+static const char * b200_buft_get_name(ggml_backend_buffer_type_t buft) {
+    return ((b200_device_ctx *) buft->context)->buft_name.c_str();
+}
+
+static ggml_backend_buffer_t b200_buft_alloc_buffer(ggml_backend_buffer_type_t buft, size_t size) {
+    b200_device_ctx * dctx = (b200_device_ctx *) buft->context;
+    if (cudaSetDevice(dctx->device) != cudaSuccess) return nullptr;
+    void * base = nullptr;
+    const size_t alloc = size > 0 ? size : 1;
+    cudaError_t e = cudaMalloc(&base, alloc);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        fprintf(stderr, "ggml-b200: allocating %.2f MiB on device %d failed: %s\n", alloc / 1024.0 / 1024.0, dctx->device, cudaGetErrorString(e));
+        return nullptr;
+    }
+    b200_buffer_ctx * ctx = new b200_buffer_ctx{dctx->device, base};
+    return ggml_backend_buffer_init(buft, b200_buffer_iface, ctx, size);
+}
+
+static size_t b200_buft_get_alignment(ggml_backend_buffer_type_t) { return 256; }
+
+static bool b200_buft_is_host(ggml_backend_buffer_type_t) { return false; }
+
+// ---------------------------------------------------------------------------------------------
+// backend (stream)
+// ---------------------------------------------------------------------------------------------
+struct b200_backend_ctx {
+    int          device;
+    cudaStream_t stream;
+    void *       scratch      = nullptr;   // Q8_0-quantised activations of the current GEMM
+    size_t       scratch_size = 0;
+    std::string  name;
+};
+
+static const char * b200_backend_get_name(ggml_backend_t backend) {
+    return ((b200_backend_ctx *) backend->context)->name.c_str();
+}
+
+static void b200_backend_free(ggml_backend_t backend) {
+    b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (ctx->scratch) cudaFree(ctx->scratch);
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    delete backend;
+}
+
+static void b200_backend_synchronize(ggml_backend_t backend) {
+    b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
+    cudaSetDevice(ctx->device);
+    cuda_ok(cudaStreamSynchronize(ctx->stream), "synchronize");
+}
+
+static bool ensure_scratch(b200_backend_ctx * ctx, size_t size) {
+    if (ctx->scratch_size >= size) return true;
+    if (ctx->scratch) {
+        cudaStreamSynchronize(ctx->stream);
+        cudaFree(ctx->scratch);
+        ctx->scratch = nullptr;
+        ctx->scratch_size = 0;
+    }
+    size = (size + (1u << 20) - 1) & ~((size_t) (1u << 20) - 1);
+    if (cudaMalloc(&ctx->scratch, size) != cudaSuccess) { cudaGetLastError(); return false; }
+    ctx->scratch_size = size;
+    return true;
+}
+
+static bool is_view_op(enum ggml_op op) {
+    return op == GGML_OP_NONE || op == GGML_OP_RESHAPE || op == GGML_OP_VIEW || op == GGML_OP_PERMUTE || op == GGML_OP_TRANSPOSE;
+}
+
+static bool b200_op_supported(const struct ggml_tensor * op);
+
+// returns 0 on success, else an error code of the kernel library
+static int compute_node(b200_backend_ctx * ctx, struct ggml_tensor * node) {
+    void * st = (void *) ctx->stream;
+    const struct ggml_tensor * s0 = node->src[0];
+    const struct ggml_tensor * s1 = node->src[1];
+    int64_t ne0[4], nb0[4], ne1[4], nb1[4], ned[4], nbd[4];
+    for (int i = 0; i < 4; ++i) {
+        ned[i] = node->ne[i]; nbd[i] = (int64_t) node->nb[i];
+        if (s0) { ne0[i] = s0->ne[i]; nb0[i] = (int64_t) s0->nb[i]; }
+        if (s1) { ne1[i] = s1->ne[i]; nb1[i] = (int64_t) s1->nb[i]; }
+    }
+    switch (node->op) {
+        case GGML_OP_MUL_MAT: {
+            if (is_quant(s0->type)) {
+                const int64_t K = s0->ne[0], M = s0->ne[1], N = s1->ne[1];
+                const int64_t nb_total = (int64_t) (ggml_nbytes(s0) / ggml_type_size(s0->type));
+                if (N <= 8) {
+                    return b200_mul_mat_vec_q((int) s0->type, s0->data, nb_total, M, K, (const float *) s1->data, nb1[1], N,
+                                              (float *) node->data, nbd[1] / 4, st);
+                }
+                const size_t q_bytes = (size_t) N * K, d_bytes = (size_t) N * (K / 32) * 4;
+                const size_t q_pad = (q_bytes + 255) & ~(size_t) 255;
+                if (!ensure_scratch(ctx, q_pad + d_bytes)) return (int) cudaErrorMemoryAllocation;
+                int8_t * xq = (int8_t *) ctx->scratch;
+                float *  xd = (float *) ((char *) ctx->scratch + q_pad);
+                int e = b200_quantize_q8_0((const float *) s1->data, N, K, nb1[1], xq, xd, st);
+                if (e) return e;
+                return b200_mul_mat_q((int) s0->type, s0->data, nb_total, M, K, xq, xd, N, (float *) node->data, nbd[1] / 4, st);
+            }
+            return b200_mul_mat_f16(s0->data, ne0, nb0, s1->data, (int) s1->type, ne1, nb1, (float *) node->data, nbd, st);
+        }
+        case GGML_OP_FLASH_ATTN_EXT: {
+            const struct ggml_tensor * k = node->src[1], * v = node->src[2], * mask = node->src[3];
+            float scale;
+            memcpy(&scale, (const float *) node->op_params + 0, sizeof(float));
+            return b200_flash_attn_ext((const float *) s0->data, nb0[1], nb0[2], k->data, (int64_t) k->nb[1], (int64_t) k->nb[2],
+                                       v->data, (int64_t) v->nb[1], (int64_t) v->nb[2],
+                                       mask ? mask->data : nullptr, mask ? (int64_t) mask->nb[1] : 0,
+                                       (float *) node->data, s0->ne[1], k->ne[1], s0->ne[2], scale, st);
+        }
+        case GGML_OP_NORM: {
+            float eps;
+            memcpy(&eps, node->op_params, sizeof(float));
+            return b200_norm((const float *) s0->data, (float *) node->data, ne0[0], ne0[1], ne0[2], ne0[3], nb0, nbd, eps, st);
+        }
+        case GGML_OP_ADD:
+            return b200_binary(0, (const float *) s0->data, ne0, nb0, (const float *) s1->data, ne1, nb1, (float *) node->data, nbd, st);
+        case GGML_OP_MUL:
+            return b200_binary(1, (const float *) s0->data, ne0, nb0, (const float *) s1->data, ne1, nb1, (float *) node->data, nbd, st);
+        case GGML_OP_SCALE: {
+            float s;
+            memcpy(&s, node->op_params, sizeof(float));
+            return b200_scale((const float *) s0->data, (float *) node->data, ggml_nelements(node), s, st);
+        }
+        case GGML_OP_UNARY:
+            return b200_gelu((const float *) s0->data, (float *) node->data, ggml_nelements(node), st);
+        case GGML_OP_CPY:
+        case GGML_OP_DUP:
+        case GGML_OP_CONT:
+            return b200_cpy(s0->data, (int) s0->type, ne0, nb0, node->data, (int) node->type, ned, nbd, st);
+        case GGML_OP_GET_ROWS: {
+            const int64_t arg = is_quant(s0->type) ? (int64_t) (ggml_nbytes(s0) / ggml_type_size(s0->type)) : nb0[1];
+            return b200_get_rows((int) s0->type, s0->data, arg, s0->ne[0], (const int32_t *) s1->data, s1->ne[0], (float *) node->data, st);
+        }
+        case GGML_OP_IM2COL: {
+            const int32_t * p = (const int32_t *) node->op_params;
+            return b200_im2col_1d_f16((const float *) s1->data, nb1[1], s1->ne[0], s1->ne[1], s0->ne[0], node->ne[1], p[0], p[2], p[4], node->data, st);
+        }
+        case GGML_OP_SOFT_MAX: {
+            float scale;
+            memcpy(&scale, (const float *) node->op_params + 0, sizeof(float));
+            return b200_soft_max((const float *) s0->data, s1 ? s1->data : nullptr, s1 ? (int) s1->type : 0, s1 ? nb1[1] : 0, s1 ? ne1[1] : 0,
+                                 (float *) node->data, ne0[0], ggml_nrows(s0), ne0[1], scale, st);
+        }
+        case GGML_OP_CONCAT: {
+            const int dim = ((const int32_t *) node->op_params)[0];
+            return b200_concat((const float *) s0->data, ne0, nb0, (const float *) s1->data, ne1, nb1, (float *) node->data, ned, nbd, dim, st);
+        }
+        default:
+            return B200_ERR_ARG;
+    }
+}
+
+static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struct ggml_cgraph * cgraph) {
+    b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return GGML_STATUS_FAILED;
+    const int n_nodes = ggml_graph_n_nodes(cgraph);
+    int64_t done = 0;
+    for (int i = 0; i < n_nodes; ++i) {
+        struct ggml_tensor * node = ggml_graph_node(cgraph, i);
+        if (is_view_op(node->op) || ggml_is_empty(node)) continue;
+        if (!b200_op_supported(node)) {
+            fprintf(stderr, "ggml-b200: unsupported node %s (%s) reached graph_compute\n", node->name, ggml_op_name(node->op));
+            return GGML_STATUS_FAILED;
+        }
+        const int e = compute_node(ctx, node);
+        if (e != 0) {
+            fprintf(stderr, "ggml-b200: node %d %s (%s) failed with code %d (%s)\n", i, node->name, ggml_op_name(node->op), e,
+                    e < 10000 ? cudaGetErrorString((cudaError_t) e) : "argument error");
+            return e == (int) cudaErrorMemoryAllocation ? GGML_STATUS_ALLOC_FAILED : GGML_STATUS_FAILED;
+        }
+        ++done;
+    }
+    g_nodes_computed += done;
+    g_graphs_computed += 1;
+    return GGML_STATUS_SUCCESS;
+}
+
+static const struct ggml_backend_i b200_backend_iface = {
+    /* .get_name           = */ b200_backend_get_name,
+    /* .free               = */ b200_backend_free,
+    /* .set_tensor_async   = */ nullptr,
+    /* .get_tensor_async   = */ nullptr,
+    /* .cpy_tensor_async   = */ nullptr,
+    /* .synchronize        = */ b200_backend_synchronize,
+    /* .graph_plan_create  = */ nullptr,
+    /* .graph_plan_free    = */ nullptr,
+    /* .graph_plan_update  = */ nullptr,
+    /* .graph_plan_compute = */ nullptr,
+    /* .graph_compute      = */ b200_backend_graph_compute,
+    /* .event_record       = */ nullptr,
+    /* .event_wait         = */ nullptr,
+};
+
+static ggml_guid_t b200_guid() {
+    static ggml_guid guid = {0xb2, 0x00, 0x5a, 0x10, 0x0a, 0x77, 0x68, 0x73, 0x70, 0x72, 0x2d, 0x62, 0x32, 0x30, 0x30, 0x01};
+    return &guid;
+}
+
+// ---------------------------------------------------------------------------------------------
+// device
+// ---------------------------------------------------------------------------------------------
+static const char * b200_dev_get_name(ggml_backend_dev_t dev)        { return ((b200_device_ctx *) dev->context)->name.c_str(); }
+static const char * b200_dev_get_description(ggml_backend_dev_t dev) { return ((b200_device_ctx *) dev->context)->description.c_str(); }
+
+static void b200_dev_get_memory(ggml_backend_dev_t dev, size_t * free, size_t * total) {
+    b200_device_ctx * ctx = (b200_device_ctx *) dev->context;
+    *free = 0; *total = 0;
+    if (cudaSetDevice(ctx->device) == cudaSuccess) cudaMemGetInfo(free, total);
+}
+
+static enum ggml_backend_dev_type b200_dev_get_type(ggml_backend_dev_t) { return GGML_BACKEND_DEVICE_TYPE_GPU; }
+
+static void b200_dev_get_props(ggml_backend_dev_t dev, struct ggml_backend_dev_props * props) {
+    props->name        = b200_dev_get_name(dev);
+    props->description = b200_dev_get_description(dev);
+    props->type        = GGML_BACKEND_DEVICE_TYPE_GPU;
+    b200_dev_get_memory(dev, &props->memory_free, &props->memory_total);
+    props->caps = { /* async */ true, /* host_buffer */ false, /* buffer_from_host_ptr */ false, /* events */ false };
+}
+
+static ggml_backend_t b200_dev_init_backend(ggml_backend_dev_t dev, const char *) {
+    b200_device_ctx * dctx = (b200_device_ctx *) dev->context;
+    if (!cuda_ok(cudaSetDevice(dctx->device), "cudaSetDevice")) return nullptr;
+    b200_backend_ctx * ctx = new b200_backend_ctx;
+    ctx->device = dctx->device;
+    ctx->name   = dctx->name;
+    if (!cuda_ok(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking), "cudaStreamCreate")) { delete ctx; return nullptr; }
+    return new ggml_backend{ b200_guid(), b200_backend_iface, dev, ctx };
+}
+
+static ggml_backend_buffer_type_t b200_dev_get_buffer_type(ggml_backend_dev_t dev) {
+    return &((b200_device_ctx *) dev->context)->buft;
+}
+
+static bool b200_op_supported(const struct ggml_tensor * op) {
+    const struct ggml_tensor * s0 = op->src[0];
+    const struct ggml_tensor * s1 = op->src[1];
+    switch (op->op) {
+        case GGML_OP_NONE: case GGML_OP_RESHAPE: case GGML_OP_VIEW: case GGML_OP_PERMUTE: case GGML_OP_TRANSPOSE:
+            return true;
+        case GGML_OP_MUL_MAT:
+            if (op->type != GGML_TYPE_F32 || op->nb[0] != 4) return false;
+            if (is_quant(s0->type)) {
+                return s0->view_src == nullptr && ggml_is_contiguous(s0) && s0->ne[2] == 1 && s0->ne[3] == 1 &&
+                       s1->type == GGML_TYPE_F32 && s1->nb[0] == 4 && s1->ne[2] == 1 && s1->ne[3] == 1 &&
+                       s1->ne[0] % 32 == 0 && (s1->nb[1] % 4) == 0;
+            }
+            if (s0->type == GGML_TYPE_F16) {
+                return s0->nb[0] == 2 && ((s1->type == GGML_TYPE_F32 && s1->nb[0] == 4) || (s1->type == GGML_TYPE_F16 && s1->nb[0] == 2)) &&
+                       s1->ne[2] % s0->ne[2] == 0 && s1->ne[3] % s0->ne[3] == 0 && s1->ne[2] * s1->ne[3] <= 65535;
+            }
+            return false;
+        case GGML_OP_FLASH_ATTN_EXT: {
+            const struct ggml_tensor * k = op->src[1], * v = op->src[2], * mask = op->src[3];
+            float max_bias, softcap;
+            memcpy(&max_bias, (const float *) op->op_params + 1, sizeof(float));
+            memcpy(&softcap,  (const float *) op->op_params + 2, sizeof(float));
+            return s0->type == GGML_TYPE_F32 && k->type == GGML_TYPE_F16 && v->type == GGML_TYPE_F16 &&
+                   s0->ne[0] == 64 && k->ne[0] == 64 && v->ne[0] == 64 && s0->ne[3] == 1 && k->ne[3] == 1 && v->ne[3] == 1 &&
+                   k->ne[2] == s0->ne[2] && v->ne[2] == s0->ne[2] && k->ne[1] == v->ne[1] &&
+                   s0->nb[0] == 4 && k->nb[0] == 2 && v->nb[0] == 2 && max_bias == 0.0f && softcap == 0.0f &&
+                   (!mask || (mask->type == GGML_TYPE_F16 && mask->nb[0] == 2 && mask->ne[0] >= k->ne[1] && mask->ne[1] >= s0->ne[1]));
+        }
+        case GGML_OP_NORM:
+            return s0->type == GGML_TYPE_F32 && s0->nb[0] == 4 && op->nb[0] == 4;
+        case GGML_OP_ADD:
+        case GGML_OP_MUL:
+            return s0->type == GGML_TYPE_F32 && s1->type == GGML_TYPE_F32 && op->type == GGML_TYPE_F32 && ggml_can_repeat(s1, s0);
+        case GGML_OP_SCALE:
+            return s0->type == GGML_TYPE_F32 && ggml_is_contiguous(s0) && ggml_is_contiguous(op);
+        case GGML_OP_UNARY:
+            return ggml_get_unary_op(op) == GGML_UNARY_OP_GELU && s0->type == GGML_TYPE_F32 && ggml_is_contiguous(s0) && ggml_is_contiguous(op);
+        case GGML_OP_CPY:
+        case GGML_OP_DUP:
+        case GGML_OP_CONT: {
+            const enum ggml_type a = s0->type, b = op->type;
+            return (a == GGML_TYPE_F32 && (b == GGML_TYPE_F32 || b == GGML_TYPE_F16)) ||
+                   (a == GGML_TYPE_F16 && (b == GGML_TYPE_F32 || b == GGML_TYPE_F16)) || (a == GGML_TYPE_I32 && b == GGML_TYPE_I32);
+        }
+        case GGML_OP_GET_ROWS:
+            if (s1->type != GGML_TYPE_I32 || s1->ne[1] != 1 || s1->ne[2] != 1 || !ggml_is_contiguous(s1)) return false;
+            if (is_quant(s0->type)) return s0->view_src == nullptr && ggml_is_contiguous(s0) && s0->ne[2] == 1 && s0->ne[3] == 1;
+            return (s0->type == GGML_TYPE_F16 || s0->type == GGML_TYPE_F32) && s0->ne[2] == 1 && s0->ne[3] == 1;
+        case GGML_OP_IM2COL: {
+            const int32_t * p = (const int32_t *) op->op_params;
+            return p[6] == 0 && op->type == GGML_TYPE_F16 && s1->type == GGML_TYPE_F32 && s1->nb[0] == 4 && s1->ne[2] == 1 && s1->ne[3] == 1;
+        }
+        case GGML_OP_SOFT_MAX: {
+            float max_bias;
+            memcpy(&max_bias, (const float *) op->op_params + 1, sizeof(float));
+            return max_bias == 0.0f && s0->type == GGML_TYPE_F32 && ggml_is_contiguous(s0) && ggml_is_contiguous(op) &&
+                   (!s1 || ((s1->type == GGML_TYPE_F32 || s1->type == GGML_TYPE_F16) && ggml_is_contiguous(s1)));
+        }
+        case GGML_OP_CONCAT:
+            return s0->type == GGML_TYPE_F32 && s1->type == GGML_TYPE_F32;
+        default:
+            return false;
+    }
+}
+
+static bool b200_dev_supports_op(ggml_backend_dev_t, const struct ggml_tensor * op) { return b200_op_supported(op); }
+
+static bool b200_dev_supports_buft(ggml_backend_dev_t dev, ggml_backend_buffer_type_t buft) {
+    return buft == &((b200_device_ctx *) dev->context)->buft;
+}
+
+static const struct ggml_backend_device_i b200_device_iface = {
+    /* .get_name             = */ b200_dev_get_name,
+    /* .get_description      = */ b200_dev_get_description,
+    /* .get_memory           = */ b200_dev_get_memory,
+    /* .get_type             = */ b200_dev_get_type,
+    /* .get_props            = */ b200_dev_get_props,
+    /* .init_backend         = */ b200_dev_init_backend,
+    /* .get_buffer_type      = */ b200_dev_get_buffer_type,
+    /* .get_host_buffer_type = */ nullptr,
+    /* .buffer_from_host_ptr = */ nullptr,
+    /* .supports_op          = */ b200_dev_supports_op,
+    /* .supports_buft        = */ b200_dev_supports_buft,
+    /* .offload_op           = */ nullptr,
+    /* .event_new            = */ nullptr,
+    /* .event_free           = */ nullptr,
+    /* .event_synchronize    = */ nullptr,
+};
+
+// ---------------------------------------------------------------------------------------------
+// registry
+// ---------------------------------------------------------------------------------------------
+struct b200_reg_ctx {
+    std::vector<ggml_backend_device *> devices;
+};
+
+static const char * b200_reg_get_name(ggml_backend_reg_t) { return "B200"; }
+static size_t b200_reg_get_device_count(ggml_backend_reg_t reg) { return ((b200_reg_ctx *) reg->context)->devices.size(); }
+static ggml_backend_dev_t b200_reg_get_device(ggml_backend_reg_t reg, size_t index) {
+    b200_reg_ctx * ctx = (b200_reg_ctx *) reg->context;
+    GGML_ASSERT(index < ctx->devices.size());
+    return ctx->devices[index];
+}
+
+static struct ggml_backend_feature * b200_get_features(ggml_backend_reg_t) {
+    static struct ggml_backend_feature features[] = {
+        { "ARCH", "sm_100a" },
+        { "CPU_PARITY", "avx2-fma-f16c" },
+        { nullptr, nullptr },
+    };
+    return features;
+}
+
+static void * b200_reg_get_proc_address(ggml_backend_reg_t, const char * name) {
+    if (strcmp(name, "ggml_backend_get_features") == 0) return (void *) b200_get_features;
+    if (strcmp(name, "b200_stat_nodes") == 0)  return (void *) b200_stat_nodes;
+    if (strcmp(name, "b200_stat_graphs") == 0) return (void *) b200_stat_graphs;
+    if (strcmp(name, "b200_stat_h2d") == 0)    return (void *) b200_stat_h2d;
+    if (strcmp(name, "b200_stat_d2h") == 0)    return (void *) b200_stat_d2h;
+    if (strcmp(name, "b200_launch_count") == 0) return (void *) b200_launch_count;
+    return nullptr;
+}
+
+static const struct ggml_backend_reg_i b200_reg_iface = {
+    /* .get_name         = */ b200_reg_get_name,
+    /* .get_device_count = */ b200_reg_get_device_count,
+    /* .get_device       = */ b200_reg_get_device,
+    /* .get_proc_address = */ b200_reg_get_proc_address,
+};
+
+static int b200_visible_devices() {
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); return 0; }
+    return n > B200_MAX_DEVICES ? B200_MAX_DEVICES : n;
+}
+
+extern "C" {
+
+GGML_BACKEND_API int ggml_backend_score(void) {
+    // 0 = "not supported on this system": without a CUDA device the plugin refuses to load,
+    // it never computes on the host.
+    return b200_visible_devices() > 0 ? 100 : 0;
+}
+
+GGML_BACKEND_API ggml_backend_reg_t ggml_backend_init(void) {
+    static std::mutex mu;
+    static ggml_backend_reg reg;
+    static bool initialised = false;
+    std::lock_guard<std::mutex> lk(mu);
+    if (!initialised) {
+        b200_reg_ctx * ctx = new b200_reg_ctx;
+        const int n = b200_visible_devices();
+        for (int i = 0; i < n; ++i) {
+            cudaDeviceProp prop;
+            if (cudaGetDeviceProperties(&prop, i) != cudaSuccess) continue;
+            if (prop.major != 10) {
+                fprintf(stderr, "ggml-b200: device %d (%s, sm_%d%d) is not sm_100: skipped\n", i, prop.name, prop.major, prop.minor);
+                continue;
+            }
+            b200_device_ctx * dctx = new b200_device_ctx;
+            dctx->device      = i;
+            dctx->name        = "B200_" + std::to_string(i);
+            dctx->description = prop.name;
+            dctx->buft_name   = dctx->name;
+            ggml_backend_device * dev = new ggml_backend_device{ b200_device_iface, &reg, dctx };
+            dctx->buft = { { b200_buft_get_name, b200_buft_alloc_buffer, b200_buft_get_alignment, nullptr, nullptr, b200_buft_is_host }, dev, dctx };
+            ctx->devices.push_back(dev);
+        }
+        reg = ggml_backend_reg{ GGML_BACKEND_API_VERSION, b200_reg_iface, ctx };
+        initialised = true;
+    }
+    return &reg;
+}
+
+}

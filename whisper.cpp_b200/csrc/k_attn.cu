@@ -1,0 +1,296 @@
+// Attention kernels that keep the arithmetic order of the reference CPU backend:
+//  * flash_attn_ext with F16 K/V (ggml/src/ggml-cpu/ops.cpp:6638-6851): scores by the f16 dot
+//    product order of vec.cpp:128-167, one key after the other through the online softmax, the V
+//    accumulator held in F16 and rounded after every key (vec.h:180-197, 295-322), exp() as glibc's
+//    expf (table of 2^(i/32) + degree-3 polynomial in double);
+//  * soft_max (ops.cpp:4641-4737) with the vectorised exp of vec.h:603-640 and its 8-wide sums.
+#include "b200_common.cuh"
+#include <math.h>
+#include <mutex>
+
+// ---- glibc expf -----------------------------------------------------------------------------
+__constant__ uint64_t c_exp2f_tab[32];
+
+static void ensure_exp_table() {
+    static std::mutex mu;
+    static bool done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    std::lock_guard<std::mutex> lk(mu);
+    if (dev < 0 || dev >= 64 || done[dev]) return;
+    uint64_t tab[32];
+    for (int i = 0; i < 32; ++i) {
+        const double v = (double) exp2l((long double) i / 32.0L);
+        uint64_t bits;
+        memcpy(&bits, &v, 8);
+        tab[i] = bits - ((uint64_t) i << 47);
+    }
+    cudaMemcpyToSymbol(c_exp2f_tab, tab, sizeof(tab));
+    done[dev] = true;
+}
+
+__device__ __forceinline__ float expf_glibc(float x) {
+    const uint32_t ux = __float_as_uint(x);
+    const uint32_t abstop = (ux >> 20) & 0x7ffu;
+    if (abstop >= 0x42bu) {                       // |x| >= 88
+        if (ux == 0xff800000u) return 0.0f;       // -inf
+        if (abstop >= 0x7f8u) return x + x;       // nan, +inf
+        if (x > 0x1.62e42ep6f) return __int_as_float(0x7f800000);
+        if (x < -0x1.9fe368p6f) return 0.0f;
+    }
+    const double InvLn2N = 0x1.71547652b82fep+0 * 32.0;
+    const double Shift   = 0x1.8p+52;
+    const double C0 = 0x1.c6af84b912394p-5 / 32.0 / 32.0 / 32.0;
+    const double C1 = 0x1.ebfce50fac4f3p-3 / 32.0 / 32.0;
+    const double C2 = 0x1.62e42ff0c52d6p-1 / 32.0;
+    const double xd = (double) x;
+    double z  = __dmul_rn(InvLn2N, xd);
+    double kd = __dadd_rn(z, Shift);
+    const uint64_t ki = (uint64_t) __double_as_longlong(kd);
+    kd = __dadd_rn(kd, -Shift);
+    const double r = __dadd_rn(z, -kd);
+    uint64_t t = c_exp2f_tab[ki & 31];
+    t += ki << 47;
+    const double s = __longlong_as_double((long long) t);
+    z = __fma_rn(C0, r, C1);
+    const double r2 = __dmul_rn(r, r);
+    double y = __fma_rn(C2, r, 1.0);
+    y = __fma_rn(z, r2, y);
+    y = __dmul_rn(y, s);
+    return (float) y;
+}
+
+// ---- flash attention ------------------------------------------------------------------------
+// One warp per (query row, head).  Per 32 keys: every lane computes one score with the exact
+// reduction tree, a prefix maximum tells each key the running maximum it meets, exp() runs in
+// parallel, and the 64-wide F16 accumulator (two dims per lane) is then updated key by key.
+template <bool S_FMA>
+__global__ void __launch_bounds__(128)
+k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
+                 const char * __restrict__ k, int64_t nbk1, int64_t nbk2,
+                 const char * __restrict__ v, int64_t nbv1, int64_t nbv2,
+                 const char * __restrict__ mask, int64_t nbm1,
+                 float * __restrict__ dst, int64_t n_q, int64_t n_kv, int64_t n_head, float scale) {
+    __shared__ __align__(16) float Qs[4][64];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t iq1 = (int64_t) blockIdx.x * 4 + warp;
+    const int64_t h   = blockIdx.y;
+    if (iq1 >= n_q) return;
+
+    {
+        const float * qp = (const float *) (q + iq1 * nbq1 + h * nbq2);
+        Qs[warp][lane]      = round_f16(qp[lane]);
+        Qs[warp][lane + 32] = round_f16(qp[lane + 32]);
+    }
+    __syncwarp();
+
+    const char * kh = k + h * nbk2;
+    const char * vh = v + h * nbv2;
+    const __half * mp = mask ? (const __half *) (mask + iq1 * nbm1) : nullptr;
+
+    float M = -INFINITY, S = 0.0f;
+    float a0 = 0.0f, a1 = 0.0f;      // F16 accumulator values for dims 2*lane, 2*lane+1
+
+    for (int64_t ic0 = 0; ic0 < n_kv; ic0 += 32) {
+        const int64_t ic = ic0 + lane;
+        const bool valid = ic < n_kv;
+        float mv = 0.0f;
+        if (mp && valid) mv = __half2float(mp[ic]);
+        const bool skip = !valid || (mv == -INFINITY);
+
+        float s = -INFINITY;
+        if (!skip) {
+            float acc[32];
+            const uint4 * kp = (const uint4 *) (kh + ic * nbk1);
+#pragma unroll
+            for (int step = 0; step < 2; ++step) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint4 kv = kp[step * 4 + c];
+                    const float4 qa = *(const float4 *) &Qs[warp][step * 32 + c * 8];
+                    const float4 qb = *(const float4 *) &Qs[warp][step * 32 + c * 8 + 4];
+                    const float2 k0 = __half22float2(*(const __half2 *) &kv.x);
+                    const float2 k1 = __half22float2(*(const __half2 *) &kv.y);
+                    const float2 k2 = __half22float2(*(const __half2 *) &kv.z);
+                    const float2 k3 = __half22float2(*(const __half2 *) &kv.w);
+                    float * a = &acc[c * 8];
+                    if (step == 0) {
+                        a[0] = __fmaf_rn(k0.x, qa.x, 0.0f); a[1] = __fmaf_rn(k0.y, qa.y, 0.0f);
+                        a[2] = __fmaf_rn(k1.x, qa.z, 0.0f); a[3] = __fmaf_rn(k1.y, qa.w, 0.0f);
+                        a[4] = __fmaf_rn(k2.x, qb.x, 0.0f); a[5] = __fmaf_rn(k2.y, qb.y, 0.0f);
+                        a[6] = __fmaf_rn(k3.x, qb.z, 0.0f); a[7] = __fmaf_rn(k3.y, qb.w, 0.0f);
+                    } else {
+                        a[0] = __fmaf_rn(k0.x, qa.x, a[0]); a[1] = __fmaf_rn(k0.y, qa.y, a[1]);
+                        a[2] = __fmaf_rn(k1.x, qa.z, a[2]); a[3] = __fmaf_rn(k1.y, qa.w, a[3]);
+                        a[4] = __fmaf_rn(k2.x, qb.x, a[4]); a[5] = __fmaf_rn(k2.y, qb.y, a[5]);
+                        a[6] = __fmaf_rn(k3.x, qb.z, a[6]); a[7] = __fmaf_rn(k3.y, qb.w, a[7]);
+                    }
+                }
+            }
+            float y[8];
+#pragma unroll
+            for (int p = 0; p < 8; ++p)
+                y[p] = __fadd_rn(__fadd_rn(acc[p], acc[16 + p]), __fadd_rn(acc[8 + p], acc[24 + p]));
+            const float t0 = __fadd_rn(y[0], y[4]), t1 = __fadd_rn(y[1], y[5]);
+            const float t2 = __fadd_rn(y[2], y[6]), t3 = __fadd_rn(y[3], y[7]);
+            s = __fadd_rn(__fadd_rn(t0, t1), __fadd_rn(t2, t3));
+            s = __fmul_rn(s, scale);
+            s = __fadd_rn(s, mv);
+        }
+
+        // running maximum seen by each key (exclusive prefix over non-skipped keys)
+        float pm = s;   // skipped keys carry -inf
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float t = __shfl_up_sync(0xffffffffu, pm, o);
+            if (lane >= o) pm = fmaxf(pm, t);
+        }
+        float ex = __shfl_up_sync(0xffffffffu, pm, 1);
+        if (lane == 0) ex = -INFINITY;
+        const float Mprev  = fmaxf(M, ex);
+        const bool  newmax = !skip && (s > Mprev);
+        float e = 1.0f;
+        if (!skip) e = expf_glibc(newmax ? __fadd_rn(Mprev, -s) : __fadd_rn(s, -Mprev));
+        const float ms_l = newmax ? e : 1.0f;
+        const float vs_l = newmax ? 1.0f : e;
+        const unsigned skipmask = __ballot_sync(0xffffffffu, skip);
+        M = fmaxf(M, __shfl_sync(0xffffffffu, pm, 31));
+
+        const int nk = (int) min((int64_t) 32, n_kv - ic0);
+        __half2 vraw[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (i < nk && !((skipmask >> i) & 1u))
+                vraw[i] = *(const __half2 *) (vh + (ic0 + i) * nbv1 + lane * 4);
+            else
+                vraw[i] = __floats2half2_rn(0.0f, 0.0f);
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            const float ms = __shfl_sync(0xffffffffu, ms_l, i);
+            const float vs = __shfl_sync(0xffffffffu, vs_l, i);
+            if (i < nk && !((skipmask >> i) & 1u)) {
+                if (ms != 1.0f) {
+                    a0 = round_f16(__fmul_rn(a0, ms));
+                    a1 = round_f16(__fmul_rn(a1, ms));
+                }
+                const float2 vf = __half22float2(vraw[i]);
+                a0 = round_f16(__fmaf_rn(vf.x, vs, a0));
+                a1 = round_f16(__fmaf_rn(vf.y, vs, a1));
+                S = S_FMA ? __fmaf_rn(S, ms, vs) : __fadd_rn(__fmul_rn(S, ms), vs);
+            }
+        }
+    }
+
+    const float S_inv = __fdiv_rn(1.0f, S);
+    float2 o;
+    o.x = __fmul_rn(a0, S_inv);
+    o.y = __fmul_rn(a1, S_inv);
+    *(float2 *) (dst + (iq1 * n_head + h) * 64 + lane * 2) = o;
+}
+
+// The host compiler of the reference contracts "S*ms + vs" into one FMA (GNU mode, -mfma).
+static bool g_fa_s_fma = true;
+extern "C" void b200_set_fa_sum_fma(int on) { g_fa_s_fma = on != 0; }
+
+extern "C" int b200_flash_attn_ext(const float * q, int64_t nbq1, int64_t nbq2,
+                                   const void * k, int64_t nbk1, int64_t nbk2,
+                                   const void * v, int64_t nbv1, int64_t nbv2,
+                                   const void * mask, int64_t nbm1,
+                                   float * dst, int64_t n_q, int64_t n_kv, int64_t n_head, float scale, void * stream) {
+    if (n_q <= 0 || n_head <= 0) return 0;
+    if (n_kv <= 0 || n_head > 65535) return B200_ERR_ARG;
+    if (((uintptr_t) k & 15) || (nbk1 & 15) || (nbk2 & 15) || ((uintptr_t) v & 3) || (nbv1 & 3) || (nbv2 & 3)) return B200_ERR_ARG;
+    if (((uintptr_t) q & 3) || (nbq1 & 3) || (nbq2 & 3) || ((uintptr_t) dst & 7)) return B200_ERR_ARG;
+    ensure_exp_table();
+    dim3 grid((unsigned) ((n_q + 3) / 4), (unsigned) n_head);
+    if (g_fa_s_fma)
+        k_flash_attn_ext<true><<<grid, 128, 0, as_stream(stream)>>>((const char *) q, nbq1, nbq2, (const char *) k, nbk1, nbk2,
+            (const char *) v, nbv1, nbv2, (const char *) mask, nbm1, dst, n_q, n_kv, n_head, scale);
+    else
+        k_flash_attn_ext<false><<<grid, 128, 0, as_stream(stream)>>>((const char *) q, nbq1, nbq2, (const char *) k, nbk1, nbk2,
+            (const char *) v, nbv1, nbv2, (const char *) mask, nbm1, dst, n_q, n_kv, n_head, scale);
+    B200_RETURN_LAST();
+}
+
+// ---- soft_max -------------------------------------------------------------------------------
+__device__ __forceinline__ float v_expf_avx2(float x) {     // vec.h:603-640, one element
+    const float r = 0x1.8p23f;
+    const float z = __fmaf_rn(x, 0x1.715476p+0f, r);
+    const float n = __fadd_rn(z, -r);
+    const float b = __fmaf_rn(-n, 0x1.7f7d1cp-20f, __fmaf_rn(-n, 0x1.62e4p-1f, x));
+    const uint32_t e = __float_as_uint(z) << 23;
+    const float kf = __uint_as_float(e + 0x3f800000u);
+    const bool  c = fabsf(n) > 126.0f;
+    const float u = __fmul_rn(b, b);
+    const float j = __fmaf_rn(__fmaf_rn(__fmaf_rn(0x1.0e4020p-7f, b, 0x1.573e2ep-5f), u,
+                                        __fmaf_rn(0x1.555e66p-3f, b, 0x1.fffdb6p-2f)),
+                              u, __fmul_rn(0x1.ffffecp-1f, b));
+    if (!c) return __fmaf_rn(j, kf, kf);
+    const uint32_t g = (n <= 0.0f) ? 0x82000000u : 0u;
+    const float s1 = __uint_as_float(g + 0x7f000000u);
+    const float s2 = __uint_as_float(e - g);
+    if (fabsf(n) > 192.0f) return __fmul_rn(s1, s1);
+    return __fmul_rn(__fmaf_rn(s2, j, s2), s1);
+}
+
+// one warp per row; mask row = (row % ne01), f16 or f32
+__global__ void __launch_bounds__(128)
+k_soft_max(const float * __restrict__ x, const char * __restrict__ mask, int mask_f16, int64_t mask_nb1,
+           float * __restrict__ y, int64_t ne00, int64_t nrows, int64_t ne01, float scale) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row = (int64_t) blockIdx.x * 4 + warp;
+    if (row >= nrows) return;
+    const float * sp = x + row * ne00;
+    float *       dp = y + row * ne00;
+    const char *  mp = mask ? mask + (row % ne01) * mask_nb1 : nullptr;
+
+    float mx = -INFINITY;
+    for (int64_t i = lane; i < ne00; i += 32) {
+        float w = __fmul_rn(sp[i], scale);
+        if (mp) w = __fadd_rn(w, mask_f16 ? __half2float(((const __half *) mp)[i]) : ((const float *) mp)[i]);
+        dp[i] = w;
+        mx = fmaxf(mx, w);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    __syncwarp();
+
+    // groups of 8 elements: lanes 8g'..8g'+7 handle one group; 4 groups per pass, in order
+    const int64_t n8 = ne00 & ~(int64_t) 7;
+    const int sub = lane >> 3, l8 = lane & 7;
+    double sum = 0.0;    // exact replay needs group order: accumulate in lane 0 of the warp
+    for (int64_t base = 0; base < n8; base += 32) {
+        const int64_t i = base + sub * 8 + l8;
+        float val = 0.0f;
+        if (i < n8) { val = v_expf_avx2(__fadd_rn(dp[i], -mx)); dp[i] = val; }
+        float t = __fadd_rn(val, __shfl_xor_sync(0xffffffffu, val, 4));
+        t = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, 2));
+        t = __fadd_rn(t, __shfl_xor_sync(0xffffffffu, t, 1));
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+            const float tg = __shfl_sync(0xffffffffu, t, g * 8);
+            if (base + g * 8 < n8) sum += (double) tg;
+        }
+    }
+    for (int64_t i = n8; i < ne00; ++i) {       // scalar tail uses libm expf
+        float val = 0.0f;
+        if (lane == 0) { val = expf_glibc(__fadd_rn(dp[i], -mx)); dp[i] = val; }
+        val = __shfl_sync(0xffffffffu, val, 0);
+        sum += (double) val;
+    }
+    __syncwarp();
+    const float inv = (float) (1.0 / sum);
+    for (int64_t i = lane; i < ne00; i += 32) dp[i] = __fmul_rn(dp[i], inv);
+}
+
+extern "C" int b200_soft_max(const float * x, const void * mask, int mask_type, int64_t mask_nb1, int64_t mask_ne1,
+                             float * y, int64_t ne00, int64_t nrows, int64_t ne01, float scale, void * stream) {
+    (void) mask_ne1;
+    if (nrows <= 0 || ne00 <= 0) return 0;
+    if (mask && mask_type != B200_TYPE_F16 && mask_type != B200_TYPE_F32) return B200_ERR_ARG;
+    ensure_exp_table();
+    k_soft_max<<<(unsigned) ((nrows + 3) / 4), 128, 0, as_stream(stream)>>>(x, (const char *) mask, mask_type == B200_TYPE_F16,
+                                                                            mask_nb1, y, ne00, nrows, ne01, scale);
+    B200_RETURN_LAST();
+}

@@ -1,0 +1,226 @@
+// Row-wise and element-wise operators: norm, add/mul with broadcast, scale, GELU (F16 table),
+// cpy/dup/cont, get_rows (f16/f32 tables), concat.
+#include "b200_common.cuh"
+#include <mutex>
+
+// ---- norm: one warp per row (ggml/src/ggml-cpu/ops.cpp:3109-3158) -----------------------------
+// Sums are formed in double as in the reference; only their association differs, which moves the
+// double result by ~1e-16 relative, far below the f32 rounding of mean and variance.
+__global__ void __launch_bounds__(128)
+k_norm(const char * __restrict__ x, char * __restrict__ y, int64_t ne00, int64_t ne01, int64_t ne02, int64_t nrows,
+       int64_t nbx1, int64_t nbx2, int64_t nbx3, int64_t nby1, int64_t nby2, int64_t nby3, float eps) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row = (int64_t) blockIdx.x * 4 + warp;
+    if (row >= nrows) return;
+    const int64_t i3 = row / (ne01 * ne02), i2 = (row / ne01) % ne02, i1 = row % ne01;
+    const float * xp = (const float *) (x + i1 * nbx1 + i2 * nbx2 + i3 * nbx3);
+    float *       yp = (float *)       (y + i1 * nby1 + i2 * nby2 + i3 * nby3);
+
+    double sum = 0.0;
+    for (int64_t i = lane; i < ne00; i += 32) sum += (double) xp[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = (float) (sum / (double) ne00);
+
+    double sum2 = 0.0;
+    for (int64_t i = lane; i < ne00; i += 32) {
+        const float v = __fadd_rn(xp[i], -mean);
+        sum2 += (double) __fmul_rn(v, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum2 += __shfl_xor_sync(0xffffffffu, sum2, o);
+    const float variance = (float) (sum2 / (double) ne00);
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(variance, eps)));
+    for (int64_t i = lane; i < ne00; i += 32) yp[i] = __fmul_rn(__fadd_rn(xp[i], -mean), scale);
+}
+
+extern "C" int b200_norm(const float * x, float * y, int64_t ne00, int64_t ne01, int64_t ne02, int64_t ne03,
+                         const int64_t * nbx, const int64_t * nby, float eps, void * stream) {
+    const int64_t nrows = ne01 * ne02 * ne03;
+    if (nrows <= 0 || ne00 <= 0) return 0;
+    k_norm<<<(unsigned) ((nrows + 3) / 4), 128, 0, as_stream(stream)>>>((const char *) x, (char *) y, ne00, ne01, ne02, nrows,
+        nbx[1], nbx[2], nbx[3], nby[1], nby[2], nby[3], eps);
+    B200_RETURN_LAST();
+}
+
+// ---- add / mul with broadcast ----------------------------------------------------------------
+template <int OP>
+__global__ void k_binary(const char * __restrict__ a, Dims4 da, const char * __restrict__ b, Dims4 db,
+                         char * __restrict__ d, int64_t nbd0, int64_t nbd1, int64_t nbd2, int64_t nbd3, int64_t n) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int64_t i0 = i % da.ne[0], t1 = i / da.ne[0];
+    const int64_t i1 = t1 % da.ne[1], t2 = t1 / da.ne[1];
+    const int64_t i2 = t2 % da.ne[2], i3 = t2 / da.ne[2];
+    const float x = *(const float *) (a + i0 * da.nb[0] + i1 * da.nb[1] + i2 * da.nb[2] + i3 * da.nb[3]);
+    const float y = *(const float *) (b + (i0 % db.ne[0]) * db.nb[0] + (i1 % db.ne[1]) * db.nb[1] +
+                                          (i2 % db.ne[2]) * db.nb[2] + (i3 % db.ne[3]) * db.nb[3]);
+    *(float *) (d + i0 * nbd0 + i1 * nbd1 + i2 * nbd2 + i3 * nbd3) = OP == 0 ? __fadd_rn(x, y) : __fmul_rn(x, y);
+}
+
+extern "C" int b200_binary(int op, const float * a, const int64_t * nea, const int64_t * nba,
+                           const float * b, const int64_t * neb, const int64_t * nbb,
+                           float * dst, const int64_t * nbd, void * stream) {
+    const Dims4 da = make_dims(nea, nba), db = make_dims(neb, nbb);
+    const int64_t n = da.ne[0] * da.ne[1] * da.ne[2] * da.ne[3];
+    if (n <= 0) return 0;
+    for (int i = 0; i < 4; ++i) if (db.ne[i] <= 0 || da.ne[i] % db.ne[i] != 0) return B200_ERR_ARG;
+    const unsigned grid = (unsigned) ((n + 255) / 256);
+    if (op == 0)      k_binary<0><<<grid, 256, 0, as_stream(stream)>>>((const char *) a, da, (const char *) b, db, (char *) dst, nbd[0], nbd[1], nbd[2], nbd[3], n);
+    else if (op == 1) k_binary<1><<<grid, 256, 0, as_stream(stream)>>>((const char *) a, da, (const char *) b, db, (char *) dst, nbd[0], nbd[1], nbd[2], nbd[3], n);
+    else return B200_ERR_ARG;
+    B200_RETURN_LAST();
+}
+
+// ---- scale -----------------------------------------------------------------------------------
+__global__ void k_scale(const float * __restrict__ x, float * __restrict__ y, int64_t n, float s) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = __fmul_rn(x[i], s);
+}
+extern "C" int b200_scale(const float * x, float * y, int64_t n, float s, void * stream) {
+    if (n <= 0) return 0;
+    k_scale<<<(unsigned) ((n + 255) / 256), 256, 0, as_stream(stream)>>>(x, y, n, s);
+    B200_RETURN_LAST();
+}
+
+// ---- GELU through the F16 table ----------------------------------------------------------------
+__device__ uint16_t g_gelu_table[1 << 16];
+extern "C" void b200_build_gelu_table(uint16_t * table);
+
+static int ensure_gelu_table() {
+    static std::mutex mu;
+    static bool done[64] = {false};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int) e;
+    std::lock_guard<std::mutex> lk(mu);
+    if (dev < 0 || dev >= 64) return B200_ERR_ARG;
+    if (done[dev]) return 0;
+    static uint16_t host_table[1 << 16];
+    static bool built = false;
+    if (!built) { b200_build_gelu_table(host_table); built = true; }
+    e = cudaMemcpyToSymbol(g_gelu_table, host_table, sizeof(host_table));
+    if (e != cudaSuccess) return (int) e;
+    done[dev] = true;
+    return 0;
+}
+
+__global__ void k_gelu(const float * __restrict__ x, float * __restrict__ y, int64_t n) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = x[i];
+    float r;
+    if (v <= -10.0f)      r = 0.0f;
+    else if (v >= 10.0f)  r = v;
+    else                  r = __half2float(__ushort_as_half(g_gelu_table[__half_as_ushort(__float2half_rn(v))]));
+    y[i] = r;
+}
+extern "C" int b200_gelu(const float * x, float * y, int64_t n, void * stream) {
+    if (n <= 0) return 0;
+    const int e = ensure_gelu_table();
+    if (e) return e;
+    k_gelu<<<(unsigned) ((n + 255) / 256), 256, 0, as_stream(stream)>>>(x, y, n);
+    B200_RETURN_LAST();
+}
+
+// ---- cpy / dup / cont --------------------------------------------------------------------------
+template <typename TS, typename TD> __device__ __forceinline__ TD cvt(TS v);
+template <> __device__ __forceinline__ float  cvt<float, float>(float v)   { return v; }
+template <> __device__ __forceinline__ __half cvt<float, __half>(float v)  { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __half cvt<__half, __half>(__half v){ return v; }
+template <> __device__ __forceinline__ float  cvt<__half, float>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ int    cvt<int, int>(int v)         { return v; }
+
+template <typename TS, typename TD>
+__global__ void k_cpy(const char * __restrict__ s, Dims4 ds, char * __restrict__ d, Dims4 dd, int64_t n) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int64_t r = i;
+    const int64_t s0 = r % ds.ne[0]; r /= ds.ne[0];
+    const int64_t s1 = r % ds.ne[1]; r /= ds.ne[1];
+    const int64_t s2 = r % ds.ne[2]; const int64_t s3 = r / ds.ne[2];
+    r = i;
+    const int64_t d0 = r % dd.ne[0]; r /= dd.ne[0];
+    const int64_t d1 = r % dd.ne[1]; r /= dd.ne[1];
+    const int64_t d2 = r % dd.ne[2]; const int64_t d3 = r / dd.ne[2];
+    const TS v = *(const TS *) (s + s0 * ds.nb[0] + s1 * ds.nb[1] + s2 * ds.nb[2] + s3 * ds.nb[3]);
+    *(TD *) (d + d0 * dd.nb[0] + d1 * dd.nb[1] + d2 * dd.nb[2] + d3 * dd.nb[3]) = cvt<TS, TD>(v);
+}
+
+extern "C" int b200_cpy(const void * src, int src_type, const int64_t * nes, const int64_t * nbs,
+                        void * dst, int dst_type, const int64_t * ned, const int64_t * nbd, void * stream) {
+    const Dims4 ds = make_dims(nes, nbs), dd = make_dims(ned, nbd);
+    const int64_t n = ds.ne[0] * ds.ne[1] * ds.ne[2] * ds.ne[3];
+    if (n != dd.ne[0] * dd.ne[1] * dd.ne[2] * dd.ne[3]) return B200_ERR_ARG;
+    if (n <= 0) return 0;
+    const unsigned grid = (unsigned) ((n + 255) / 256);
+    cudaStream_t st = as_stream(stream);
+    if      (src_type == B200_TYPE_F32 && dst_type == B200_TYPE_F32) k_cpy<float, float><<<grid, 256, 0, st>>>((const char *) src, ds, (char *) dst, dd, n);
+    else if (src_type == B200_TYPE_F32 && dst_type == B200_TYPE_F16) k_cpy<float, __half><<<grid, 256, 0, st>>>((const char *) src, ds, (char *) dst, dd, n);
+    else if (src_type == B200_TYPE_F16 && dst_type == B200_TYPE_F16) k_cpy<__half, __half><<<grid, 256, 0, st>>>((const char *) src, ds, (char *) dst, dd, n);
+    else if (src_type == B200_TYPE_F16 && dst_type == B200_TYPE_F32) k_cpy<__half, float><<<grid, 256, 0, st>>>((const char *) src, ds, (char *) dst, dd, n);
+    else if (src_type == B200_TYPE_I32 && dst_type == B200_TYPE_I32) k_cpy<int, int><<<grid, 256, 0, st>>>((const char *) src, ds, (char *) dst, dd, n);
+    else return B200_ERR_ARG;
+    B200_RETURN_LAST();
+}
+
+// ---- get_rows ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void k_get_rows(const char * __restrict__ table, int64_t row_stride, int64_t ne00, const int32_t * __restrict__ ids,
+                           int64_t n_ids, float * __restrict__ dst) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= ne00 * n_ids) return;
+    const int64_t r = i / ne00, c = i - r * ne00;
+    dst[i] = cvt<T, float>(*(const T *) (table + (int64_t) ids[r] * row_stride + c * (int64_t) sizeof(T)));
+}
+
+int b200_get_rows_q_launch(int type, const void * table, int64_t nb_total, int64_t ne00, const int32_t * ids,
+                           int64_t n_ids, float * dst, cudaStream_t st);
+
+extern "C" int b200_get_rows(int type, const void * table, int64_t nb_total_or_row_stride, int64_t ne00,
+                             const int32_t * ids, int64_t n_ids, float * dst, void * stream) {
+    const int64_t n = ne00 * n_ids;
+    if (n <= 0) return 0;
+    cudaStream_t st = as_stream(stream);
+    const unsigned grid = (unsigned) ((n + 255) / 256);
+    if (type == B200_TYPE_Q5_0 || type == B200_TYPE_Q8_0) {
+        if (ne00 % 32 != 0) return B200_ERR_ARG;
+        return b200_get_rows_q_launch(type, table, nb_total_or_row_stride, ne00, ids, n_ids, dst, st);
+    }
+    if (type == B200_TYPE_F16)      k_get_rows<__half><<<grid, 256, 0, st>>>((const char *) table, nb_total_or_row_stride, ne00, ids, n_ids, dst);
+    else if (type == B200_TYPE_F32) k_get_rows<float><<<grid, 256, 0, st>>>((const char *) table, nb_total_or_row_stride, ne00, ids, n_ids, dst);
+    else return B200_ERR_ARG;
+    B200_RETURN_LAST();
+}
+
+// ---- concat --------------------------------------------------------------------------------------
+__global__ void k_concat(const char * __restrict__ a, Dims4 da, const char * __restrict__ b, Dims4 db,
+                         char * __restrict__ d, Dims4 dd, int dim, int64_t n) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    int64_t idx[4];
+    int64_t r = i;
+    idx[0] = r % dd.ne[0]; r /= dd.ne[0];
+    idx[1] = r % dd.ne[1]; r /= dd.ne[1];
+    idx[2] = r % dd.ne[2]; idx[3] = r / dd.ne[2];
+    float v;
+    if (idx[dim] < da.ne[dim]) {
+        v = *(const float *) (a + idx[0] * da.nb[0] + idx[1] * da.nb[1] + idx[2] * da.nb[2] + idx[3] * da.nb[3]);
+    } else {
+        int64_t jb[4] = {idx[0], idx[1], idx[2], idx[3]};
+        jb[dim] -= da.ne[dim];
+        v = *(const float *) (b + jb[0] * db.nb[0] + jb[1] * db.nb[1] + jb[2] * db.nb[2] + jb[3] * db.nb[3]);
+    }
+    *(float *) (d + idx[0] * dd.nb[0] + idx[1] * dd.nb[1] + idx[2] * dd.nb[2] + idx[3] * dd.nb[3]) = v;
+}
+
+extern "C" int b200_concat(const float * a, const int64_t * nea, const int64_t * nba,
+                           const float * b, const int64_t * neb, const int64_t * nbb,
+                           float * dst, const int64_t * ned, const int64_t * nbd, int dim, void * stream) {
+    if (dim < 0 || dim > 3) return B200_ERR_ARG;
+    const Dims4 da = make_dims(nea, nba), db = make_dims(neb, nbb), dd = make_dims(ned, nbd);
+    const int64_t n = dd.ne[0] * dd.ne[1] * dd.ne[2] * dd.ne[3];
+    if (n <= 0) return 0;
+    k_concat<<<(unsigned) ((n + 255) / 256), 256, 0, as_stream(stream)>>>((const char *) a, da, (const char *) b, db, (char *) dst, dd, dim, n);
+    B200_RETURN_LAST();
+}

@@ -1,0 +1,455 @@
+// Block-quantised weights: plane layout, dequantise, Q8_0 activation quantisation and the
+// Q5_0/Q8_0 x Q8_0 matrix products.  Every sum is formed in the order of the reference's AVX2
+// kernels: eight partial sums ("lanes", four consecutive elements of a 32-block each) that are
+// FMA-accumulated block after block and reduced at the end as hsum_float_8 does
+// (ggml/src/ggml-cpu/ggml-cpu-quants.c:49-55, 3076-3100, 3869-3886).
+#include "b200_common.cuh"
+#include <string.h>
+
+std::atomic<int64_t> g_b200_launches{0};
+
+extern "C" int64_t b200_launch_count(void) { return g_b200_launches.load(); }
+extern "C" const char * b200_version(void) { return "b200-whisper 0.1 (sm_100a)"; }
+
+// ------------------------------------------------------------------------------------------------
+// host: ggml blocks <-> planes
+// ------------------------------------------------------------------------------------------------
+extern "C" int b200_blocks_to_planes(int type, const void * blocks, void * planes, int64_t nb_total,
+                                     int64_t nb_first, int64_t nb_count) {
+    const uint8_t * src = (const uint8_t *) blocks;   // nb_count blocks, starting at block nb_first
+    uint8_t * dst = (uint8_t *) planes;               // the whole tensor's planes
+    if (nb_first < 0 || nb_count < 0 || nb_first + nb_count > nb_total) return B200_ERR_ARG;
+    if (type == B200_TYPE_Q5_0) {
+        uint8_t * qs = dst, * qh = dst + 16 * nb_total, * d = dst + 20 * nb_total;
+        for (int64_t i = 0; i < nb_count; ++i) {
+            const uint8_t * b = src + 22 * i;
+            const int64_t   o = nb_first + i;
+            memcpy(d + 2 * o, b, 2);
+            memcpy(qh + 4 * o, b + 2, 4);
+            memcpy(qs + 16 * o, b + 6, 16);
+        }
+    } else if (type == B200_TYPE_Q8_0) {
+        uint8_t * qs = dst, * d = dst + 32 * nb_total;
+        for (int64_t i = 0; i < nb_count; ++i) {
+            const uint8_t * b = src + 34 * i;
+            const int64_t   o = nb_first + i;
+            memcpy(d + 2 * o, b, 2);
+            memcpy(qs + 32 * o, b + 2, 32);
+        }
+    } else {
+        return B200_ERR_ARG;
+    }
+    return 0;
+}
+
+extern "C" int b200_planes_to_blocks(int type, const void * planes, void * blocks, int64_t nb_total,
+                                     int64_t nb_first, int64_t nb_count) {
+    const uint8_t * src = (const uint8_t *) planes;
+    uint8_t * dst = (uint8_t *) blocks;
+    if (nb_first < 0 || nb_count < 0 || nb_first + nb_count > nb_total) return B200_ERR_ARG;
+    if (type == B200_TYPE_Q5_0) {
+        const uint8_t * qs = src, * qh = src + 16 * nb_total, * d = src + 20 * nb_total;
+        for (int64_t i = 0; i < nb_count; ++i) {
+            uint8_t *     b = dst + 22 * i;
+            const int64_t o = nb_first + i;
+            memcpy(b, d + 2 * o, 2);
+            memcpy(b + 2, qh + 4 * o, 4);
+            memcpy(b + 6, qs + 16 * o, 16);
+        }
+    } else if (type == B200_TYPE_Q8_0) {
+        const uint8_t * qs = src, * d = src + 32 * nb_total;
+        for (int64_t i = 0; i < nb_count; ++i) {
+            uint8_t *     b = dst + 34 * i;
+            const int64_t o = nb_first + i;
+            memcpy(b, d + 2 * o, 2);
+            memcpy(b + 2, qs + 32 * o, 32);
+        }
+    } else {
+        return B200_ERR_ARG;
+    }
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// dequantise (one thread per element)
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float dequant_elem(int type, const QPlanes & p, int64_t blk, int e) {
+    const float d = __half2float(p.d[blk]);
+    if (type == B200_TYPE_Q5_0) {
+        const uint8_t  b  = p.qs[blk * 16 + (e & 15)];
+        const uint32_t qh = p.qh[blk];
+        const int nib = (e < 16) ? (b & 0x0F) : (b >> 4);
+        const int hi  = (int) ((qh >> e) & 1u) << 4;
+        return (float) ((nib | hi) - 16) * d;     // x0*d with x0 converted int -> float
+    } else {
+        return (float) ((const int8_t *) p.qs)[blk * 32 + e] * d;
+    }
+}
+
+__global__ void k_dequantize(int type, QPlanes p, int64_t nb_first, int64_t n_elem, float * out) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_elem) return;
+    out[i] = dequant_elem(type, p, nb_first + (i >> 5), (int) (i & 31));
+}
+
+extern "C" int b200_dequantize(int type, const void * planes, int64_t nb_total, int64_t nb_first, int64_t nb_count,
+                               float * out, void * stream) {
+    if (type != B200_TYPE_Q5_0 && type != B200_TYPE_Q8_0) return B200_ERR_ARG;
+    if (nb_count <= 0) return 0;
+    const int64_t n = nb_count * 32;
+    k_dequantize<<<(unsigned) ((n + 255) / 256), 256, 0, as_stream(stream)>>>(type, q_planes(type, planes, nb_total), nb_first, n, out);
+    B200_RETURN_LAST();
+}
+
+// GET_ROWS from a quantised table: one thread per output element
+__global__ void k_get_rows_q(int type, QPlanes p, int64_t ne00, const int32_t * ids, int64_t n_ids, float * dst) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= ne00 * n_ids) return;
+    const int64_t r = i / ne00, c = i - r * ne00;
+    const int64_t blk = (int64_t) ids[r] * (ne00 >> 5) + (c >> 5);
+    dst[i] = dequant_elem(type, p, blk, (int) (c & 31));
+}
+
+int b200_get_rows_q_launch(int type, const void * table, int64_t nb_total, int64_t ne00, const int32_t * ids,
+                           int64_t n_ids, float * dst, cudaStream_t st) {
+    const int64_t n = ne00 * n_ids;
+    if (n <= 0) return 0;
+    k_get_rows_q<<<(unsigned) ((n + 255) / 256), 256, 0, st>>>(type, q_planes(type, table, nb_total), ne00, ids, n_ids, dst);
+    B200_RETURN_LAST();
+}
+
+// ------------------------------------------------------------------------------------------------
+// activation quantisation: one warp per 32-block
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void quantize_block_q8_0(float v, int lane, int8_t & q, float & d_out) {
+    float amax = fabsf(v);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float d  = __fdiv_rn(amax, 127.f);
+    const float id = (amax != 0.0f) ? __fdiv_rn(127.f, amax) : 0.0f;
+    q = (int8_t) __float2int_rn(__fmul_rn(v, id));
+    d_out = round_f16(d);
+    (void) lane;
+}
+
+__global__ void k_quantize_q8_0(const float * x, int64_t n_rows, int64_t nbk, int64_t row_stride, int8_t * qs, float * d) {
+    const int     lane = threadIdx.x & 31;
+    const int64_t blk  = ((int64_t) blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (blk >= n_rows * nbk) return;
+    const int64_t r = blk / nbk, ib = blk - r * nbk;
+    const float v = *(const float *) ((const char *) x + r * row_stride + (ib * 32 + lane) * 4);
+    int8_t q; float dd;
+    quantize_block_q8_0(v, lane, q, dd);
+    qs[blk * 32 + lane] = q;
+    if (lane == 0) d[blk] = dd;
+}
+
+extern "C" int b200_quantize_q8_0(const float * x, int64_t n_rows, int64_t k, int64_t row_stride_bytes,
+                                  int8_t * qs, float * d, void * stream) {
+    if (k % 32 != 0) return B200_ERR_ARG;
+    const int64_t nblk = n_rows * (k / 32);
+    if (nblk <= 0) return 0;
+    k_quantize_q8_0<<<(unsigned) ((nblk + 7) / 8), 256, 0, as_stream(stream)>>>(x, n_rows, k / 32, row_stride_bytes, qs, d);
+    B200_RETURN_LAST();
+}
+
+// ------------------------------------------------------------------------------------------------
+// GEMM: 64 x 32 output tile per CTA, 256 threads = 32 groups x 8 lanes; a thread owns lane j of an
+// 8 x 8 block of outputs.  Per 32-block: q = dp4a(w, x) (exact), acc = fma(dw*dx, q, acc).
+// ------------------------------------------------------------------------------------------------
+#define MAGIC_I 0x4B400000          // bits of 12582912.0f: integer adds to it stay exact floats
+#define MAGIC_F 12582912.0f
+
+template <int TYPE>
+__global__ void __launch_bounds__(256, 2)
+k_mul_mat_q(QPlanes w, int64_t M, int64_t nbk, const int8_t * __restrict__ xq, const float * __restrict__ xd,
+            int64_t N, float * __restrict__ dst, int64_t ldd) {
+    constexpr int BM = 64, BN = 32, KC = 4;
+    __shared__ __align__(16) int   Ws[KC][8][BM + 4];
+    __shared__ __align__(16) int   Xs[KC][8][BN + 4];
+    __shared__ __align__(16) float dWs[KC][BM];
+    __shared__ __align__(16) float dXs[KC][BN];
+
+    const int tid = threadIdx.x;
+    const int j   = tid & 7;
+    const int g   = tid >> 3;
+    const int gm  = g & 7;
+    const int gn  = g >> 3;
+    const int64_t m0 = (int64_t) blockIdx.x * BM;
+    const int64_t n0 = (int64_t) blockIdx.y * BN;
+
+    float acc[8][8];
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) acc[a][b] = 0.0f;
+
+    const int     sr  = tid & 63;      // W staging: row in tile
+    const int     skb = tid >> 6;      // W staging: block in chunk
+    const int     xc  = tid & 31;      // X staging: column in tile
+    const int     xkb = (tid >> 5) & 3;
+
+    for (int64_t kb0 = 0; kb0 < nbk; kb0 += KC) {
+        {   // stage W (dequantised to int8 lane words)
+            int   wv[8];
+            float dw = 0.0f;
+#pragma unroll
+            for (int t = 0; t < 8; ++t) wv[t] = 0;
+            const int64_t m = m0 + sr, ib = kb0 + skb;
+            if (m < M && ib < nbk) {
+                const int64_t blk = m * nbk + ib;
+                if (TYPE == B200_TYPE_Q5_0) {
+                    const uint4    q  = ((const uint4 *) w.qs)[blk];
+                    const uint32_t qh = w.qh[blk];
+                    const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                    for (int t = 0; t < 8; ++t) wv[t] = q5_lane_word(qw[t & 3], qh, t);
+                } else {
+                    const uint4 a = ((const uint4 *) w.qs)[blk * 2], b = ((const uint4 *) w.qs)[blk * 2 + 1];
+                    wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w;
+                    wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
+                }
+                dw = __half2float(w.d[blk]);
+            }
+#pragma unroll
+            for (int t = 0; t < 8; ++t) Ws[skb][t][sr] = wv[t];
+            dWs[skb][sr] = dw;
+        }
+        if (tid < 128) {   // stage X
+            int   xv[8];
+            float dx = 0.0f;
+#pragma unroll
+            for (int t = 0; t < 8; ++t) xv[t] = 0;
+            const int64_t n = n0 + xc, ib = kb0 + xkb;
+            if (n < N && ib < nbk) {
+                const uint4 * p = (const uint4 *) (xq + (n * nbk + ib) * 32);
+                const uint4 a = p[0], b = p[1];
+                xv[0] = a.x; xv[1] = a.y; xv[2] = a.z; xv[3] = a.w;
+                xv[4] = b.x; xv[5] = b.y; xv[6] = b.z; xv[7] = b.w;
+                dx = xd[n * nbk + ib];
+            }
+#pragma unroll
+            for (int t = 0; t < 8; ++t) Xs[xkb][t][xc] = xv[t];
+            dXs[xkb][xc] = dx;
+        }
+        __syncthreads();
+
+#pragma unroll
+        for (int kb = 0; kb < KC; ++kb) {
+            int wv[8], xv[8];
+            float dw[8], dx[8];
+            *(int4 *) &wv[0] = *(const int4 *) &Ws[kb][j][gm * 8];
+            *(int4 *) &wv[4] = *(const int4 *) &Ws[kb][j][gm * 8 + 4];
+            *(int4 *) &xv[0] = *(const int4 *) &Xs[kb][j][gn * 8];
+            *(int4 *) &xv[4] = *(const int4 *) &Xs[kb][j][gn * 8 + 4];
+            *(float4 *) &dw[0] = *(const float4 *) &dWs[kb][gm * 8];
+            *(float4 *) &dw[4] = *(const float4 *) &dWs[kb][gm * 8 + 4];
+            *(float4 *) &dx[0] = *(const float4 *) &dXs[kb][gn * 8];
+            *(float4 *) &dx[4] = *(const float4 *) &dXs[kb][gn * 8 + 4];
+#pragma unroll
+            for (int a = 0; a < 8; ++a)
+#pragma unroll
+                for (int b = 0; b < 8; ++b) {
+                    const float q = __fadd_rn(__int_as_float(__dp4a(wv[a], xv[b], MAGIC_I)), -MAGIC_F);
+                    acc[a][b] = __fmaf_rn(__fmul_rn(dw[a], dx[b]), q, acc[a][b]);
+                }
+        }
+        __syncthreads();
+    }
+
+    // hsum_float_8: (l0+l4, l1+l5, l2+l6, l3+l7) -> (+2) -> (+1)
+#pragma unroll
+    for (int a = 0; a < 8; ++a)
+#pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            float v = acc[a][b];
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+            acc[a][b] = v;
+        }
+#pragma unroll
+    for (int a = 0; a < 8; ++a) {
+        if (a == j) {
+            const int64_t m = m0 + gm * 8 + a;
+            if (m < M) {
+#pragma unroll
+                for (int b = 0; b < 8; ++b) {
+                    const int64_t n = n0 + gn * 8 + b;
+                    if (n < N) dst[n * ldd + m] = acc[a][b];
+                }
+            }
+        }
+    }
+}
+
+extern "C" int b200_mul_mat_q(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                              const int8_t * xq, const float * xd, int64_t N,
+                              float * dst, int64_t dst_stride, void * stream) {
+    if (K % 32 != 0 || M <= 0 || N <= 0) return B200_ERR_ARG;
+    if (((uintptr_t) xq & 15) != 0 || ((uintptr_t) w_planes & 15) != 0) return B200_ERR_ARG;
+    const int64_t nbk = K / 32;
+    if (M * nbk > nb_total) return B200_ERR_ARG;
+    dim3 grid((unsigned) ((M + 63) / 64), (unsigned) ((N + 31) / 32));
+    const QPlanes w = q_planes(wtype, w_planes, nb_total);
+    if (wtype == B200_TYPE_Q5_0)
+        k_mul_mat_q<B200_TYPE_Q5_0><<<grid, 256, 0, as_stream(stream)>>>(w, M, nbk, xq, xd, N, dst, dst_stride);
+    else if (wtype == B200_TYPE_Q8_0)
+        k_mul_mat_q<B200_TYPE_Q8_0><<<grid, 256, 0, as_stream(stream)>>>(w, M, nbk, xq, xd, N, dst, dst_stride);
+    else
+        return B200_ERR_ARG;
+    B200_RETURN_LAST();
+}
+
+// ------------------------------------------------------------------------------------------------
+// GEMV for 1..8 columns: a warp streams one weight row (coalesced plane loads), forms the exact
+// integer lane sums for 32 blocks in parallel, then eight threads per column replay the FMA chain in
+// block order.  Activations are quantised by the CTA itself.
+// ------------------------------------------------------------------------------------------------
+template <int TYPE, int N>
+__global__ void __launch_bounds__(128)
+k_mul_mat_vec_q(QPlanes w, int64_t M, int64_t nbk, const float * __restrict__ x, int64_t x_stride,
+                float * __restrict__ dst, int64_t ldd, int rows_per_warp) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int PSTR = 32 * 8 + 8;                 // padded per-column stride of P
+    const int K = (int) nbk * 32;
+    int *   Xq = (int *) smem_raw;                                   // [N][K/4]
+    float * Xd = (float *) (Xq + (size_t) N * (K / 4));              // [N][nbk]
+    unsigned char * wbase = (unsigned char *) (Xd + (size_t) N * nbk);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int WARP_BYTES = (32 * 12 + 32 + N * PSTR + N * 32) * 4;
+    int *   sW  = (int *) (wbase + (size_t) warp * WARP_BYTES);      // [32][12] (8 used)
+    float * sDw = (float *) (sW + 32 * 12);                          // [32]
+    float * P   = sDw + 32;                                          // [N][PSTR]
+    float * D   = P + N * PSTR;                                      // [N][32]
+
+    // quantise the activation columns (whole CTA)
+    for (int b = warp; b < N * (int) nbk; b += 4) {
+        const int n = b / (int) nbk, ib = b - n * (int) nbk;
+        const float v = *(const float *) ((const char *) x + (size_t) n * x_stride + (size_t) (ib * 32 + lane) * 4);
+        int8_t q; float dd;
+        quantize_block_q8_0(v, lane, q, dd);
+        ((int8_t *) Xq)[(size_t) n * K + ib * 32 + lane] = q;
+        if (lane == 0) Xd[n * nbk + ib] = dd;
+    }
+    __syncthreads();
+
+    const int j = lane & 7, bsub = lane >> 3, cn = lane >> 3;
+    const int64_t row0 = ((int64_t) blockIdx.x * 4 + warp) * rows_per_warp;
+
+    for (int r = 0; r < rows_per_warp; ++r) {
+        const int64_t m = row0 + r;
+        if (m >= M) break;
+        float acc0 = 0.0f, acc1 = 0.0f;
+        for (int c0 = 0; c0 < (int) nbk; c0 += 32) {
+            {   // each lane fetches one block of the row
+                const int ib = c0 + lane;
+                int wv[8];
+                float dw = 0.0f;
+#pragma unroll
+                for (int t = 0; t < 8; ++t) wv[t] = 0;
+                if (ib < (int) nbk) {
+                    const int64_t blk = m * nbk + ib;
+                    if (TYPE == B200_TYPE_Q5_0) {
+                        const uint4    q  = __ldg(((const uint4 *) w.qs) + blk);
+                        const uint32_t qh = __ldg(w.qh + blk);
+                        const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) wv[t] = q5_lane_word(qw[t & 3], qh, t);
+                    } else {
+                        const uint4 a = __ldg(((const uint4 *) w.qs) + blk * 2), b = __ldg(((const uint4 *) w.qs) + blk * 2 + 1);
+                        wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w;
+                        wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
+                    }
+                    dw = __half2float(w.d[blk]);
+                }
+                *(int4 *) &sW[lane * 12]     = make_int4(wv[0], wv[1], wv[2], wv[3]);
+                *(int4 *) &sW[lane * 12 + 4] = make_int4(wv[4], wv[5], wv[6], wv[7]);
+                sDw[lane] = dw;
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int ibl = i * 4 + bsub;
+                const int ib  = c0 + ibl;
+                if (ib < (int) nbk) {
+                    const int wv = sW[ibl * 12 + j];
+#pragma unroll
+                    for (int n = 0; n < N; ++n) {
+                        const int xv = Xq[(size_t) n * (K / 4) + ib * 8 + j];
+                        P[n * PSTR + ibl * 8 + j] = __fadd_rn(__int_as_float(__dp4a(wv, xv, MAGIC_I)), -MAGIC_F);
+                    }
+                    if (j == 0) {
+                        const float dw = sDw[ibl];
+#pragma unroll
+                        for (int n = 0; n < N; ++n) D[n * 32 + ibl] = __fmul_rn(dw, Xd[n * nbk + ib]);
+                    }
+                }
+            }
+            __syncwarp();
+            const int nblk = min(32, (int) nbk - c0);
+            if (cn < N) {
+                for (int ibl = 0; ibl < nblk; ++ibl) acc0 = __fmaf_rn(D[cn * 32 + ibl], P[cn * PSTR + ibl * 8 + j], acc0);
+            }
+            if (N > 4 && cn + 4 < N) {
+                for (int ibl = 0; ibl < nblk; ++ibl) acc1 = __fmaf_rn(D[(cn + 4) * 32 + ibl], P[(cn + 4) * PSTR + ibl * 8 + j], acc1);
+            }
+            __syncwarp();
+        }
+#pragma unroll
+        for (int o = 4; o > 0; o >>= 1) {
+            acc0 = __fadd_rn(acc0, __shfl_xor_sync(0xffffffffu, acc0, o));
+            acc1 = __fadd_rn(acc1, __shfl_xor_sync(0xffffffffu, acc1, o));
+        }
+        if (j == 0) {
+            if (cn < N) dst[(int64_t) cn * ldd + m] = acc0;
+            if (N > 4 && cn + 4 < N) dst[(int64_t) (cn + 4) * ldd + m] = acc1;
+        }
+    }
+}
+
+template <int TYPE, int N>
+static int launch_vec(const QPlanes & w, int64_t M, int64_t nbk, const float * x, int64_t xs, float * dst, int64_t ldd, cudaStream_t st) {
+    constexpr int PSTR = 32 * 8 + 8;
+    const size_t smem = (size_t) N * nbk * 32 + (size_t) N * nbk * 4 + 4 * (size_t) ((32 * 12 + 32 + N * PSTR + N * 32) * 4);
+    static bool attr_done = false;   // per instantiation; benign race (idempotent call)
+    if (!attr_done) {
+        cudaFuncSetAttribute(k_mul_mat_vec_q<TYPE, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        attr_done = true;
+    }
+    if (smem > 200 * 1024) return B200_ERR_ARG;
+    // rows per warp: keep at least ~4 CTAs per SM worth of blocks when M allows it
+    int rpw = 1;
+    while (rpw < 8 && (M + 4 * (rpw * 2) - 1) / (4 * (rpw * 2)) >= 148 * 4) rpw *= 2;
+    const int64_t rows_per_cta = 4 * rpw;
+    k_mul_mat_vec_q<TYPE, N><<<(unsigned) ((M + rows_per_cta - 1) / rows_per_cta), 128, smem, st>>>(w, M, nbk, x, xs, dst, ldd, rpw);
+    B200_RETURN_LAST();
+}
+
+template <int TYPE>
+static int launch_vec_n(int N, const QPlanes & w, int64_t M, int64_t nbk, const float * x, int64_t xs, float * dst, int64_t ldd, cudaStream_t st) {
+    switch (N) {
+        case 1: return launch_vec<TYPE, 1>(w, M, nbk, x, xs, dst, ldd, st);
+        case 2: return launch_vec<TYPE, 2>(w, M, nbk, x, xs, dst, ldd, st);
+        case 3: return launch_vec<TYPE, 3>(w, M, nbk, x, xs, dst, ldd, st);
+        case 4: return launch_vec<TYPE, 4>(w, M, nbk, x, xs, dst, ldd, st);
+        case 5: return launch_vec<TYPE, 5>(w, M, nbk, x, xs, dst, ldd, st);
+        case 6: return launch_vec<TYPE, 6>(w, M, nbk, x, xs, dst, ldd, st);
+        case 7: return launch_vec<TYPE, 7>(w, M, nbk, x, xs, dst, ldd, st);
+        case 8: return launch_vec<TYPE, 8>(w, M, nbk, x, xs, dst, ldd, st);
+    }
+    return B200_ERR_ARG;
+}
+
+extern "C" int b200_mul_mat_vec_q(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                                  const float * x, int64_t x_stride_bytes, int64_t N,
+                                  float * dst, int64_t dst_stride, void * stream) {
+    if (K % 32 != 0 || M <= 0 || N < 1 || N > 8) return B200_ERR_ARG;
+    if (((uintptr_t) w_planes & 15) != 0) return B200_ERR_ARG;
+    const int64_t nbk = K / 32;
+    if (M * nbk > nb_total) return B200_ERR_ARG;
+    const QPlanes w = q_planes(wtype, w_planes, nb_total);
+    if (wtype == B200_TYPE_Q5_0) return launch_vec_n<B200_TYPE_Q5_0>((int) N, w, M, nbk, x, x_stride_bytes, dst, dst_stride, as_stream(stream));
+    if (wtype == B200_TYPE_Q8_0) return launch_vec_n<B200_TYPE_Q8_0>((int) N, w, M, nbk, x, x_stride_bytes, dst, dst_stride, as_stream(stream));
+    return B200_ERR_ARG;
+}
