@@ -1,0 +1,303 @@
+#!/usr/bin/env python
+"""Throughput benchmark of the whisper.cpp hot path on the B200 ggml backend plugin.
+
+Workload (BASELINE.json configs[3]): Whisper large-v3, Q5_0 weights (random init, quantised by the rules of
+the reference tool), a batch of 64 seeded 30 s clips, each: log-mel -> encoder -> greedy decode of 224 tokens
+after the forced prefix [SOT, en, transcribe, notimestamps], driven through the unmodified whisper.h API
+(whisper_set_mel / whisper_encode / whisper_decode).  The batch is split evenly over the ranks (one rank per
+GPU, strong scaling: 64 clips in total at every N), no collective on the data path.
+
+One "step" = one pass over the rank's share of the batch.
+  value : audio-seconds / second with the log-mel inputs prepared before the timed region (they still enter
+          through whisper_set_mel, the only input door of the plugin boundary);
+  e2e   : the same from host PCM buffers: PCM -> device log-mel -> host mel -> whisper_set_mel -> encode ->
+          decode -> token ids on the host, everything inside the timed region.
+
+`--impl reference` times the reference's own CPU backend (oracle/_ref, all host cores) on a bounded sample of
+the same workload (one clip per step).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+from conftest import load_pkg  # noqa: E402  (path-based import of the dotted package directory)
+
+N_NEW = 224
+CLIP_SECONDS = 30.0
+TOTAL_CLIPS = 64
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """nvidia-smi clocks / throttle reasons during the timed region."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.stop_flag, self.rows = index, threading.Event(), []
+
+    def run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            self.stop_flag.wait(0.25)
+
+    def summary(self):
+        sm = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({names[i] for r in self.rows for i in range(4) if len(r) > 2 + i and r[2 + i].lower().startswith("active")})
+        return {"sm_mhz": int(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": reasons,
+                "samples": len(sm)}
+
+
+def model_file(pkg, arch, wtype, rank, barrier):
+    d = os.environ.get("B200_MODEL_DIR", "/tmp/b200_models")
+    os.makedirs(d, exist_ok=True)
+    path = os.path.join(d, f"{arch}-{wtype}.bin")
+    if rank == 0 and not os.path.exists(path):
+        tmp = path + ".tmp"
+        pkg.synth.write_model(tmp, arch, wtype, seed=0)
+        os.replace(tmp, path)
+    barrier()
+    return path
+
+
+def make_pcm(pkg, n, first_seed):
+    return np.stack([pkg.synth.pcm_f32(pkg.synth.make_clip(first_seed + i, CLIP_SECONDS, n_tones=None, envelopes=True))
+                     for i in range(n)])
+
+
+def timing_table(lib):
+    def proc(name, restype, argtypes):
+        p = lib.drv_backend_proc(b"B200", name.encode())
+        return C.CFUNCTYPE(restype, *argtypes)(p)
+    n = proc("b200_timing_classes", C.c_int, [])()
+    name = proc("b200_timing_name", C.c_char_p, [C.c_int])
+    get = proc("b200_timing_get", None, [C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_double), C.POINTER(C.c_double)])
+    out = {}
+    for c in range(n):
+        cnt, ms, work = C.c_int64(0), C.c_double(0), C.c_double(0)
+        get(c, C.byref(cnt), C.byref(ms), C.byref(work))
+        if cnt.value:
+            out[name(c).decode()] = {"launch_groups": cnt.value, "ms": ms.value, "work": work.value}
+    return out
+
+
+def run_reference(args, pkg):
+    """The reference's own CPU implementation (unmodified whisper.cpp + ggml CPU backend, AVX2 build), rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = len(os.sched_getaffinity(0))
+    path = model_file(pkg, args.arch, args.wtype, 0, lambda: None)
+    w = pkg.Whisper(path, use_gpu=False, flash_attn=True, threads=cores)
+    pcm = make_pcm(pkg, 1, 1000)
+    times = []
+    for s in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        w.greedy_batch(N_NEW, pcm=pcm, device_mel=False)
+        dt = time.perf_counter() - t0
+        if s >= args.warmup:
+            times.append(dt)
+    w.close()
+    total = sum(times)
+    value = CLIP_SECONDS * len(times) / total
+    sample = f"1 clip per step (log-mel + encoder + {N_NEW} greedy tokens), {cores} threads"
+    print(json.dumps({
+        "impl": "reference", "metric": "audio_seconds_per_second", "value": value, "unit": "audio-s/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * total / len(times), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "q5_0 weights x q8_0 activations (i8 dot, f32 accumulate)" if args.wtype != "f16" else "f16",
+        "data": "synthetic", "config": {"workload": f"whisper {args.arch} {args.wtype}: encode + greedy {N_NEW} tokens per 30 s clip",
+                                        "clips_per_step": 1, "l2": "weights (1.1 GB) exceed L2"},
+        "cpu_baseline": {"value": value, "unit": "audio-s/s", "cores": cores, "kind": "reference", "sample": sample},
+        "e2e": {"value": value, "unit": "audio-s/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--arch", default="large-v3")
+    ap.add_argument("--wtype", default="q5_0")
+    ap.add_argument("--clips", type=int, default=TOTAL_CLIPS, help="clips in the whole batch (all ranks)")
+    ap.add_argument("--states", type=int, default=0, help="whisper_states (host threads / streams) per GPU; 0 = auto")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    pkg = load_pkg()
+
+    if args.impl == "reference":
+        run_reference(args, pkg)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the B200 path has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    cores = len(os.sched_getaffinity(0))
+    n_states = args.states or max(1, min(16, cores // max(1, world)))
+    path = model_file(pkg, args.arch, args.wtype, rank, barrier)
+    clips_rank = args.clips // world
+    pcm = make_pcm(pkg, clips_rank, 1000 + rank * clips_rank)
+    w = pkg.Whisper(path, use_gpu=True, flash_attn=True, gpu_device=local, n_states=n_states, threads=max(1, cores // max(1, world)))
+    lib = w.lib
+
+    def stat(name):
+        return C.CFUNCTYPE(C.c_int64)(lib.drv_backend_proc(b"B200", name.encode()))()
+
+    # inputs of the `value` arm: log-mels prepared once by the device front-end (not timed)
+    f = w.filters()
+    kl = pkg.kernels_lib()
+    kl.b200_mel_create.restype = C.c_void_p
+    kl.b200_mel_create.argtypes = [C.c_int, C.c_void_p, C.c_int]
+    kl.b200_mel_compute.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    kl.b200_mel_destroy.argtypes = [C.c_void_p]
+    plan = kl.b200_mel_create(local, f.ctypes.data, f.shape[0])
+    if not plan:
+        raise SystemExit("b200_mel_create failed")
+    mels = np.empty((clips_rank, w.n_mels, 3000), np.float32)
+    tmp = np.empty((w.n_mels, 6000), np.float32)
+    for i in range(clips_rank):
+        nl, nlo = C.c_int(0), C.c_int(0)
+        e = kl.b200_mel_compute(plan, pcm[i].ctypes.data, pcm.shape[1], tmp.ctypes.data, tmp.size, C.byref(nl), C.byref(nlo))
+        if e != 0:
+            raise SystemExit(f"b200_mel_compute failed: {e}")
+        mels[i] = tmp[:, :3000]
+    kl.b200_mel_destroy(plan)
+
+    def run_steps(kind):
+        """W warm-up + K timed steps; returns (seconds of the timed steps (max over ranks), launches, h2d, d2h)."""
+        sampler = ClockSampler(local)
+        times = []
+        for s in range(args.warmup + args.steps):
+            if s == args.warmup:
+                barrier()
+                sampler.start()
+                l0, h0, d0 = kl.b200_launch_count(), stat("b200_stat_h2d"), stat("b200_stat_d2h")
+                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                ev0.record()
+                t0 = time.perf_counter()
+            if kind == "value":
+                w.greedy_batch(N_NEW, mels=mels)
+            else:
+                w.greedy_batch(N_NEW, pcm=pcm, device_mel=True)
+        barrier()
+        ev1.record()
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        dev_s = ev0.elapsed_time(ev1) / 1000.0
+        sampler.stop_flag.set()
+        sampler.join()
+        l1, h1, d1 = kl.b200_launch_count(), stat("b200_stat_h2d"), stat("b200_stat_d2h")
+        t = torch.tensor([max(dt, dev_s)], device="cuda", dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()), l1 - l0, h1 - h0, d1 - d0, sampler.summary()
+
+    sec_v, launches, _, _, clocks = run_steps("value")
+    sec_e, _, h2d, d2h, _ = run_steps("e2e")
+    audio = CLIP_SECONDS * clips_rank * world * args.steps
+    value, e2e = audio / sec_v, audio / sec_e
+    # the device mel front-end moves PCM in and the mel out, besides what crosses the plugin boundary
+    mel_h2d = pcm.shape[1] * 4 + 400 * 4
+    mel_d2h = w.n_mels * 6000 * 4
+    h2d_step = h2d / args.steps + clips_rank * mel_h2d
+    d2h_step = d2h / args.steps + clips_rank * mel_d2h
+
+    # roofline of the dominant kernel: one extra pass of a few clips with per-operator CUDA events
+    roof = None
+    tt = {}
+    if rank == 0:
+        en = C.CFUNCTYPE(None, C.c_int)(lib.drv_backend_proc(b"B200", b"b200_timing_enable"))
+        rs = C.CFUNCTYPE(None)(lib.drv_backend_proc(b"B200", b"b200_timing_reset"))
+        one = pkg.Whisper.__new__(pkg.Whisper)  # reuse the context with a single state for a serial pass
+        one.__dict__.update(w.__dict__)
+        one.states = w.states[:1]
+        rs()
+        en(1)
+        one.greedy_batch(N_NEW, mels=mels[:2])
+        en(0)
+        tt = timing_table(lib)
+        hbm, tf, which = peaks()
+        top = max(tt.items(), key=lambda kv: kv[1]["ms"])[0] if tt else None
+        if top:
+            r = tt[top]
+            per_launch_work = r["work"] / r["launch_groups"]
+            per_launch_s = r["ms"] / 1000.0 / r["launch_groups"]
+            if top in ("mul_mat_q", "mul_mat_f16", "flash_attn_ext"):
+                ach, peak, unit, bound = per_launch_work / per_launch_s / 1e12, tf, "TFLOP/s", "tensor"
+            else:
+                ach, peak, unit, bound = per_launch_work / per_launch_s / 1e9, hbm, "GB/s", "hbm"
+            roof = {"kernel": top, "bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak, "traffic": None,
+                    "peak_source": which, "launches": r["launch_groups"], "avg_us": per_launch_s * 1e6,
+                    "share_of_gpu_time": r["ms"] / sum(v["ms"] for v in tt.values())}
+
+    cpu_base = None
+    if rank == 0 and not args.no_cpu_baseline:
+        cw = pkg.Whisper(path, use_gpu=False, flash_attn=True, threads=cores)
+        t0 = time.perf_counter()
+        cw.greedy_batch(N_NEW, pcm=pcm[:1], device_mel=False)
+        dt = time.perf_counter() - t0
+        cw.close()
+        cpu_base = {"value": CLIP_SECONDS / dt, "unit": "audio-s/s", "cores": cores, "kind": "reference",
+                    "sample": f"1 clip (log-mel + encoder + {N_NEW} greedy tokens) on the reference CPU backend, {cores} threads, {dt:.1f} s"}
+    w.close()
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": "audio_seconds_per_second", "value": value, "unit": "audio-s/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1000.0 * sec_v / args.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "q5_0 weights x q8_0 activations (i8 dot, f32 accumulate)" if args.wtype != "f16" else "f16",
+            "data": "synthetic",
+            "config": {"workload": f"whisper {args.arch} {args.wtype}: encode + greedy {N_NEW} tokens per 30 s clip",
+                       "clips_total": clips_rank * world, "clips_per_gpu": clips_rank, "states_per_gpu": n_states, "flash_attn": True,
+                       "l2": "inputs larger than L2: 1.1 GB of weights are streamed per decode step per state"},
+            "e2e": {"value": e2e, "unit": "audio-s/s", "h2d_bytes_per_step": int(h2d_step), "d2h_bytes_per_step": int(d2h_step),
+                    "ms_per_step": 1000.0 * sec_e / args.steps},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu_base,
+            "kernel_classes": {k: {"launch_groups": v["launch_groups"], "ms": round(v["ms"], 3)} for k, v in tt.items()},
+        }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

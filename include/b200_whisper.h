@@ -130,6 +130,14 @@ int b200_concat(const float * a, const int64_t * nea, const int64_t * nba,
 int b200_log_mel(int device, const float * pcm_host, int64_t n_samples, const float * filters_host,
                  int n_mel, float * out_host, int64_t out_capacity, int * n_len, int * n_len_org);
 
+/* Same front-end with persistent device buffers, tables and a private stream, for repeated use
+ * (one plan per host thread).  b200_mel_compute is synchronous: on return out_host holds
+ * [n_mel][n_len] floats.  No counterpart in the reference (its mel runs on host threads). */
+void * b200_mel_create(int device, const float * filters_host, int n_mel);
+int    b200_mel_compute(void * plan, const float * pcm_host, int64_t n_samples, float * out_host, int64_t out_capacity,
+                        int * n_len, int * n_len_org);
+void   b200_mel_destroy(void * plan);
+
 /* Library info: number of kernel launches issued so far by this process (all entry points). */
 int64_t b200_launch_count(void);
 const char * b200_version(void);

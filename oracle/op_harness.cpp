@@ -29,6 +29,8 @@ int64_t oph_quantize(int type, const float * src, void * dst, int64_t nrows, int
 
 // to_float of the reference type traits (dequantize_row_*): block bytes -> f32
 int oph_dequantize(int type, const void * src, float * dst, int64_t n) {
+    static bool tables_ready = false;      // ggml_init fills the f16 -> f32 table that ggml-base's to_float uses
+    if (!tables_ready) { struct ggml_init_params ip = { 0, nullptr, false }; ggml_free(ggml_init(ip)); tables_ready = true; }
     const struct ggml_type_traits * tr = ggml_get_type_traits((enum ggml_type) type);
     if (!tr || !tr->to_float) return -1;
     tr->to_float(src, dst, n);

@@ -188,20 +188,62 @@ int drv_full(void * vctx, void * vst, const float * pcm, int n_samples, int beam
     return n;
 }
 
+// Mel filterbank stored in a legacy ggml model file (header layout: src/whisper.cpp:1508-1607).
+// whisper.h has no getter for it; an application that computes the mel itself reads it from the file.
+int drv_read_filters(const char * model_path, float * out, int cap, int * n_mel, int * n_fft) {
+    FILE * f = fopen(model_path, "rb");
+    if (!f) return -1;
+    uint32_t magic = 0;
+    int32_t hp[11];
+    int32_t nm = 0, nf = 0;
+    int rc = -2;
+    if (fread(&magic, 4, 1, f) == 1 && magic == 0x67676d6c && fread(hp, 4, 11, f) == 11 && fread(&nm, 4, 1, f) == 1 && fread(&nf, 4, 1, f) == 1) {
+        *n_mel = nm; *n_fft = nf;
+        if (nm > 0 && nf > 0 && (int64_t) nm * nf <= cap && fread(out, 4, (size_t) nm * nf, f) == (size_t) nm * nf) rc = 0;
+    }
+    fclose(f);
+    return rc;
+}
+
+// B200 mel front-end of libb200_kernels.so (include/b200_whisper.h)
+void * b200_mel_create(int device, const float * filters_host, int n_mel);
+int    b200_mel_compute(void * plan, const float * pcm_host, int64_t n_samples, float * out_host, int64_t out_capacity, int * n_len, int * n_len_org);
+void   b200_mel_destroy(void * plan);
+
+void * drv_mel_create(int device, const float * filters, int n_mel) { return b200_mel_create(device, filters, n_mel); }
+void   drv_mel_destroy(void * plan) { b200_mel_destroy(plan); }
+
 // A batch of clips on one context: n_states worker threads, each with its own whisper_state (and so
-// its own backend stream), pull clips from a shared counter.  mels = [n_clips][n_mel][n_len] f32.
+// its own backend stream), pull clips from a shared counter.  Input is either PCM
+// [n_clips][n_samples] (mel computed per clip: on the device when mel_plans != NULL, else by
+// whisper_pcm_to_mel on the host threads) or ready mels [n_clips][n_mel][n_len] when pcm == NULL.
 // tokens_out = [n_clips][n_new].  Returns 0 or the first error; *seconds = wall time of the batch.
-int drv_greedy_batch(void * vctx, void ** states, int n_states, const float * mels, int n_clips, int n_len, int n_mel,
-                     int n_new, int threads, int * tokens_out, double * seconds) {
+int drv_greedy_batch(void * vctx, void ** states, int n_states, void ** mel_plans, const float * pcm, int n_samples,
+                     const float * mels, int n_len, int n_mel, int n_clips, int n_new, int threads, int * tokens_out, double * seconds) {
     struct whisper_context * ctx = (struct whisper_context *) vctx;
     std::atomic<int> next{0}, err{0};
     const auto t0 = std::chrono::steady_clock::now();
     auto work = [&](int w) {
         struct whisper_state * st = (struct whisper_state *) states[w];
+        std::vector<float> melbuf;
         for (;;) {
             const int c = next.fetch_add(1);
             if (c >= n_clips || err.load()) break;
-            if (whisper_set_mel_with_state(ctx, st, mels + (size_t) c * n_len * n_mel, n_len, n_mel) != 0) { err = -10; break; }
+            if (pcm) {
+                const float * x = pcm + (size_t) c * n_samples;
+                if (mel_plans) {
+                    const int64_t cap = (int64_t) n_mel * ((n_samples + 480000 + 400 - 400) / 160);
+                    if ((int64_t) melbuf.size() < cap) melbuf.resize(cap);
+                    int nl = 0, nlo = 0;
+                    const int e = b200_mel_compute(mel_plans[w], x, n_samples, melbuf.data(), cap, &nl, &nlo);
+                    if (e) { err = -20 - (e & 0xff); break; }
+                    if (whisper_set_mel_with_state(ctx, st, melbuf.data(), nl, n_mel) != 0) { err = -10; break; }
+                } else {
+                    if (whisper_pcm_to_mel_with_state(ctx, st, x, n_samples, threads) != 0) { err = -11; break; }
+                }
+            } else {
+                if (whisper_set_mel_with_state(ctx, st, mels + (size_t) c * n_len * n_mel, n_len, n_mel) != 0) { err = -10; break; }
+            }
             const int e = drv_greedy(ctx, st, n_new, threads, nullptr, tokens_out + (size_t) c * n_new, nullptr, nullptr);
             if (e) { err = e; break; }
         }

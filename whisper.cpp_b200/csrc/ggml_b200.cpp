@@ -39,7 +39,31 @@ static std::atomic<int64_t> g_graphs_computed{0};
 static std::atomic<int64_t> g_h2d_bytes{0};
 static std::atomic<int64_t> g_d2h_bytes{0};
 
+// Optional per-operator timing (off by default): CUDA events recorded on the backend's own stream
+// around every launch group, summed per class after the graph finishes.  Used by the benchmark for
+// its roofline line; the extra event records and the sync make it unsuitable for throughput runs.
+enum b200_timing_class { TC_MMQ_VEC = 0, TC_MMQ_GEMM, TC_MM_F16, TC_FATTN, TC_NORM, TC_BINARY, TC_SCALE, TC_GELU, TC_CPY,
+                         TC_GET_ROWS, TC_IM2COL, TC_SOFT_MAX, TC_CONCAT, TC_COUNT };
+static const char * const g_tc_names[TC_COUNT] = { "mul_mat_vec_q", "mul_mat_q", "mul_mat_f16", "flash_attn_ext", "norm", "binary",
+                                                   "scale", "gelu", "cpy", "get_rows", "im2col", "soft_max", "concat" };
+static std::atomic<int> g_timing_on{0};
+static std::mutex       g_timing_mu;
+static double  g_tc_ms[TC_COUNT];
+static double  g_tc_work[TC_COUNT];     // algorithmic bytes (memory-bound classes) or FLOPs (mul_mat_q, mul_mat_f16, flash_attn_ext)
+static int64_t g_tc_count[TC_COUNT];
+
 extern "C" {
+void b200_timing_enable(int on) { g_timing_on = on; }
+void b200_timing_reset(void) {
+    std::lock_guard<std::mutex> lk(g_timing_mu);
+    for (int i = 0; i < TC_COUNT; ++i) { g_tc_ms[i] = 0; g_tc_work[i] = 0; g_tc_count[i] = 0; }
+}
+int b200_timing_classes(void) { return TC_COUNT; }
+const char * b200_timing_name(int c) { return c >= 0 && c < TC_COUNT ? g_tc_names[c] : ""; }
+void b200_timing_get(int c, int64_t * count, double * ms, double * work) {
+    std::lock_guard<std::mutex> lk(g_timing_mu);
+    *count = g_tc_count[c]; *ms = g_tc_ms[c]; *work = g_tc_work[c];
+}
 int64_t b200_stat_nodes(void)   { return g_nodes_computed.load(); }
 int64_t b200_stat_graphs(void)  { return g_graphs_computed.load(); }
 int64_t b200_stat_h2d(void)     { return g_h2d_bytes.load(); }
@@ -218,6 +242,7 @@ struct b200_backend_ctx {
     void *       scratch      = nullptr;   // Q8_0-quantised activations of the current GEMM
     size_t       scratch_size = 0;
     std::string  name;
+    std::vector<cudaEvent_t> events;       // timing mode only
 };
 
 static const char * b200_backend_get_name(ggml_backend_t backend) {
@@ -229,6 +254,7 @@ static void b200_backend_free(ggml_backend_t backend) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    for (cudaEvent_t e : ctx->events) cudaEventDestroy(e);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
     delete backend;
@@ -343,11 +369,49 @@ static int compute_node(b200_backend_ctx * ctx, struct ggml_tensor * node) {
     }
 }
 
+// timing class of a node and its algorithmic work (bytes for memory-bound classes, FLOPs for contractions)
+static int node_class(const struct ggml_tensor * node, double * work) {
+    const struct ggml_tensor * s0 = node->src[0];
+    const struct ggml_tensor * s1 = node->src[1];
+    const double out_bytes = (double) ggml_nbytes(node);
+    switch (node->op) {
+        case GGML_OP_MUL_MAT:
+            if (is_quant(s0->type)) {
+                if (s1->ne[1] <= 8) { *work = (double) ggml_nbytes(s0) + (double) ggml_nbytes(s1) + out_bytes; return TC_MMQ_VEC; }
+                *work = 2.0 * (double) s0->ne[0] * (double) s0->ne[1] * (double) s1->ne[1];
+                return TC_MMQ_GEMM;
+            }
+            *work = 2.0 * (double) s0->ne[0] * (double) s0->ne[1] * (double) s1->ne[1] * (double) s1->ne[2] * (double) s1->ne[3];
+            return TC_MM_F16;
+        case GGML_OP_FLASH_ATTN_EXT:
+            *work = 4.0 * 64.0 * (double) s0->ne[1] * (double) s0->ne[2] * (double) node->src[1]->ne[1];
+            return TC_FATTN;
+        case GGML_OP_NORM:     *work = 2.0 * out_bytes; return TC_NORM;
+        case GGML_OP_ADD: case GGML_OP_MUL: *work = 2.0 * out_bytes + (double) ggml_nbytes(s1); return TC_BINARY;
+        case GGML_OP_SCALE:    *work = 2.0 * out_bytes; return TC_SCALE;
+        case GGML_OP_UNARY:    *work = 2.0 * out_bytes; return TC_GELU;
+        case GGML_OP_CPY: case GGML_OP_DUP: case GGML_OP_CONT: *work = (double) ggml_nbytes(s0) + out_bytes; return TC_CPY;
+        case GGML_OP_GET_ROWS: *work = 2.0 * out_bytes; return TC_GET_ROWS;
+        case GGML_OP_IM2COL:   *work = (double) ggml_nbytes(s1) + out_bytes; return TC_IM2COL;
+        case GGML_OP_SOFT_MAX: *work = 2.0 * out_bytes; return TC_SOFT_MAX;
+        case GGML_OP_CONCAT:   *work = 2.0 * out_bytes; return TC_CONCAT;
+        default: *work = 0; return TC_CONCAT;
+    }
+}
+
 static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struct ggml_cgraph * cgraph) {
     b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
     if (cudaSetDevice(ctx->device) != cudaSuccess) return GGML_STATUS_FAILED;
     const int n_nodes = ggml_graph_n_nodes(cgraph);
     int64_t done = 0;
+    const bool timing = g_timing_on.load() != 0;
+    std::vector<int>    t_class;
+    std::vector<double> t_work;
+    size_t n_ev = 0;
+    auto next_event = [&]() -> cudaEvent_t {
+        if (n_ev == ctx->events.size()) { cudaEvent_t e; cudaEventCreate(&e); ctx->events.push_back(e); }
+        return ctx->events[n_ev++];
+    };
     for (int i = 0; i < n_nodes; ++i) {
         struct ggml_tensor * node = ggml_graph_node(cgraph, i);
         if (is_view_op(node->op) || ggml_is_empty(node)) continue;
@@ -355,7 +419,14 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
             fprintf(stderr, "ggml-b200: unsupported node %s (%s) reached graph_compute\n", node->name, ggml_op_name(node->op));
             return GGML_STATUS_FAILED;
         }
+        if (timing) {
+            double work = 0;
+            t_class.push_back(node_class(node, &work));
+            t_work.push_back(work);
+            cudaEventRecord(next_event(), ctx->stream);
+        }
         const int e = compute_node(ctx, node);
+        if (timing) cudaEventRecord(next_event(), ctx->stream);
         if (e != 0) {
             fprintf(stderr, "ggml-b200: node %d %s (%s) failed with code %d (%s)\n", i, node->name, ggml_op_name(node->op), e,
                     e < 10000 ? cudaGetErrorString((cudaError_t) e) : "argument error");
@@ -365,6 +436,17 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
     }
     g_nodes_computed += done;
     g_graphs_computed += 1;
+    if (timing && !t_class.empty()) {
+        if (!cuda_ok(cudaStreamSynchronize(ctx->stream), "timing sync")) return GGML_STATUS_FAILED;
+        std::lock_guard<std::mutex> lk(g_timing_mu);
+        for (size_t k = 0; k < t_class.size(); ++k) {
+            float ms = 0;
+            cudaEventElapsedTime(&ms, ctx->events[2 * k], ctx->events[2 * k + 1]);
+            g_tc_ms[t_class[k]] += ms;
+            g_tc_work[t_class[k]] += t_work[k];
+            g_tc_count[t_class[k]] += 1;
+        }
+    }
     return GGML_STATUS_SUCCESS;
 }
 
@@ -546,6 +628,11 @@ static void * b200_reg_get_proc_address(ggml_backend_reg_t, const char * name) {
     if (strcmp(name, "b200_stat_h2d") == 0)    return (void *) b200_stat_h2d;
     if (strcmp(name, "b200_stat_d2h") == 0)    return (void *) b200_stat_d2h;
     if (strcmp(name, "b200_launch_count") == 0) return (void *) b200_launch_count;
+    if (strcmp(name, "b200_timing_enable") == 0)  return (void *) b200_timing_enable;
+    if (strcmp(name, "b200_timing_reset") == 0)   return (void *) b200_timing_reset;
+    if (strcmp(name, "b200_timing_classes") == 0) return (void *) b200_timing_classes;
+    if (strcmp(name, "b200_timing_name") == 0)    return (void *) b200_timing_name;
+    if (strcmp(name, "b200_timing_get") == 0)     return (void *) b200_timing_get;
     return nullptr;
 }
 

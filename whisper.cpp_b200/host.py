@@ -64,7 +64,12 @@ def _driver(probe: bool) -> C.CDLL:
         lib.drv_probe_embd_enc.argtypes = [vp, C.c_void_p, C.c_int64]
         lib.drv_greedy.argtypes = [vp, vp, ci, ci, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         lib.drv_full.argtypes = [vp, vp, C.c_void_p, ci, ci, ci, ci, C.c_void_p, ci]
-        lib.drv_greedy_batch.argtypes = [vp, C.POINTER(vp), ci, C.c_void_p, ci, ci, ci, ci, ci, C.c_void_p, C.POINTER(C.c_double)]
+        lib.drv_greedy_batch.argtypes = [vp, C.POINTER(vp), ci, C.c_void_p, C.c_void_p, ci, C.c_void_p, ci, ci, ci, ci, ci,
+                                         C.c_void_p, C.POINTER(C.c_double)]
+        lib.drv_read_filters.argtypes = [C.c_char_p, C.c_void_p, ci, C.POINTER(ci), C.POINTER(ci)]
+        lib.drv_mel_create.restype = vp
+        lib.drv_mel_create.argtypes = [ci, C.c_void_p, ci]
+        lib.drv_mel_destroy.argtypes = [vp]
         lib.drv_system_info.restype = C.c_char_p
         _drivers[probe] = lib
     return _drivers[probe]
@@ -96,6 +101,10 @@ class Whisper:
                  probe: bool = False, n_states: int = 1, threads: int | None = None, quiet: bool = True):
         self.lib = _driver(probe)
         self.probe = probe
+        self.model_path = model_path
+        self.gpu_device = gpu_device
+        self.use_gpu = use_gpu
+        self.mel_plans = []
         self.lib.drv_set_quiet(1 if quiet else 0)
         if use_gpu and load_plugin(probe) <= 0:
             raise RuntimeError("B200 plugin exposes no device: refusing to run (there is no CPU fallback in the product path)")
@@ -112,6 +121,9 @@ class Whisper:
         self.n_audio_ctx = self.lib.drv_n_audio_ctx(self.ctx)
 
     def close(self):
+        for p in self.mel_plans:
+            self.lib.drv_mel_destroy(p)
+        self.mel_plans = []
         for s in self.states:
             self.lib.drv_state_free(s)
         self.states = []
@@ -172,15 +184,43 @@ class Whisper:
             raise RuntimeError(f"drv_greedy failed: {e}")
         return out, margins, logits
 
-    def greedy_batch(self, mels: np.ndarray, n_new: int):
-        """mels [n_clips, n_mel, n_len] -> (tokens [n_clips, n_new], seconds); clips are spread over all states."""
-        mels = np.ascontiguousarray(mels, np.float32)
-        n_clips, n_mel, n_len = mels.shape
-        toks = np.zeros((n_clips, n_new), np.int32)
-        secs = C.c_double(0)
+    def filters(self) -> np.ndarray:
+        """mel filterbank [n_mel, 201] as stored in the model file."""
+        buf = np.empty(256 * 201, np.float32)
+        nm, nf = C.c_int(0), C.c_int(0)
+        if self.lib.drv_read_filters(self.model_path.encode(), buf.ctypes.data, buf.size, C.byref(nm), C.byref(nf)) != 0:
+            raise RuntimeError("cannot read mel filters from the model file")
+        return buf[: nm.value * nf.value].reshape(nm.value, nf.value).copy()
+
+    def _ensure_mel_plans(self):
+        if not self.mel_plans:
+            f = self.filters()
+            self.mel_plans = [self.lib.drv_mel_create(self.gpu_device, f.ctypes.data, f.shape[0]) for _ in self.states]
+            if not all(self.mel_plans):
+                raise RuntimeError("b200_mel_create failed (no CUDA device?)")
+
+    def greedy_batch(self, n_new: int, mels: np.ndarray | None = None, pcm: np.ndarray | None = None, device_mel: bool = True):
+        """Encode + greedy-decode a batch of clips spread over all states.
+        mels [n_clips, n_mel, n_len] or pcm [n_clips, n_samples] (mel on the B200 when device_mel, else
+        whisper_pcm_to_mel on host threads).  Returns (tokens [n_clips, n_new], seconds)."""
         arr = (C.c_void_p * len(self.states))(*self.states)
-        e = self.lib.drv_greedy_batch(self.ctx, arr, len(self.states), mels.ctypes.data, n_clips, n_len, n_mel, n_new,
-                                      self.threads, toks.ctypes.data, C.byref(secs))
+        secs = C.c_double(0)
+        if pcm is not None:
+            pcm = np.ascontiguousarray(pcm, np.float32)
+            n_clips, n_samples = pcm.shape
+            toks = np.zeros((n_clips, n_new), np.int32)
+            plans = None
+            if device_mel:
+                self._ensure_mel_plans()
+                plans = (C.c_void_p * len(self.mel_plans))(*self.mel_plans)
+            e = self.lib.drv_greedy_batch(self.ctx, arr, len(self.states), plans, pcm.ctypes.data, n_samples, None, 0, self.n_mels,
+                                          n_clips, n_new, self.threads, toks.ctypes.data, C.byref(secs))
+        else:
+            mels = np.ascontiguousarray(mels, np.float32)
+            n_clips, n_mel, n_len = mels.shape
+            toks = np.zeros((n_clips, n_new), np.int32)
+            e = self.lib.drv_greedy_batch(self.ctx, arr, len(self.states), None, None, 0, mels.ctypes.data, n_len, n_mel,
+                                          n_clips, n_new, self.threads, toks.ctypes.data, C.byref(secs))
         if e != 0:
             raise RuntimeError(f"drv_greedy_batch failed: {e}")
         return toks, secs.value
