@@ -1,0 +1,214 @@
+"""Parity of the CUDA kernels called through the C ABI (include/b200_whisper.h) against the CPU restatement
+(oracle/liboracle.so) on seeded inputs.  torch only provides device memory and the stream.  Bit-exact unless noted."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import oracle_lib as O
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+i64, vp = C.c_int64, C.c_void_p
+
+
+def rnd(seed, *shape, scale=1.0):
+    return (np.random.default_rng(seed).standard_normal(shape) * scale).astype(np.float32)
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def ptr(t):
+    return vp(t.data_ptr())
+
+
+def arr4(v):
+    return (i64 * 4)(*v)
+
+
+def sync_ok(rc):
+    assert rc == 0, f"kernel entry point returned {rc}"
+    torch.cuda.synchronize()
+
+
+def bits_equal(a, b):
+    a, b = np.ascontiguousarray(a), np.ascontiguousarray(b)
+    return a.shape == b.shape and np.array_equal(a.view(np.uint8), b.view(np.uint8))
+
+
+@pytest.fixture(scope="module")
+def K(pkg):
+    lib = pkg.kernels_lib()
+    assert torch.cuda.is_available(), "these tests need the B200; the kernel library has no CPU path"
+    return lib
+
+
+def planes_of(lib, pkg, wtype, w):
+    q = pkg.synth.quantize_q5_0 if wtype == 6 else pkg.synth.quantize_q8_0
+    blocks = q(w)
+    nb = blocks.shape[0] * blocks.shape[1]
+    planes = np.zeros(blocks.size, np.uint8)
+    assert lib.b200_blocks_to_planes(wtype, blocks.ctypes.data_as(vp), planes.ctypes.data_as(vp), i64(nb), i64(0), i64(nb)) == 0
+    return blocks, planes, nb
+
+
+@pytest.mark.parametrize("wtype", [6, 8])
+def test_dequantize(K, pkg, wtype):
+    blocks, planes, nb = planes_of(K, pkg, wtype, rnd(1, 16, 256, scale=0.02))
+    d_planes, out = dev(planes), torch.empty(nb * 32, device="cuda")
+    sync_ok(K.b200_dequantize(wtype, ptr(d_planes), i64(nb), i64(0), i64(nb), ptr(out), None))
+    assert bits_equal(out.cpu().numpy(), O.dequantize(wtype, blocks))
+    sync_ok(K.b200_dequantize(wtype, ptr(d_planes), i64(nb), i64(7), i64(3), ptr(out), None))   # ragged range
+    assert bits_equal(out.cpu().numpy()[:96], O.dequantize(wtype, blocks).reshape(-1, 32)[7:10].reshape(-1))
+
+
+def test_quantize_q8_0(K):
+    x = rnd(2, 9, 384) * np.linspace(1e-4, 50, 9, dtype=np.float32)[:, None]
+    x[3] = 0
+    dx, qs, d = dev(x), torch.empty((9, 384), dtype=torch.int8, device="cuda"), torch.empty((9, 12), device="cuda")
+    sync_ok(K.b200_quantize_q8_0(ptr(dx), i64(9), i64(384), i64(384 * 4), ptr(qs), ptr(d), None))
+    rq, rd = O.quantize_row_q8_0(x)
+    assert np.array_equal(qs.cpu().numpy().reshape(-1), rq) and bits_equal(d.cpu().numpy().reshape(-1), rd)
+
+
+@pytest.mark.parametrize("wtype", [6, 8])
+@pytest.mark.parametrize("Kd,M,N", [(384, 384, 1), (1280, 200, 8), (512, 130, 3), (384, 96, 40), (1280, 64, 33), (2048, 70, 9)])
+def test_mul_mat_q_both_paths(K, pkg, wtype, Kd, M, N):
+    w, x = rnd(3, M, Kd, scale=0.02), rnd(4, N, Kd)
+    blocks, planes, nb = planes_of(K, pkg, wtype, w)
+    ref = O.mul_mat_q(wtype, blocks, M, Kd, x)
+    d_planes, dx, dst = dev(planes), dev(x), torch.zeros((N, M), device="cuda")
+    if N <= 8:
+        sync_ok(K.b200_mul_mat_vec_q(wtype, ptr(d_planes), i64(nb), i64(M), i64(Kd), ptr(dx), i64(Kd * 4), i64(N), ptr(dst), i64(M), None))
+        assert bits_equal(dst.cpu().numpy(), ref), "GEMV path"
+    qs, d = torch.empty((N, Kd), dtype=torch.int8, device="cuda"), torch.empty((N, Kd // 32), device="cuda")
+    sync_ok(K.b200_quantize_q8_0(ptr(dx), i64(N), i64(Kd), i64(Kd * 4), ptr(qs), ptr(d), None))
+    dst.zero_()
+    sync_ok(K.b200_mul_mat_q(wtype, ptr(d_planes), i64(nb), i64(M), i64(Kd), ptr(qs), ptr(d), i64(N), ptr(dst), i64(M), None))
+    assert bits_equal(dst.cpu().numpy(), ref), "GEMM path"
+
+
+def test_mul_mat_q_rejects_bad_arguments(K):
+    assert K.b200_mul_mat_vec_q(6, None, i64(0), i64(4), i64(48), None, i64(0), i64(1), None, i64(4), None) != 0   # K % 32
+    assert K.b200_mul_mat_vec_q(6, None, i64(0), i64(4), i64(64), None, i64(0), i64(9), None, i64(4), None) != 0   # N > 8
+    assert K.b200_mul_mat_q(7, None, i64(0), i64(4), i64(64), None, None, i64(9), None, i64(4), None) != 0          # unknown type
+
+
+@pytest.mark.parametrize("Kd,M,N", [(384, 50, 3), (240, 33, 20), (64, 8, 1)])
+def test_mul_mat_f16(K, Kd, M, N):
+    w, x = rnd(5, M, Kd, scale=0.02).astype(np.float16), rnd(6, N, Kd)
+    dw, dx, dst = dev(w), dev(x), torch.zeros((N, M), device="cuda")
+    sync_ok(K.b200_mul_mat_f16(ptr(dw), arr4([Kd, M, 1, 1]), arr4([2, Kd * 2, Kd * M * 2, Kd * M * 2]), ptr(dx), 0, arr4([Kd, N, 1, 1]),
+                               arr4([4, Kd * 4, Kd * N * 4, Kd * N * 4]), ptr(dst), arr4([4, M * 4, M * N * 4, M * N * 4]), None))
+    assert bits_equal(dst.cpu().numpy(), O.mul_mat_f16(w, x))
+
+
+@pytest.mark.parametrize("n_q,n_kv,H,masked", [(1, 1536, 4, False), (3, 100, 2, True), (7, 33, 3, True), (2, 1, 1, False)])
+def test_flash_attn_ext(K, n_q, n_kv, H, masked):
+    d = 64 * H
+    q, k, v = rnd(7, n_q, H, 64, scale=0.5), rnd(8, n_kv, H, 64, scale=0.5).astype(np.float16), rnd(9, n_kv, H, 64).astype(np.float16)
+    mask = None
+    if masked:
+        mask = np.zeros((n_q, n_kv), np.float16)
+        mask[np.random.default_rng(10).random((n_q, n_kv)) < 0.4] = -np.inf
+        mask[:, 0] = 0
+    dq, dk, dv, dst = dev(q), dev(k), dev(v), torch.zeros((n_q, H, 64), device="cuda")
+    dm = dev(mask) if mask is not None else None
+    sync_ok(K.b200_flash_attn_ext(ptr(dq), i64(d * 4), i64(64 * 4), ptr(dk), i64(d * 2), i64(128), ptr(dv), i64(d * 2), i64(128),
+                                  ptr(dm) if dm is not None else None, i64(n_kv * 2), ptr(dst), i64(n_q), i64(n_kv), i64(H), C.c_float(0.125), None))
+    assert bits_equal(dst.cpu().numpy(), O.flash_attn(q, k, v, mask, 0.125))
+
+
+def test_norm_and_gelu(K):
+    x = rnd(11, 37, 1280) * 2 + 0.3
+    dx, dy = dev(x), torch.empty((37, 1280), device="cuda")
+    nb = arr4([4, 1280 * 4, 1280 * 37 * 4, 1280 * 37 * 4])
+    sync_ok(K.b200_norm(ptr(dx), ptr(dy), i64(1280), i64(37), i64(1), i64(1), nb, nb, C.c_float(1e-5), None))
+    assert bits_equal(dy.cpu().numpy(), O.norm(x))
+    g = np.concatenate([rnd(12, 5000) * 4, np.array([-10, 10, -10.5, 11, 0], np.float32)])
+    dg, dgy = dev(g), torch.empty(g.size, device="cuda")
+    sync_ok(K.b200_gelu(ptr(dg), ptr(dgy), i64(g.size), None))
+    assert bits_equal(dgy.cpu().numpy(), O.gelu(g))
+
+
+@pytest.mark.parametrize("mask_kind", [None, np.float32, np.float16])
+def test_soft_max(K, mask_kind):
+    x = rnd(13, 3, 5, 77, scale=2.0)
+    mask = None
+    if mask_kind is not None:
+        mask = np.zeros((5, 77), np.float32)
+        mask[np.random.default_rng(14).random((5, 77)) < 0.3] = -np.inf
+        mask[:, 0] = 0
+        mask = mask.astype(mask_kind)
+    dx, dy = dev(x), torch.empty(x.shape, device="cuda")
+    dm = dev(mask) if mask is not None else None
+    mt = 0 if mask_kind in (None, np.float32) else 1
+    sync_ok(K.b200_soft_max(ptr(dx), ptr(dm) if dm is not None else None, mt, i64(77 * (4 if mt == 0 else 2)), i64(5), ptr(dy), i64(77), i64(15), i64(5),
+                            C.c_float(0.125), None))
+    assert bits_equal(dy.cpu().numpy(), O.soft_max(x, mask, 0.125, 5))
+
+
+@pytest.mark.parametrize("stride", [1, 2])
+def test_im2col(K, stride):
+    x = rnd(15, 80, 300)
+    OW = (300 + 2 - 3) // stride + 1
+    dx, dy = dev(x), torch.empty((OW, 240), dtype=torch.float16, device="cuda")
+    sync_ok(K.b200_im2col_1d_f16(ptr(dx), i64(300 * 4), i64(300), i64(80), i64(3), i64(OW), stride, 1, 1, ptr(dy), None))
+    assert bits_equal(dy.cpu().numpy(), O.im2col_1d(x, 3, stride))
+
+
+def test_elementwise_and_copies(K, pkg):
+    a, b = rnd(16, 7, 384), rnd(17, 1, 384)
+    da, db, dd = dev(a), dev(b), torch.empty((7, 384), device="cuda")
+    nba, nbb = arr4([4, 384 * 4, 384 * 7 * 4, 384 * 7 * 4]), arr4([4, 384 * 4, 384 * 4, 384 * 4])
+    sync_ok(K.b200_binary(0, ptr(da), arr4([384, 7, 1, 1]), nba, ptr(db), arr4([384, 1, 1, 1]), nbb, ptr(dd), nba, None))
+    assert bits_equal(dd.cpu().numpy(), a + b)
+    sync_ok(K.b200_binary(1, ptr(da), arr4([384, 7, 1, 1]), nba, ptr(db), arr4([384, 1, 1, 1]), nbb, ptr(dd), nba, None))
+    assert bits_equal(dd.cpu().numpy(), a * b)
+    sync_ok(K.b200_scale(ptr(da), ptr(dd), i64(a.size), C.c_float(0.3535), None))
+    assert bits_equal(dd.cpu().numpy(), a * np.float32(0.3535))
+    # cont(transpose): src viewed as [7, 384] with swapped strides -> contiguous [7(fast), 384]
+    dt = torch.empty((384, 7), device="cuda")
+    sync_ok(K.b200_cpy(ptr(da), 0, arr4([7, 384, 1, 1]), arr4([384 * 4, 4, 7 * 384 * 4, 7 * 384 * 4]), ptr(dt), 0, arr4([7, 384, 1, 1]),
+                       arr4([4, 7 * 4, 7 * 384 * 4, 7 * 384 * 4]), None))
+    assert bits_equal(dt.cpu().numpy(), a.T)
+    dh = torch.empty((7, 384), dtype=torch.float16, device="cuda")
+    sync_ok(K.b200_cpy(ptr(da), 0, arr4([384, 7, 1, 1]), nba, ptr(dh), 1, arr4([384 * 7, 1, 1, 1]), arr4([2, 384 * 7 * 2, 384 * 7 * 2, 384 * 7 * 2]), None))
+    assert bits_equal(dh.cpu().numpy(), a.astype(np.float16))
+    # get_rows from a quantised table and an f32 table
+    table = rnd(18, 50, 128, scale=0.02)
+    ids = np.array([3, 49, 0, 3], np.int32)
+    for wtype in (6, 8):
+        blocks, planes, nb = planes_of(K, pkg, wtype, table)
+        dp, di, dr = dev(planes), dev(ids), torch.empty((4, 128), device="cuda")
+        sync_ok(K.b200_get_rows(wtype, ptr(dp), i64(nb), i64(128), ptr(di), i64(4), ptr(dr), None))
+        assert bits_equal(dr.cpu().numpy(), O.dequantize(wtype, blocks).reshape(50, 128)[ids])
+    dtab, di, dr = dev(table), dev(ids), torch.empty((4, 128), device="cuda")
+    sync_ok(K.b200_get_rows(0, ptr(dtab), i64(128 * 4), i64(128), ptr(di), i64(4), ptr(dr), None))
+    assert bits_equal(dr.cpu().numpy(), table[ids])
+    # concat along dim 1
+    x1, x2 = rnd(19, 3, 64), rnd(20, 5, 64)
+    d1, d2, dc = dev(x1), dev(x2), torch.empty((8, 64), device="cuda")
+    sync_ok(K.b200_concat(ptr(d1), arr4([64, 3, 1, 1]), arr4([4, 256, 768, 768]), ptr(d2), arr4([64, 5, 1, 1]), arr4([4, 256, 1280, 1280]),
+                          ptr(dc), arr4([64, 8, 1, 1]), arr4([4, 256, 2048, 2048]), 1, None))
+    assert bits_equal(dc.cpu().numpy(), np.concatenate([x1, x2], 0))
+
+
+@pytest.mark.parametrize("n_mel,seconds", [(80, 1.0), (128, 30.0), (80, 11.0)])
+def test_log_mel(K, pkg, n_mel, seconds):
+    pcm = pkg.synth.pcm_f32(pkg.synth.make_clip(21, seconds, n_tones=None, envelopes=True))
+    filters = pkg.synth.mel_filterbank(n_mel)
+    ref = O.log_mel(pcm, filters)
+    out = np.empty_like(ref)
+    nl, nlo = C.c_int(0), C.c_int(0)
+    rc = K.b200_log_mel(0, pcm.ctypes.data_as(vp), i64(pcm.size), filters.ctypes.data_as(vp), n_mel, out.ctypes.data_as(vp), i64(out.size),
+                        C.byref(nl), C.byref(nlo))
+    assert rc == 0 and nl.value == ref.shape[1]
+    mism = int((out.view(np.uint32) != ref.view(np.uint32)).sum())
+    # log10 of the device maths library may differ from libm's in the last double bit; after rounding to float
+    # that can flip an isolated value by one ulp.  Tolerance: at most 1e-5 of the values, each within 1 f32 ulp.
+    assert mism <= max(1, out.size // 100000), f"{mism} of {out.size} mel values differ"
+    assert np.abs(out - ref).max() <= 2.4e-7 * max(1.0, np.abs(ref).max())

@@ -30,9 +30,11 @@ def run_pair(pkg, model_dir, arch, wtype, flash, n_new=32, seed=1):
     out = {}
     cpu = pkg.Whisper(path, use_gpu=False, flash_attn=flash, probe=True)
     mel = cpu.pcm_to_mel(pcm)[:, :3000].copy()
+    from whisper_cpp_b200.host import backend_stat
     for name, w in (("cpu", cpu), ("gpu", None)):
         if w is None:
             w = pkg.Whisper(path, use_gpu=True, flash_attn=flash, probe=True)
+            nodes0, launches0 = backend_stat("b200_stat_nodes", True), pkg.kernels_lib().b200_launch_count()
         w.set_mel(mel)
         enc = w.encode()
         force = out["cpu"]["tokens"] if name == "gpu" else None
@@ -41,6 +43,10 @@ def run_pair(pkg, model_dir, arch, wtype, flash, n_new=32, seed=1):
         if name == "gpu":   # free-running ids as well
             w.set_mel(mel)
             out[name]["free_tokens"] = w.greedy(n_new)[0]
+            # the plugin, not the CPU backend, must have executed the graphs
+            n_layers = {"tiny": 4, "base": 6}[arch]
+            assert backend_stat("b200_stat_nodes", True) - nodes0 > 2 * (20 * n_layers * (n_new + 1))
+            assert pkg.kernels_lib().b200_launch_count() - launches0 > 0
         w.close()
     return out
 
