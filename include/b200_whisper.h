@@ -70,6 +70,28 @@ int b200_mul_mat_vec_q(int wtype, const void * w_planes, int64_t nb_total, int64
                        const float * x, int64_t x_stride_bytes, int64_t N,
                        float * dst, int64_t dst_stride, void * stream);
 
+/* Fused form of the above for the decode step: the product value passes through up to four steps, in the
+ * order given, before it is stored - the ADD / SCALE / UNARY(GELU) / CPY nodes that follow a MUL_MAT node in
+ * the whisper decoder graph (src/whisper.cpp:2533-2830), evaluated with the same single-precision
+ * operations, so the stored bits equal those of the unfused node sequence.
+ *   B200_EP_ADD   v = v + ptr[m + n*stride_n]   (stride_n = 0: bias broadcast over columns)
+ *   B200_EP_SCALE v = v * scalar
+ *   B200_EP_GELU  v = gelu_table(v)
+ * store_f16 != 0 stores round-to-nearest-even f16 (the F32->F16 CPY into the KV cache) instead of f32. */
+#define B200_EP_ADD   1
+#define B200_EP_SCALE 2
+#define B200_EP_GELU  3
+typedef struct { int kind; const float * ptr; int64_t stride_n; float scalar; } b200_ep_step;
+typedef struct { int n_steps; b200_ep_step step[4]; int store_f16; } b200_epilogue;
+int b200_mul_mat_vec_q_ep(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                          const float * x, int64_t x_stride_bytes, int64_t N,
+                          void * dst, int64_t dst_stride, const b200_epilogue * ep, void * stream);
+
+/* NORM -> MUL(gamma) -> ADD(beta) in one pass (ops.cpp:3109-3158 followed by binary-ops.cpp:50-137), each of the
+ * three roundings kept: y = ((x - mean) * rstd) * gamma + beta. */
+int b200_layer_norm(const float * x, const float * gamma, const float * beta, float * y, int64_t ne00, int64_t nrows,
+                    int64_t x_row_stride_bytes, int64_t y_row_stride_bytes, float eps, void * stream);
+
 /* mul_mat with F16 src0 (ggml_vec_dot_f16, ggml/src/ggml-cpu/vec.cpp:128-167): src1 is f32 (rounded
  * to f16 first, ggml-cpu.c:1329-1362) or f16.  Strides in bytes; src0 [K, M, ne02, ne03],
  * src1 [K, N, ne12, ne13] with ne12 % ne02 == 0, dst f32 contiguous [M, N, ne12, ne13]. */

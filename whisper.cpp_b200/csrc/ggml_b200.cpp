@@ -19,6 +19,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #define B200_MAX_DEVICES 16
@@ -369,6 +370,119 @@ static int compute_node(b200_backend_ctx * ctx, struct ggml_tensor * node) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// node-sequence fusion.  A fused launch evaluates the same single-precision operations in the same
+// order as the node sequence it replaces, so the bits that reach memory do not change; what goes
+// away is the round trip of the intermediate through HBM and the extra launches.
+// ---------------------------------------------------------------------------------------------
+struct graph_info {
+    std::unordered_map<const struct ggml_tensor *, int> index;   // node -> position
+    std::vector<int> uses;                                        // consumers inside the graph
+};
+
+static void analyse_graph(struct ggml_cgraph * g, graph_info & gi) {
+    const int n = ggml_graph_n_nodes(g);
+    gi.uses.assign(n, 0);
+    gi.index.reserve(n * 2);
+    for (int i = 0; i < n; ++i) gi.index[ggml_graph_node(g, i)] = i;
+    for (int i = 0; i < n; ++i) {
+        const struct ggml_tensor * t = ggml_graph_node(g, i);
+        for (int k = 0; k < GGML_MAX_SRC; ++k) {
+            if (!t->src[k]) continue;
+            auto it = gi.index.find(t->src[k]);
+            if (it != gi.index.end()) gi.uses[it->second]++;
+        }
+        if (t->view_src) {
+            auto it = gi.index.find(t->view_src);
+            if (it != gi.index.end()) gi.uses[it->second]++;
+        }
+    }
+}
+
+// operand is available before position i (a leaf, or a node computed earlier)
+static bool ready_before(const graph_info & gi, const struct ggml_tensor * t, int i) {
+    const struct ggml_tensor * base = t;
+    while (base->view_src) base = base->view_src;
+    auto it = gi.index.find(t);
+    if (it != gi.index.end() && it->second >= i) return false;
+    it = gi.index.find(base);
+    if (it != gi.index.end() && it->second >= i) return false;
+    return true;
+}
+
+static bool overlaps(const struct ggml_tensor * a, const struct ggml_tensor * b) {
+    const char * a0 = (const char *) a->data, * b0 = (const char *) b->data;
+    return a0 < b0 + ggml_nbytes(b) && b0 < a0 + ggml_nbytes(a);
+}
+
+static bool only_feeds(const graph_info & gi, const struct ggml_tensor * t, int pos) {
+    return gi.uses[pos] == 1 && !(t->flags & GGML_TENSOR_FLAG_OUTPUT);
+}
+
+// NORM -> MUL(gamma) -> ADD(beta) starting at node i; returns the index of the ADD node or -1
+static int match_layer_norm(struct ggml_cgraph * g, const graph_info & gi, int i, const struct ggml_tensor ** gamma, const struct ggml_tensor ** beta) {
+    const int n = ggml_graph_n_nodes(g);
+    struct ggml_tensor * nrm = ggml_graph_node(g, i);
+    if (i + 2 >= n || !only_feeds(gi, nrm, i)) return -1;
+    struct ggml_tensor * mul = ggml_graph_node(g, i + 1);
+    struct ggml_tensor * add = ggml_graph_node(g, i + 2);
+    if (mul->op != GGML_OP_MUL || add->op != GGML_OP_ADD || mul->src[0] != nrm || add->src[0] != mul || !only_feeds(gi, mul, i + 1)) return -1;
+    const struct ggml_tensor * ga = mul->src[1], * be = add->src[1], * x = nrm->src[0];
+    auto vec_ok = [&](const struct ggml_tensor * v) {
+        return v->type == GGML_TYPE_F32 && v->ne[0] == x->ne[0] && v->ne[1] == 1 && v->ne[2] == 1 && v->ne[3] == 1 && v->nb[0] == 4;
+    };
+    if (!vec_ok(ga) || !vec_ok(be) || !ready_before(gi, ga, i) || !ready_before(gi, be, i)) return -1;
+    if (x->ne[2] != 1 || x->ne[3] != 1 || x->nb[0] != 4 || add->nb[0] != 4 || !ggml_are_same_shape(x, add)) return -1;
+    *gamma = ga; *beta = be;
+    return i + 2;
+}
+
+// MUL_MAT (quantised weights, <= 8 columns) followed by ADD / SCALE / GELU nodes and an optional F32->F16 CPY.
+// Fills ep, *last = index of the last fused node, *out = tensor whose memory receives the result.
+static void match_vec_epilogue(struct ggml_cgraph * g, const graph_info & gi, int i, b200_epilogue * ep, int * last, struct ggml_tensor ** out,
+                               std::vector<char> & fused) {
+    const int n = ggml_graph_n_nodes(g);
+    struct ggml_tensor * cur = ggml_graph_node(g, i);
+    const int64_t M = cur->ne[0], N = cur->ne[1];
+    int cur_pos = i;
+    ep->n_steps = 0; ep->store_f16 = 0;
+    *last = i; *out = cur;
+    for (int j = i + 1; j < n && ep->n_steps < 4; ++j) {
+        struct ggml_tensor * t = ggml_graph_node(g, j);
+        if (is_view_op(t->op)) {
+            if (t->src[0] == cur || t->view_src == cur) break;      // someone looks at cur itself
+            continue;
+        }
+        if (!only_feeds(gi, cur, cur_pos)) break;
+        b200_ep_step st = {0, nullptr, 0, 0.0f};
+        if (t->op == GGML_OP_ADD && (t->src[0] == cur || t->src[1] == cur) && t->type == GGML_TYPE_F32) {
+            const struct ggml_tensor * o = t->src[0] == cur ? t->src[1] : t->src[0];
+            if (o == cur || o->type != GGML_TYPE_F32 || o->nb[0] != 4 || o->ne[0] != M || o->ne[2] != 1 || o->ne[3] != 1) break;
+            if (o->ne[1] != 1 && o->ne[1] != N) break;
+            if (!ggml_are_same_shape(t, cur) || !ready_before(gi, o, i)) break;
+            st.kind = B200_EP_ADD; st.ptr = (const float *) o->data; st.stride_n = (o->ne[1] == 1) ? 0 : (int64_t) o->nb[1] / 4;
+        } else if (t->op == GGML_OP_SCALE && t->src[0] == cur) {
+            st.kind = B200_EP_SCALE;
+            memcpy(&st.scalar, t->op_params, sizeof(float));
+        } else if (t->op == GGML_OP_UNARY && t->src[0] == cur && ggml_get_unary_op(t) == GGML_UNARY_OP_GELU) {
+            st.kind = B200_EP_GELU;
+        } else if (t->op == GGML_OP_CPY && t->src[0] == cur && t->type == GGML_TYPE_F16 && ggml_is_contiguous(t) &&
+                   ggml_nelements(t) == M * N && ggml_is_contiguous(cur)) {
+            ep->store_f16 = 1;
+            fused[j] = 1;
+            *last = j; *out = t;
+            return;
+        } else {
+            break;
+        }
+        if (t->nb[0] != 4) break;
+        ep->step[ep->n_steps++] = st;
+        fused[j] = 1;
+        cur = t; cur_pos = j;
+        *last = j; *out = t;
+    }
+}
+
 // timing class of a node and its algorithmic work (bytes for memory-bound classes, FLOPs for contractions)
 static int node_class(const struct ggml_tensor * node, double * work) {
     const struct ggml_tensor * s0 = node->src[0];
@@ -412,9 +526,14 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
         if (n_ev == ctx->events.size()) { cudaEvent_t e; cudaEventCreate(&e); ctx->events.push_back(e); }
         return ctx->events[n_ev++];
     };
+    static const bool fuse = getenv("GGML_B200_NO_FUSION") == nullptr;
+    graph_info gi;
+    std::vector<char> fused(n_nodes, 0);
+    if (fuse) analyse_graph(cgraph, gi);
     for (int i = 0; i < n_nodes; ++i) {
         struct ggml_tensor * node = ggml_graph_node(cgraph, i);
         if (is_view_op(node->op) || ggml_is_empty(node)) continue;
+        if (fused[i]) { ++done; continue; }
         if (!b200_op_supported(node)) {
             fprintf(stderr, "ggml-b200: unsupported node %s (%s) reached graph_compute\n", node->name, ggml_op_name(node->op));
             return GGML_STATUS_FAILED;
@@ -425,7 +544,38 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
             t_work.push_back(work);
             cudaEventRecord(next_event(), ctx->stream);
         }
-        const int e = compute_node(ctx, node);
+        int e = -1;
+        if (fuse && node->op == GGML_OP_NORM) {
+            const struct ggml_tensor * ga = nullptr, * be = nullptr;
+            const int last = match_layer_norm(cgraph, gi, i, &ga, &be);
+            struct ggml_tensor * out = last > 0 ? ggml_graph_node(cgraph, last) : nullptr;
+            const struct ggml_tensor * x = node->src[0];
+            // rows are read and written by the same lanes, so exact in-place is fine; a shifted overlap is not
+            const bool alias_ok = out && (!overlaps(out, x) || (out->data == x->data && out->nb[1] == x->nb[1]));
+            if (last > 0 && alias_ok && b200_op_supported(ggml_graph_node(cgraph, i + 1)) && b200_op_supported(out)) {
+                float eps;
+                memcpy(&eps, node->op_params, sizeof(float));
+                e = b200_layer_norm((const float *) x->data, (const float *) ga->data, (const float *) be->data, (float *) out->data,
+                                    x->ne[0], x->ne[1], (int64_t) x->nb[1], (int64_t) out->nb[1], eps, (void *) ctx->stream);
+                fused[i + 1] = 1; fused[last] = 1;
+            }
+        } else if (fuse && node->op == GGML_OP_MUL_MAT && is_quant(node->src[0]->type) && node->src[1]->ne[1] <= 8) {
+            b200_epilogue ep;
+            int last = i;
+            struct ggml_tensor * out = node;
+            match_vec_epilogue(cgraph, gi, i, &ep, &last, &out, fused);
+            const struct ggml_tensor * s0 = node->src[0], * s1 = node->src[1];
+            if (out != node && overlaps(out, s1)) {
+                // the allocator placed the final tensor over the activations, which every CTA still reads: run unfused
+                for (int j = i + 1; j <= last; ++j) fused[j] = 0;
+                ep.n_steps = 0; ep.store_f16 = 0; out = node;
+            }
+            const int64_t nb_total = (int64_t) (ggml_nbytes(s0) / ggml_type_size(s0->type));
+            const int64_t ldd = ep.store_f16 ? node->ne[0] : (int64_t) out->nb[1] / 4;
+            e = b200_mul_mat_vec_q_ep((int) s0->type, s0->data, nb_total, s0->ne[1], s0->ne[0], (const float *) s1->data, (int64_t) s1->nb[1],
+                                      s1->ne[1], out->data, ldd, &ep, (void *) ctx->stream);
+        }
+        if (e == -1) e = compute_node(ctx, node);
         if (timing) cudaEventRecord(next_event(), ctx->stream);
         if (e != 0) {
             fprintf(stderr, "ggml-b200: node %d %s (%s) failed with code %d (%s)\n", i, node->name, ggml_op_name(node->op), e,

@@ -189,6 +189,157 @@ k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
     *(float2 *) (dst + (iq1 * n_head + h) * 64 + lane * 2) = o;
 }
 
+
+// Few query rows (token-by-token decode, beams): one CTA per (query row, head).  The work of the kernel above is
+// split by role so that the sequential part is as short as possible: all threads score the keys, a block scan gives
+// every key the running maximum it meets, exp() runs in parallel, then 64 threads (one per output dim) replay the
+// F16 accumulation key by key while one more thread replays the running sum.
+#define FA_DEC_THREADS 256
+#define FA_DEC_MAX_KV  8192
+template <bool S_FMA>
+__global__ void __launch_bounds__(FA_DEC_THREADS)
+k_flash_attn_decode(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
+                    const char * __restrict__ k, int64_t nbk1, int64_t nbk2,
+                    const char * __restrict__ v, int64_t nbv1, int64_t nbv2,
+                    const char * __restrict__ mask, int64_t nbm1,
+                    float * __restrict__ dst, int64_t n_q, int n_kv, int64_t n_head, float scale) {
+    extern __shared__ __align__(16) float fa_smem[];
+    float * Qs  = fa_smem;                 // [64]
+    float * sc  = Qs + 64;                 // [n_kv] scores, later vs
+    float * msv = sc + n_kv;               // [n_kv] ms (1 unless a new maximum), < 0 marks a skipped key
+    __shared__ float seg_max[FA_DEC_THREADS];
+    __shared__ float s_S;
+    const int tid = threadIdx.x;
+    const int64_t iq1 = blockIdx.x, h = blockIdx.y;
+
+    if (tid < 64) Qs[tid] = round_f16(*(const float *) (q + iq1 * nbq1 + h * nbq2 + tid * 4));
+    __syncthreads();
+
+    const char * kh = k + h * nbk2;
+    const char * vh = v + h * nbv2;
+    const __half * mp = mask ? (const __half *) (mask + iq1 * nbm1) : nullptr;
+
+    // scores
+    for (int ic = tid; ic < n_kv; ic += FA_DEC_THREADS) {
+        float mv = 0.0f;
+        if (mp) mv = __half2float(mp[ic]);
+        float s = -INFINITY;
+        bool skip = (mv == -INFINITY);
+        if (!skip) {
+            float acc[32];
+            const uint4 * kp = (const uint4 *) (kh + (int64_t) ic * nbk1);
+#pragma unroll
+            for (int step = 0; step < 2; ++step) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const uint4 kv = kp[step * 4 + c];
+                    const float4 qa = *(const float4 *) &Qs[step * 32 + c * 8];
+                    const float4 qb = *(const float4 *) &Qs[step * 32 + c * 8 + 4];
+                    const float2 k0 = __half22float2(*(const __half2 *) &kv.x);
+                    const float2 k1 = __half22float2(*(const __half2 *) &kv.y);
+                    const float2 k2 = __half22float2(*(const __half2 *) &kv.z);
+                    const float2 k3 = __half22float2(*(const __half2 *) &kv.w);
+                    float * a = &acc[c * 8];
+                    if (step == 0) {
+                        a[0] = __fmaf_rn(k0.x, qa.x, 0.0f); a[1] = __fmaf_rn(k0.y, qa.y, 0.0f);
+                        a[2] = __fmaf_rn(k1.x, qa.z, 0.0f); a[3] = __fmaf_rn(k1.y, qa.w, 0.0f);
+                        a[4] = __fmaf_rn(k2.x, qb.x, 0.0f); a[5] = __fmaf_rn(k2.y, qb.y, 0.0f);
+                        a[6] = __fmaf_rn(k3.x, qb.z, 0.0f); a[7] = __fmaf_rn(k3.y, qb.w, 0.0f);
+                    } else {
+                        a[0] = __fmaf_rn(k0.x, qa.x, a[0]); a[1] = __fmaf_rn(k0.y, qa.y, a[1]);
+                        a[2] = __fmaf_rn(k1.x, qa.z, a[2]); a[3] = __fmaf_rn(k1.y, qa.w, a[3]);
+                        a[4] = __fmaf_rn(k2.x, qb.x, a[4]); a[5] = __fmaf_rn(k2.y, qb.y, a[5]);
+                        a[6] = __fmaf_rn(k3.x, qb.z, a[6]); a[7] = __fmaf_rn(k3.y, qb.w, a[7]);
+                    }
+                }
+            }
+            float y[8];
+#pragma unroll
+            for (int p = 0; p < 8; ++p)
+                y[p] = __fadd_rn(__fadd_rn(acc[p], acc[16 + p]), __fadd_rn(acc[8 + p], acc[24 + p]));
+            const float t0 = __fadd_rn(y[0], y[4]), t1 = __fadd_rn(y[1], y[5]);
+            const float t2 = __fadd_rn(y[2], y[6]), t3 = __fadd_rn(y[3], y[7]);
+            s = __fadd_rn(__fadd_rn(t0, t1), __fadd_rn(t2, t3));
+            s = __fmul_rn(s, scale);
+            s = __fadd_rn(s, mv);
+        }
+        sc[ic]  = s;                       // -inf for skipped keys: never a new maximum
+        msv[ic] = skip ? -1.0f : 1.0f;
+    }
+    __syncthreads();
+
+    // contiguous segment per thread: segment maxima, exclusive block scan, then the per-key pass
+    const int seg = (n_kv + FA_DEC_THREADS - 1) / FA_DEC_THREADS;
+    const int i0 = tid * seg, i1 = min(n_kv, i0 + seg);
+    float m = -INFINITY;
+    for (int i = i0; i < i1; ++i) m = fmaxf(m, sc[i]);
+    seg_max[tid] = m;
+    __syncthreads();
+    if (tid < 32) {                        // exclusive prefix maximum over the 256 segment maxima
+        float carry = -INFINITY;
+        for (int base = 0; base < FA_DEC_THREADS; base += 32) {
+            const float x = seg_max[base + tid];
+            float inc = x;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float t = __shfl_up_sync(0xffffffffu, inc, o);
+                if (tid >= o) inc = fmaxf(inc, t);
+            }
+            float exc = __shfl_up_sync(0xffffffffu, inc, 1);
+            if (tid == 0) exc = -INFINITY;
+            seg_max[base + tid] = fmaxf(carry, exc);
+            carry = fmaxf(carry, __shfl_sync(0xffffffffu, inc, 31));
+        }
+    }
+    __syncthreads();
+    {
+        float M = seg_max[tid];
+        for (int i = i0; i < i1; ++i) {
+            if (msv[i] < 0.0f) continue;
+            const float s = sc[i];
+            if (s > M) { msv[i] = expf_glibc(__fadd_rn(M, -s)); sc[i] = 1.0f; M = s; }
+            else       { sc[i] = expf_glibc(__fadd_rn(s, -M)); }
+        }
+    }
+    __syncthreads();
+
+    if (tid < 64) {
+        const char * vp = vh + tid * 2;
+        float a = 0.0f;
+        int i = 0;
+        for (; i + 8 <= n_kv; i += 8) {
+            __half hv[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) hv[u] = *(const __half *) (vp + (int64_t) (i + u) * nbv1);
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float ms = msv[i + u], vs = sc[i + u];
+                if (ms >= 0.0f) {
+                    if (ms != 1.0f) a = round_f16(__fmul_rn(a, ms));
+                    a = round_f16(__fmaf_rn(__half2float(hv[u]), vs, a));
+                }
+            }
+        }
+        for (; i < n_kv; ++i) {
+            const float ms = msv[i], vs = sc[i];
+            if (ms >= 0.0f) {
+                if (ms != 1.0f) a = round_f16(__fmul_rn(a, ms));
+                a = round_f16(__fmaf_rn(__half2float(*(const __half *) (vp + (int64_t) i * nbv1)), vs, a));
+            }
+        }
+        Qs[tid] = a;                       // Qs is free now
+    } else if (tid == 64) {
+        float S = 0.0f;
+        for (int i = 0; i < n_kv; ++i) {
+            const float ms = msv[i];
+            if (ms >= 0.0f) S = S_FMA ? __fmaf_rn(S, ms, sc[i]) : __fadd_rn(__fmul_rn(S, ms), sc[i]);
+        }
+        s_S = S;
+    }
+    __syncthreads();
+    if (tid < 64) dst[(iq1 * n_head + h) * 64 + tid] = __fmul_rn(Qs[tid], __fdiv_rn(1.0f, s_S));
+}
+
 // The host compiler of the reference contracts "S*ms + vs" into one FMA (GNU mode, -mfma).
 static bool g_fa_s_fma = true;
 extern "C" void b200_set_fa_sum_fma(int on) { g_fa_s_fma = on != 0; }
@@ -203,6 +354,25 @@ extern "C" int b200_flash_attn_ext(const float * q, int64_t nbq1, int64_t nbq2,
     if (((uintptr_t) k & 15) || (nbk1 & 15) || (nbk2 & 15) || ((uintptr_t) v & 3) || (nbv1 & 3) || (nbv2 & 3)) return B200_ERR_ARG;
     if (((uintptr_t) q & 3) || (nbq1 & 3) || (nbq2 & 3) || ((uintptr_t) dst & 7)) return B200_ERR_ARG;
     ensure_exp_table();
+    if (n_q <= 16 && n_kv <= FA_DEC_MAX_KV) {
+        dim3 dgrid((unsigned) n_q, (unsigned) n_head);
+        const size_t smem = (64 + 2 * (size_t) n_kv) * sizeof(float);
+        static bool attr_done[64] = {false};
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+            cudaFuncSetAttribute(k_flash_attn_decode<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (64 + 2 * FA_DEC_MAX_KV) * 4);
+            cudaFuncSetAttribute(k_flash_attn_decode<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (64 + 2 * FA_DEC_MAX_KV) * 4);
+            attr_done[dev] = true;
+        }
+        if (g_fa_s_fma)
+            k_flash_attn_decode<true><<<dgrid, FA_DEC_THREADS, smem, as_stream(stream)>>>((const char *) q, nbq1, nbq2, (const char *) k, nbk1, nbk2,
+                (const char *) v, nbv1, nbv2, (const char *) mask, nbm1, dst, n_q, (int) n_kv, n_head, scale);
+        else
+            k_flash_attn_decode<false><<<dgrid, FA_DEC_THREADS, smem, as_stream(stream)>>>((const char *) q, nbq1, nbq2, (const char *) k, nbk1, nbk2,
+                (const char *) v, nbv1, nbv2, (const char *) mask, nbm1, dst, n_q, (int) n_kv, n_head, scale);
+        B200_RETURN_LAST();
+    }
     dim3 grid((unsigned) ((n_q + 3) / 4), (unsigned) n_head);
     if (g_fa_s_fma)
         k_flash_attn_ext<true><<<grid, 128, 0, as_stream(stream)>>>((const char *) q, nbq1, nbq2, (const char *) k, nbk1, nbk2,

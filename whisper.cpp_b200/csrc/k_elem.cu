@@ -43,6 +43,42 @@ extern "C" int b200_norm(const float * x, float * y, int64_t ne00, int64_t ne01,
     B200_RETURN_LAST();
 }
 
+__global__ void __launch_bounds__(128)
+k_layer_norm(const char * __restrict__ x, const float * __restrict__ gamma, const float * __restrict__ beta, char * __restrict__ y,
+             int64_t ne00, int64_t nrows, int64_t xs, int64_t ys, float eps) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row = (int64_t) blockIdx.x * 4 + warp;
+    if (row >= nrows) return;
+    const float * xp = (const float *) (x + row * xs);
+    float *       yp = (float *)       (y + row * ys);
+    double sum = 0.0;
+    for (int64_t i = lane; i < ne00; i += 32) sum += (double) xp[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    const float mean = (float) (sum / (double) ne00);
+    double sum2 = 0.0;
+    for (int64_t i = lane; i < ne00; i += 32) {
+        const float v = __fadd_rn(xp[i], -mean);
+        sum2 += (double) __fmul_rn(v, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum2 += __shfl_xor_sync(0xffffffffu, sum2, o);
+    const float variance = (float) (sum2 / (double) ne00);
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(variance, eps)));
+    for (int64_t i = lane; i < ne00; i += 32) {
+        const float t = __fmul_rn(__fadd_rn(xp[i], -mean), scale);
+        yp[i] = __fadd_rn(__fmul_rn(t, gamma[i]), beta[i]);
+    }
+}
+
+extern "C" int b200_layer_norm(const float * x, const float * gamma, const float * beta, float * y, int64_t ne00, int64_t nrows,
+                               int64_t x_row_stride_bytes, int64_t y_row_stride_bytes, float eps, void * stream) {
+    if (nrows <= 0 || ne00 <= 0) return 0;
+    k_layer_norm<<<(unsigned) ((nrows + 3) / 4), 128, 0, as_stream(stream)>>>((const char *) x, gamma, beta, (char *) y, ne00, nrows,
+        x_row_stride_bytes, y_row_stride_bytes, eps);
+    B200_RETURN_LAST();
+}
+
 // ---- add / mul with broadcast ----------------------------------------------------------------
 template <int OP>
 __global__ void k_binary(const char * __restrict__ a, Dims4 da, const char * __restrict__ b, Dims4 db,
@@ -103,6 +139,16 @@ static int ensure_gelu_table() {
     if (e != cudaSuccess) return (int) e;
     done[dev] = true;
     return 0;
+}
+
+// device address of the table on the current device (for kernels of other translation units)
+const uint16_t * b200_gelu_table_device(int * err) {
+    *err = ensure_gelu_table();
+    if (*err) return nullptr;
+    void * p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_gelu_table);
+    if (e != cudaSuccess) { *err = (int) e; return nullptr; }
+    return (const uint16_t *) p;
 }
 
 __global__ void k_gelu(const float * __restrict__ x, float * __restrict__ y, int64_t n) {

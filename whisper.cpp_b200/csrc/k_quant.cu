@@ -306,10 +306,33 @@ extern "C" int b200_mul_mat_q(int wtype, const void * w_planes, int64_t nb_total
 // integer lane sums for 32 blocks in parallel, then eight threads per column replay the FMA chain in
 // block order.  Activations are quantised by the CTA itself.
 // ------------------------------------------------------------------------------------------------
+struct EpDev {
+    int n_steps;
+    int kind[4];
+    const float * ptr[4];
+    int64_t stride_n[4];
+    float scalar[4];
+    int store_f16;
+    const uint16_t * gelu_table;
+};
+
+__device__ __forceinline__ void ep_store(const EpDev & ep, void * dst, int64_t ldd, int64_t n, int64_t m, float v) {
+    for (int s = 0; s < ep.n_steps; ++s) {
+        if (ep.kind[s] == B200_EP_ADD)        v = __fadd_rn(v, ep.ptr[s][m + n * ep.stride_n[s]]);
+        else if (ep.kind[s] == B200_EP_SCALE) v = __fmul_rn(v, ep.scalar[s]);
+        else {
+            if (v <= -10.0f)     v = 0.0f;
+            else if (v < 10.0f)  v = __half2float(__ushort_as_half(ep.gelu_table[__half_as_ushort(__float2half_rn(v))]));
+        }
+    }
+    if (ep.store_f16) ((__half *) dst)[n * ldd + m] = __float2half_rn(v);
+    else              ((float *) dst)[n * ldd + m] = v;
+}
+
 template <int TYPE, int N>
 __global__ void __launch_bounds__(128)
 k_mul_mat_vec_q(QPlanes w, int64_t M, int64_t nbk, const float * __restrict__ x, int64_t x_stride,
-                float * __restrict__ dst, int64_t ldd, int rows_per_warp) {
+                void * __restrict__ dst, int64_t ldd, int rows_per_warp, EpDev ep) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int PSTR = 32 * 8 + 8;                 // padded per-column stride of P
     const int K = (int) nbk * 32;
@@ -402,54 +425,79 @@ k_mul_mat_vec_q(QPlanes w, int64_t M, int64_t nbk, const float * __restrict__ x,
             acc1 = __fadd_rn(acc1, __shfl_xor_sync(0xffffffffu, acc1, o));
         }
         if (j == 0) {
-            if (cn < N) dst[(int64_t) cn * ldd + m] = acc0;
-            if (N > 4 && cn + 4 < N) dst[(int64_t) (cn + 4) * ldd + m] = acc1;
+            if (cn < N) ep_store(ep, dst, ldd, cn, m, acc0);
+            if (N > 4 && cn + 4 < N) ep_store(ep, dst, ldd, cn + 4, m, acc1);
         }
     }
 }
 
 template <int TYPE, int N>
-static int launch_vec(const QPlanes & w, int64_t M, int64_t nbk, const float * x, int64_t xs, float * dst, int64_t ldd, cudaStream_t st) {
+static int launch_vec(const QPlanes & w, int64_t M, int64_t nbk, const float * x, int64_t xs, void * dst, int64_t ldd, const EpDev & ep, cudaStream_t st) {
     constexpr int PSTR = 32 * 8 + 8;
     const size_t smem = (size_t) N * nbk * 32 + (size_t) N * nbk * 4 + 4 * (size_t) ((32 * 12 + 32 + N * PSTR + N * 32) * 4);
-    static bool attr_done = false;   // per instantiation; benign race (idempotent call)
-    if (!attr_done) {
+    static bool attr_done[64] = {false};   // per instantiation and device; benign race (idempotent call)
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
         cudaFuncSetAttribute(k_mul_mat_vec_q<TYPE, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-        attr_done = true;
+        attr_done[dev] = true;
     }
     if (smem > 200 * 1024) return B200_ERR_ARG;
     // rows per warp: keep at least ~4 CTAs per SM worth of blocks when M allows it
     int rpw = 1;
     while (rpw < 8 && (M + 4 * (rpw * 2) - 1) / (4 * (rpw * 2)) >= 148 * 4) rpw *= 2;
     const int64_t rows_per_cta = 4 * rpw;
-    k_mul_mat_vec_q<TYPE, N><<<(unsigned) ((M + rows_per_cta - 1) / rows_per_cta), 128, smem, st>>>(w, M, nbk, x, xs, dst, ldd, rpw);
+    k_mul_mat_vec_q<TYPE, N><<<(unsigned) ((M + rows_per_cta - 1) / rows_per_cta), 128, smem, st>>>(w, M, nbk, x, xs, dst, ldd, rpw, ep);
     B200_RETURN_LAST();
 }
 
 template <int TYPE>
-static int launch_vec_n(int N, const QPlanes & w, int64_t M, int64_t nbk, const float * x, int64_t xs, float * dst, int64_t ldd, cudaStream_t st) {
+static int launch_vec_n(int N, const QPlanes & w, int64_t M, int64_t nbk, const float * x, int64_t xs, void * dst, int64_t ldd, const EpDev & ep, cudaStream_t st) {
     switch (N) {
-        case 1: return launch_vec<TYPE, 1>(w, M, nbk, x, xs, dst, ldd, st);
-        case 2: return launch_vec<TYPE, 2>(w, M, nbk, x, xs, dst, ldd, st);
-        case 3: return launch_vec<TYPE, 3>(w, M, nbk, x, xs, dst, ldd, st);
-        case 4: return launch_vec<TYPE, 4>(w, M, nbk, x, xs, dst, ldd, st);
-        case 5: return launch_vec<TYPE, 5>(w, M, nbk, x, xs, dst, ldd, st);
-        case 6: return launch_vec<TYPE, 6>(w, M, nbk, x, xs, dst, ldd, st);
-        case 7: return launch_vec<TYPE, 7>(w, M, nbk, x, xs, dst, ldd, st);
-        case 8: return launch_vec<TYPE, 8>(w, M, nbk, x, xs, dst, ldd, st);
+        case 1: return launch_vec<TYPE, 1>(w, M, nbk, x, xs, dst, ldd, ep, st);
+        case 2: return launch_vec<TYPE, 2>(w, M, nbk, x, xs, dst, ldd, ep, st);
+        case 3: return launch_vec<TYPE, 3>(w, M, nbk, x, xs, dst, ldd, ep, st);
+        case 4: return launch_vec<TYPE, 4>(w, M, nbk, x, xs, dst, ldd, ep, st);
+        case 5: return launch_vec<TYPE, 5>(w, M, nbk, x, xs, dst, ldd, ep, st);
+        case 6: return launch_vec<TYPE, 6>(w, M, nbk, x, xs, dst, ldd, ep, st);
+        case 7: return launch_vec<TYPE, 7>(w, M, nbk, x, xs, dst, ldd, ep, st);
+        case 8: return launch_vec<TYPE, 8>(w, M, nbk, x, xs, dst, ldd, ep, st);
     }
+    return B200_ERR_ARG;
+}
+
+const uint16_t * b200_gelu_table_device(int * err);
+
+extern "C" int b200_mul_mat_vec_q_ep(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                                     const float * x, int64_t x_stride_bytes, int64_t N,
+                                     void * dst, int64_t dst_stride, const b200_epilogue * ep, void * stream) {
+    if (K % 32 != 0 || M <= 0 || N < 1 || N > 8) return B200_ERR_ARG;
+    if (((uintptr_t) w_planes & 15) != 0) return B200_ERR_ARG;
+    const int64_t nbk = K / 32;
+    if (M * nbk > nb_total) return B200_ERR_ARG;
+    EpDev e;
+    memset(&e, 0, sizeof(e));
+    if (ep) {
+        if (ep->n_steps < 0 || ep->n_steps > 4) return B200_ERR_ARG;
+        e.n_steps = ep->n_steps;
+        e.store_f16 = ep->store_f16;
+        for (int s = 0; s < ep->n_steps; ++s) {
+            e.kind[s] = ep->step[s].kind; e.ptr[s] = ep->step[s].ptr; e.stride_n[s] = ep->step[s].stride_n; e.scalar[s] = ep->step[s].scalar;
+            if (e.kind[s] == B200_EP_GELU && !e.gelu_table) {
+                int err = 0;
+                e.gelu_table = b200_gelu_table_device(&err);
+                if (err) return err;
+            } else if (e.kind[s] != B200_EP_ADD && e.kind[s] != B200_EP_SCALE && e.kind[s] != B200_EP_GELU) return B200_ERR_ARG;
+        }
+    }
+    const QPlanes w = q_planes(wtype, w_planes, nb_total);
+    if (wtype == B200_TYPE_Q5_0) return launch_vec_n<B200_TYPE_Q5_0>((int) N, w, M, nbk, x, x_stride_bytes, dst, dst_stride, e, as_stream(stream));
+    if (wtype == B200_TYPE_Q8_0) return launch_vec_n<B200_TYPE_Q8_0>((int) N, w, M, nbk, x, x_stride_bytes, dst, dst_stride, e, as_stream(stream));
     return B200_ERR_ARG;
 }
 
 extern "C" int b200_mul_mat_vec_q(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
                                   const float * x, int64_t x_stride_bytes, int64_t N,
                                   float * dst, int64_t dst_stride, void * stream) {
-    if (K % 32 != 0 || M <= 0 || N < 1 || N > 8) return B200_ERR_ARG;
-    if (((uintptr_t) w_planes & 15) != 0) return B200_ERR_ARG;
-    const int64_t nbk = K / 32;
-    if (M * nbk > nb_total) return B200_ERR_ARG;
-    const QPlanes w = q_planes(wtype, w_planes, nb_total);
-    if (wtype == B200_TYPE_Q5_0) return launch_vec_n<B200_TYPE_Q5_0>((int) N, w, M, nbk, x, x_stride_bytes, dst, dst_stride, as_stream(stream));
-    if (wtype == B200_TYPE_Q8_0) return launch_vec_n<B200_TYPE_Q8_0>((int) N, w, M, nbk, x, x_stride_bytes, dst, dst_stride, as_stream(stream));
-    return B200_ERR_ARG;
+    return b200_mul_mat_vec_q_ep(wtype, w_planes, nb_total, M, K, x, x_stride_bytes, N, dst, dst_stride, nullptr, stream);
 }
