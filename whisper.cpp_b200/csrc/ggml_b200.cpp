@@ -440,7 +440,7 @@ static int match_layer_norm(struct ggml_cgraph * g, const graph_info & gi, int i
 // MUL_MAT (quantised weights, <= 8 columns) followed by ADD / SCALE / GELU nodes and an optional F32->F16 CPY.
 // Fills ep, *last = index of the last fused node, *out = tensor whose memory receives the result.
 static void match_vec_epilogue(struct ggml_cgraph * g, const graph_info & gi, int i, b200_epilogue * ep, int * last, struct ggml_tensor ** out,
-                               std::vector<char> & fused) {
+                               std::vector<char> & fused, const struct ggml_tensor ** operands) {
     const int n = ggml_graph_n_nodes(g);
     struct ggml_tensor * cur = ggml_graph_node(g, i);
     const int64_t M = cur->ne[0], N = cur->ne[1];
@@ -461,6 +461,7 @@ static void match_vec_epilogue(struct ggml_cgraph * g, const graph_info & gi, in
             if (o->ne[1] != 1 && o->ne[1] != N) break;
             if (!ggml_are_same_shape(t, cur) || !ready_before(gi, o, i)) break;
             st.kind = B200_EP_ADD; st.ptr = (const float *) o->data; st.stride_n = (o->ne[1] == 1) ? 0 : (int64_t) o->nb[1] / 4;
+            operands[ep->n_steps] = o;
         } else if (t->op == GGML_OP_SCALE && t->src[0] == cur) {
             st.kind = B200_EP_SCALE;
             memcpy(&st.scalar, t->op_params, sizeof(float));
@@ -563,9 +564,15 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
             b200_epilogue ep;
             int last = i;
             struct ggml_tensor * out = node;
-            match_vec_epilogue(cgraph, gi, i, &ep, &last, &out, fused);
+            const struct ggml_tensor * operands[4] = {nullptr, nullptr, nullptr, nullptr};
+            match_vec_epilogue(cgraph, gi, i, &ep, &last, &out, fused, operands);
             const struct ggml_tensor * s0 = node->src[0], * s1 = node->src[1];
-            if (out != node && overlaps(out, s1)) {
+            bool hazard = out != node && overlaps(out, s1);
+            for (int k = 0; k < ep.n_steps; ++k) {
+                // an added tensor may share memory with the result only element for element (same thread reads then writes)
+                if (operands[k] && overlaps(out, operands[k]) && !(operands[k]->data == out->data && operands[k]->nb[1] == out->nb[1])) hazard = true;
+            }
+            if (hazard) {
                 // the allocator placed the final tensor over the activations, which every CTA still reads: run unfused
                 for (int j = i + 1; j <= last; ++j) fused[j] = 0;
                 ep.n_steps = 0; ep.store_f16 = 0; out = node;
