@@ -196,6 +196,7 @@ k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
 // F16 accumulation key by key while one more thread replays the running sum.
 #define FA_DEC_THREADS 256
 #define FA_DEC_MAX_KV  8192
+#define FA_DEC_CHUNK   256
 template <bool S_FMA>
 __global__ void __launch_bounds__(FA_DEC_THREADS)
 k_flash_attn_decode(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
@@ -220,6 +221,7 @@ k_flash_attn_decode(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
     const __half * mp = mask ? (const __half *) (mask + iq1 * nbm1) : nullptr;
 
     // scores
+#pragma unroll 2
     for (int ic = tid; ic < n_kv; ic += FA_DEC_THREADS) {
         float mv = 0.0f;
         if (mp) mv = __half2float(mp[ic]);
@@ -303,38 +305,47 @@ k_flash_attn_decode(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
     }
     __syncthreads();
 
-    if (tid < 64) {
-        const char * vp = vh + tid * 2;
-        float a = 0.0f;
-        int i = 0;
-        for (; i + 8 <= n_kv; i += 8) {
-            __half hv[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) hv[u] = *(const __half *) (vp + (int64_t) (i + u) * nbv1);
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const float ms = msv[i + u], vs = sc[i + u];
-                if (ms >= 0.0f) {
-                    if (ms != 1.0f) a = round_f16(__fmul_rn(a, ms));
-                    a = round_f16(__fmaf_rn(__half2float(hv[u]), vs, a));
+    // V is streamed through shared memory in chunks of FA_DEC_CHUNK keys, double buffered: warps 3..7 fetch chunk c+1
+    // while warps 0..1 (one thread per output dim) replay the F16 accumulation over chunk c and one thread of
+    // warp 2 replays the running sum.
+    {
+        __half * Vs = (__half *) (msv + n_kv);                       // [2][FA_DEC_CHUNK][64]
+        const int n_chunks = (n_kv + FA_DEC_CHUNK - 1) / FA_DEC_CHUNK;
+        auto fetch = [&](int c) {
+            const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
+            uint4 * dstv = (uint4 *) (Vs + (size_t) (c & 1) * FA_DEC_CHUNK * 64);
+            for (int t = tid - 96; t < kn * 8; t += FA_DEC_THREADS - 96)
+                dstv[t] = *(const uint4 *) (vh + (int64_t) (k0 + (t >> 3)) * nbv1 + (t & 7) * 16);
+        };
+        if (tid >= 96) fetch(0);
+        __syncthreads();
+        float a = 0.0f, S = 0.0f;
+        for (int c = 0; c < n_chunks; ++c) {
+            const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
+            if (tid >= 96) {
+                if (c + 1 < n_chunks) fetch(c + 1);
+            } else if (tid < 64) {
+                const __half * vb = Vs + (size_t) (c & 1) * FA_DEC_CHUNK * 64 + tid;
+#pragma unroll 8
+                for (int i = 0; i < kn; ++i) {
+                    const float ms = msv[k0 + i], vs = sc[k0 + i];
+                    const float vv = __half2float(vb[i * 64]);
+                    if (ms >= 0.0f) {
+                        if (ms != 1.0f) a = round_f16(__fmul_rn(a, ms));
+                        a = round_f16(__fmaf_rn(vv, vs, a));
+                    }
+                }
+            } else if (tid == 64) {
+#pragma unroll 8
+                for (int i = 0; i < kn; ++i) {
+                    const float ms = msv[k0 + i];
+                    if (ms >= 0.0f) S = S_FMA ? __fmaf_rn(S, ms, sc[k0 + i]) : __fadd_rn(__fmul_rn(S, ms), sc[k0 + i]);
                 }
             }
+            __syncthreads();
         }
-        for (; i < n_kv; ++i) {
-            const float ms = msv[i], vs = sc[i];
-            if (ms >= 0.0f) {
-                if (ms != 1.0f) a = round_f16(__fmul_rn(a, ms));
-                a = round_f16(__fmaf_rn(__half2float(*(const __half *) (vp + (int64_t) i * nbv1)), vs, a));
-            }
-        }
-        Qs[tid] = a;                       // Qs is free now
-    } else if (tid == 64) {
-        float S = 0.0f;
-        for (int i = 0; i < n_kv; ++i) {
-            const float ms = msv[i];
-            if (ms >= 0.0f) S = S_FMA ? __fmaf_rn(S, ms, sc[i]) : __fadd_rn(__fmul_rn(S, ms), sc[i]);
-        }
-        s_S = S;
+        if (tid < 64) Qs[tid] = a;         // Qs is free now
+        if (tid == 64) s_S = S;
     }
     __syncthreads();
     if (tid < 64) dst[(iq1 * n_head + h) * 64 + tid] = __fmul_rn(Qs[tid], __fdiv_rn(1.0f, s_S));
@@ -354,15 +365,15 @@ extern "C" int b200_flash_attn_ext(const float * q, int64_t nbq1, int64_t nbq2,
     if (((uintptr_t) k & 15) || (nbk1 & 15) || (nbk2 & 15) || ((uintptr_t) v & 3) || (nbv1 & 3) || (nbv2 & 3)) return B200_ERR_ARG;
     if (((uintptr_t) q & 3) || (nbq1 & 3) || (nbq2 & 3) || ((uintptr_t) dst & 7)) return B200_ERR_ARG;
     ensure_exp_table();
-    if (n_q <= 16 && n_kv <= FA_DEC_MAX_KV) {
+    if (n_q <= 16 && n_kv <= FA_DEC_MAX_KV && !((uintptr_t) v & 15) && !(nbv1 & 15) && !(nbv2 & 15)) {
         dim3 dgrid((unsigned) n_q, (unsigned) n_head);
-        const size_t smem = (64 + 2 * (size_t) n_kv) * sizeof(float);
+        const size_t smem = (64 + 2 * (size_t) n_kv) * sizeof(float) + 2 * FA_DEC_CHUNK * 64 * sizeof(__half);
         static bool attr_done[64] = {false};
         int dev = 0;
         cudaGetDevice(&dev);
         if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-            cudaFuncSetAttribute(k_flash_attn_decode<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (64 + 2 * FA_DEC_MAX_KV) * 4);
-            cudaFuncSetAttribute(k_flash_attn_decode<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (64 + 2 * FA_DEC_MAX_KV) * 4);
+            cudaFuncSetAttribute(k_flash_attn_decode<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (64 + 2 * FA_DEC_MAX_KV) * 4 + 2 * FA_DEC_CHUNK * 64 * 2);
+            cudaFuncSetAttribute(k_flash_attn_decode<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (64 + 2 * FA_DEC_MAX_KV) * 4 + 2 * FA_DEC_CHUNK * 64 * 2);
             attr_done[dev] = true;
         }
         if (g_fa_s_fma)

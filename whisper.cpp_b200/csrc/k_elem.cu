@@ -71,9 +71,68 @@ k_layer_norm(const char * __restrict__ x, const float * __restrict__ gamma, cons
     }
 }
 
+// few rows (decode): one CTA of 256 threads per row, row held in registers
+__global__ void __launch_bounds__(256)
+k_layer_norm_row(const char * __restrict__ x, const float * __restrict__ gamma, const float * __restrict__ beta, char * __restrict__ y,
+                 int ne00, int64_t xs, int64_t ys, float eps) {
+    __shared__ double red[8];
+    __shared__ float s_mean, s_scale;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const float * xp = (const float *) (x + (int64_t) blockIdx.x * xs);
+    float *       yp = (float *)       (y + (int64_t) blockIdx.x * ys);
+    float v[8];
+    double sum = 0.0;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int i = tid + u * 256;
+        v[u] = i < ne00 ? xp[i] : 0.0f;
+        if (i < ne00) sum += (double) v[u];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    if (tid == 0) {
+        double t = 0.0;
+        for (int w = 0; w < 8; ++w) t += red[w];
+        s_mean = (float) (t / (double) ne00);
+    }
+    __syncthreads();
+    const float mean = s_mean;
+    double sum2 = 0.0;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int i = tid + u * 256;
+        v[u] = __fadd_rn(v[u], -mean);
+        if (i < ne00) sum2 += (double) __fmul_rn(v[u], v[u]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum2 += __shfl_xor_sync(0xffffffffu, sum2, o);
+    if (lane == 0) red[warp] = sum2;
+    __syncthreads();
+    if (tid == 0) {
+        double t = 0.0;
+        for (int w = 0; w < 8; ++w) t += red[w];
+        const float variance = (float) (t / (double) ne00);
+        s_scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(variance, eps)));
+    }
+    __syncthreads();
+    const float scale = s_scale;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+        const int i = tid + u * 256;
+        if (i < ne00) yp[i] = __fadd_rn(__fmul_rn(__fmul_rn(v[u], scale), gamma[i]), beta[i]);
+    }
+}
+
 extern "C" int b200_layer_norm(const float * x, const float * gamma, const float * beta, float * y, int64_t ne00, int64_t nrows,
                                int64_t x_row_stride_bytes, int64_t y_row_stride_bytes, float eps, void * stream) {
     if (nrows <= 0 || ne00 <= 0) return 0;
+    if (nrows <= 64 && ne00 <= 2048) {
+        k_layer_norm_row<<<(unsigned) nrows, 256, 0, as_stream(stream)>>>((const char *) x, gamma, beta, (char *) y, (int) ne00,
+            x_row_stride_bytes, y_row_stride_bytes, eps);
+        B200_RETURN_LAST();
+    }
     k_layer_norm<<<(unsigned) ((nrows + 3) / 4), 128, 0, as_stream(stream)>>>((const char *) x, gamma, beta, (char *) y, ne00, nrows,
         x_row_stride_bytes, y_row_stride_bytes, eps);
     B200_RETURN_LAST();

@@ -346,51 +346,79 @@ k_mul_mat_vec_q(QPlanes w, int64_t M, int64_t nbk, const float * __restrict__ x,
     float * P   = sDw + 32;                                          // [N][PSTR]
     float * D   = P + N * PSTR;                                      // [N][32]
 
-    // quantise the activation columns (whole CTA)
-    for (int b = warp; b < N * (int) nbk; b += 4) {
-        const int n = b / (int) nbk, ib = b - n * (int) nbk;
-        const float v = *(const float *) ((const char *) x + (size_t) n * x_stride + (size_t) (ib * 32 + lane) * 4);
-        int8_t q; float dd;
-        quantize_block_q8_0(v, lane, q, dd);
-        ((int8_t *) Xq)[(size_t) n * K + ib * 32 + lane] = q;
-        if (lane == 0) Xd[n * nbk + ib] = dd;
+    // quantise the activation columns (whole CTA): every thread fetches float4 pieces up front (all loads in
+    // flight at once), eight consecutive lanes hold one 32-block and share its maximum by shuffles.
+    for (int n = 0; n < N; ++n) {
+        const float * xr = (const float *) ((const char *) x + (size_t) n * x_stride);
+        for (int base = 0; base < K; base += 128 * 4 * 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int e = base + (u * 128 + threadIdx.x) * 4;
+                v[u] = e < K ? *(const float4 *) (xr + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int e = base + (u * 128 + threadIdx.x) * 4;
+                float amax = fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w)));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                if (e < K) {
+                    const float id = (amax != 0.0f) ? __fdiv_rn(127.f, amax) : 0.0f;
+                    const int q0 = __float2int_rn(__fmul_rn(v[u].x, id)), q1 = __float2int_rn(__fmul_rn(v[u].y, id));
+                    const int q2 = __float2int_rn(__fmul_rn(v[u].z, id)), q3 = __float2int_rn(__fmul_rn(v[u].w, id));
+                    Xq[(size_t) n * (K / 4) + (e >> 2)] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
+                    if ((threadIdx.x & 7) == 0) Xd[n * nbk + (e >> 5)] = round_f16(__fdiv_rn(amax, 127.f));
+                }
+            }
+        }
     }
     __syncthreads();
 
     const int j = lane & 7, bsub = lane >> 3, cn = lane >> 3;
     const int64_t row0 = ((int64_t) blockIdx.x * 4 + warp) * rows_per_warp;
+    const int n_chunks = ((int) nbk + 31) / 32;
+    const int64_t rows_here = min((int64_t) rows_per_warp, M - row0);
 
-    for (int r = 0; r < rows_per_warp; ++r) {
+    // weight blocks are fetched one (row, chunk) ahead of the arithmetic
+    uint4 pa = make_uint4(0, 0, 0, 0), pb = make_uint4(0, 0, 0, 0);
+    uint32_t pqh = 0;
+    float pdw = 0.0f;
+    auto prefetch = [&](int64_t m, int c0) {
+        const int ib = c0 + lane;
+        pa = make_uint4(0, 0, 0, 0); pb = pa; pqh = 0; pdw = 0.0f;
+        if (ib < (int) nbk) {
+            const int64_t blk = m * nbk + ib;
+            if (TYPE == B200_TYPE_Q5_0) { pa = __ldg(((const uint4 *) w.qs) + blk); pqh = __ldg(w.qh + blk); }
+            else { pa = __ldg(((const uint4 *) w.qs) + blk * 2); pb = __ldg(((const uint4 *) w.qs) + blk * 2 + 1); }
+            pdw = __half2float(w.d[blk]);
+        }
+    };
+    if (rows_here > 0) prefetch(row0, 0);
+
+    for (int r = 0; r < rows_here; ++r) {
         const int64_t m = row0 + r;
-        if (m >= M) break;
         float acc0 = 0.0f, acc1 = 0.0f;
-        for (int c0 = 0; c0 < (int) nbk; c0 += 32) {
-            {   // each lane fetches one block of the row
-                const int ib = c0 + lane;
+        for (int c = 0; c < n_chunks; ++c) {
+            const int c0 = c * 32;
+            {   // publish the prefetched block of this lane, then start the next fetch
                 int wv[8];
-                float dw = 0.0f;
+                if (TYPE == B200_TYPE_Q5_0) {
+                    const uint32_t qw[4] = {pa.x, pa.y, pa.z, pa.w};
 #pragma unroll
-                for (int t = 0; t < 8; ++t) wv[t] = 0;
-                if (ib < (int) nbk) {
-                    const int64_t blk = m * nbk + ib;
-                    if (TYPE == B200_TYPE_Q5_0) {
-                        const uint4    q  = __ldg(((const uint4 *) w.qs) + blk);
-                        const uint32_t qh = __ldg(w.qh + blk);
-                        const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                        for (int t = 0; t < 8; ++t) wv[t] = q5_lane_word(qw[t & 3], qh, t);
-                    } else {
-                        const uint4 a = __ldg(((const uint4 *) w.qs) + blk * 2), b = __ldg(((const uint4 *) w.qs) + blk * 2 + 1);
-                        wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w;
-                        wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
-                    }
-                    dw = __half2float(w.d[blk]);
+                    for (int t = 0; t < 8; ++t) wv[t] = q5_lane_word(qw[t & 3], pqh, t);
+                } else {
+                    wv[0] = pa.x; wv[1] = pa.y; wv[2] = pa.z; wv[3] = pa.w;
+                    wv[4] = pb.x; wv[5] = pb.y; wv[6] = pb.z; wv[7] = pb.w;
                 }
                 *(int4 *) &sW[lane * 12]     = make_int4(wv[0], wv[1], wv[2], wv[3]);
                 *(int4 *) &sW[lane * 12 + 4] = make_int4(wv[4], wv[5], wv[6], wv[7]);
-                sDw[lane] = dw;
+                sDw[lane] = pdw;
             }
             __syncwarp();
+            if (c + 1 < n_chunks)       prefetch(m, c0 + 32);
+            else if (r + 1 < rows_here) prefetch(m + 1, 0);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const int ibl = i * 4 + bsub;
@@ -412,9 +440,11 @@ k_mul_mat_vec_q(QPlanes w, int64_t M, int64_t nbk, const float * __restrict__ x,
             __syncwarp();
             const int nblk = min(32, (int) nbk - c0);
             if (cn < N) {
+#pragma unroll 8
                 for (int ibl = 0; ibl < nblk; ++ibl) acc0 = __fmaf_rn(D[cn * 32 + ibl], P[cn * PSTR + ibl * 8 + j], acc0);
             }
             if (N > 4 && cn + 4 < N) {
+#pragma unroll 8
                 for (int ibl = 0; ibl < nblk; ++ibl) acc1 = __fmaf_rn(D[(cn + 4) * 32 + ibl], P[(cn + 4) * PSTR + ibl * 8 + j], acc1);
             }
             __syncwarp();
