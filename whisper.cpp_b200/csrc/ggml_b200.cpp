@@ -675,7 +675,7 @@ static bool b200_op_supported(const struct ggml_tensor * op) {
             if (is_quant(s0->type)) {
                 return s0->view_src == nullptr && ggml_is_contiguous(s0) && s0->ne[2] == 1 && s0->ne[3] == 1 &&
                        s1->type == GGML_TYPE_F32 && s1->nb[0] == 4 && s1->ne[2] == 1 && s1->ne[3] == 1 &&
-                       s1->ne[0] % 32 == 0 && (s1->nb[1] % 4) == 0;
+                       s1->ne[0] % 32 == 0 && (s1->nb[1] % 16) == 0;
             }
             if (s0->type == GGML_TYPE_F16) {
                 return s0->nb[0] == 2 && ((s1->type == GGML_TYPE_F32 && s1->nb[0] == 4) || (s1->type == GGML_TYPE_F16 && s1->nb[0] == 2)) &&

@@ -309,7 +309,7 @@ k_flash_attn_decode(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
     // while warps 0..1 (one thread per output dim) replay the F16 accumulation over chunk c and one thread of
     // warp 2 replays the running sum.
     {
-        __half * Vs = (__half *) (msv + n_kv);                       // [2][FA_DEC_CHUNK][64]
+        __half * Vs = (__half *) (fa_smem + ((64 + 2 * n_kv + 3) & ~3));   // [2][FA_DEC_CHUNK][64], 16-byte aligned
         const int n_chunks = (n_kv + FA_DEC_CHUNK - 1) / FA_DEC_CHUNK;
         auto fetch = [&](int c) {
             const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
@@ -367,13 +367,13 @@ extern "C" int b200_flash_attn_ext(const float * q, int64_t nbq1, int64_t nbq2,
     ensure_exp_table();
     if (n_q <= 16 && n_kv <= FA_DEC_MAX_KV && !((uintptr_t) v & 15) && !(nbv1 & 15) && !(nbv2 & 15)) {
         dim3 dgrid((unsigned) n_q, (unsigned) n_head);
-        const size_t smem = (64 + 2 * (size_t) n_kv) * sizeof(float) + 2 * FA_DEC_CHUNK * 64 * sizeof(__half);
+        const size_t smem = (size_t) ((64 + 2 * n_kv + 3) & ~(int64_t) 3) * sizeof(float) + 2 * FA_DEC_CHUNK * 64 * sizeof(__half);
         static bool attr_done[64] = {false};
         int dev = 0;
         cudaGetDevice(&dev);
         if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-            cudaFuncSetAttribute(k_flash_attn_decode<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (64 + 2 * FA_DEC_MAX_KV) * 4 + 2 * FA_DEC_CHUNK * 64 * 2);
-            cudaFuncSetAttribute(k_flash_attn_decode<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (64 + 2 * FA_DEC_MAX_KV) * 4 + 2 * FA_DEC_CHUNK * 64 * 2);
+            cudaFuncSetAttribute(k_flash_attn_decode<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (64 + 2 * FA_DEC_MAX_KV + 4) * 4 + 2 * FA_DEC_CHUNK * 64 * 2);
+            cudaFuncSetAttribute(k_flash_attn_decode<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (64 + 2 * FA_DEC_MAX_KV + 4) * 4 + 2 * FA_DEC_CHUNK * 64 * 2);
             attr_done[dev] = true;
         }
         if (g_fa_s_fma)

@@ -338,7 +338,7 @@ k_mul_mat_vec_q(QPlanes w, int64_t M, int64_t nbk, const float * __restrict__ x,
     const int K = (int) nbk * 32;
     int *   Xq = (int *) smem_raw;                                   // [N][K/4]
     float * Xd = (float *) (Xq + (size_t) N * (K / 4));              // [N][nbk]
-    unsigned char * wbase = (unsigned char *) (Xd + (size_t) N * nbk);
+    unsigned char * wbase = smem_raw + (((size_t) N * K + (size_t) N * nbk * 4 + 15) & ~(size_t) 15);   // 16-byte aligned
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int WARP_BYTES = (32 * 12 + 32 + N * PSTR + N * 32) * 4;
     int *   sW  = (int *) (wbase + (size_t) warp * WARP_BYTES);      // [32][12] (8 used)
@@ -464,7 +464,7 @@ k_mul_mat_vec_q(QPlanes w, int64_t M, int64_t nbk, const float * __restrict__ x,
 template <int TYPE, int N>
 static int launch_vec(const QPlanes & w, int64_t M, int64_t nbk, const float * x, int64_t xs, void * dst, int64_t ldd, const EpDev & ep, cudaStream_t st) {
     constexpr int PSTR = 32 * 8 + 8;
-    const size_t smem = (size_t) N * nbk * 32 + (size_t) N * nbk * 4 + 4 * (size_t) ((32 * 12 + 32 + N * PSTR + N * 32) * 4);
+    const size_t smem = (((size_t) N * nbk * 32 + (size_t) N * nbk * 4 + 15) & ~(size_t) 15) + 4 * (size_t) ((32 * 12 + 32 + N * PSTR + N * 32) * 4);
     static bool attr_done[64] = {false};   // per instantiation and device; benign race (idempotent call)
     int dev = 0;
     cudaGetDevice(&dev);
@@ -502,7 +502,7 @@ extern "C" int b200_mul_mat_vec_q_ep(int wtype, const void * w_planes, int64_t n
                                      const float * x, int64_t x_stride_bytes, int64_t N,
                                      void * dst, int64_t dst_stride, const b200_epilogue * ep, void * stream) {
     if (K % 32 != 0 || M <= 0 || N < 1 || N > 8) return B200_ERR_ARG;
-    if (((uintptr_t) w_planes & 15) != 0) return B200_ERR_ARG;
+    if (((uintptr_t) w_planes & 15) != 0 || ((uintptr_t) x & 15) != 0 || (x_stride_bytes & 15) != 0) return B200_ERR_ARG;
     const int64_t nbk = K / 32;
     if (M * nbk > nb_total) return B200_ERR_ARG;
     EpDev e;
