@@ -14,6 +14,7 @@
 #include <cuda_runtime.h>
 
 #include <atomic>
+#include <chrono>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -39,6 +40,9 @@ static std::atomic<int64_t> g_nodes_computed{0};    // non-view nodes executed b
 static std::atomic<int64_t> g_graphs_computed{0};
 static std::atomic<int64_t> g_h2d_bytes{0};
 static std::atomic<int64_t> g_d2h_bytes{0};
+static std::atomic<int64_t> g_host_ns_compute{0};   // host time inside graph_compute (launching)
+static std::atomic<int64_t> g_host_ns_sync{0};      // host time waiting in synchronize
+static inline int64_t now_ns() { return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::steady_clock::now().time_since_epoch()).count(); }
 
 // Optional per-operator timing (off by default): CUDA events recorded on the backend's own stream
 // around every launch group, summed per class after the graph finishes.  Used by the benchmark for
@@ -69,6 +73,8 @@ int64_t b200_stat_nodes(void)   { return g_nodes_computed.load(); }
 int64_t b200_stat_graphs(void)  { return g_graphs_computed.load(); }
 int64_t b200_stat_h2d(void)     { return g_h2d_bytes.load(); }
 int64_t b200_stat_d2h(void)     { return g_d2h_bytes.load(); }
+int64_t b200_stat_host_ns_compute(void) { return g_host_ns_compute.load(); }
+int64_t b200_stat_host_ns_sync(void)    { return g_host_ns_sync.load(); }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -264,7 +270,9 @@ static void b200_backend_free(ggml_backend_t backend) {
 static void b200_backend_synchronize(ggml_backend_t backend) {
     b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
     cudaSetDevice(ctx->device);
+    const int64_t t0 = now_ns();
     cuda_ok(cudaStreamSynchronize(ctx->stream), "synchronize");
+    g_host_ns_sync += now_ns() - t0;
 }
 
 static bool ensure_scratch(b200_backend_ctx * ctx, size_t size) {
@@ -517,6 +525,7 @@ static int node_class(const struct ggml_tensor * node, double * work) {
 static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struct ggml_cgraph * cgraph) {
     b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
     if (cudaSetDevice(ctx->device) != cudaSuccess) return GGML_STATUS_FAILED;
+    const int64_t t_enter = now_ns();
     const int n_nodes = ggml_graph_n_nodes(cgraph);
     int64_t done = 0;
     const bool timing = g_timing_on.load() != 0;
@@ -593,6 +602,7 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
     }
     g_nodes_computed += done;
     g_graphs_computed += 1;
+    g_host_ns_compute += now_ns() - t_enter;
     if (timing && !t_class.empty()) {
         if (!cuda_ok(cudaStreamSynchronize(ctx->stream), "timing sync")) return GGML_STATUS_FAILED;
         std::lock_guard<std::mutex> lk(g_timing_mu);
@@ -784,6 +794,8 @@ static void * b200_reg_get_proc_address(ggml_backend_reg_t, const char * name) {
     if (strcmp(name, "b200_stat_graphs") == 0) return (void *) b200_stat_graphs;
     if (strcmp(name, "b200_stat_h2d") == 0)    return (void *) b200_stat_h2d;
     if (strcmp(name, "b200_stat_d2h") == 0)    return (void *) b200_stat_d2h;
+    if (strcmp(name, "b200_stat_host_ns_compute") == 0) return (void *) b200_stat_host_ns_compute;
+    if (strcmp(name, "b200_stat_host_ns_sync") == 0)    return (void *) b200_stat_host_ns_sync;
     if (strcmp(name, "b200_launch_count") == 0) return (void *) b200_launch_count;
     if (strcmp(name, "b200_timing_enable") == 0)  return (void *) b200_timing_enable;
     if (strcmp(name, "b200_timing_reset") == 0)   return (void *) b200_timing_reset;
