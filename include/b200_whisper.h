@@ -92,6 +92,27 @@ int b200_mul_mat_vec_q_ep(int wtype, const void * w_planes, int64_t nb_total, in
 int b200_layer_norm(const float * x, const float * gamma, const float * beta, float * y, int64_t ne00, int64_t nrows,
                     int64_t x_row_stride_bytes, int64_t y_row_stride_bytes, float eps, void * stream);
 
+/* No counterpart in the reference.  b200_mul_mat_q needs the activations quantised into scratch memory that
+ * the caller allocates.  Some callers cannot allocate device memory at the point where they need a product:
+ * code that runs inside another framework's memory plan (all device memory handed out up front), hosts that
+ * forbid the implicit device-wide synchronisation of cudaMalloc/cudaFree on a latency-critical path, or a
+ * plugin callback that is only given input and output pointers.  For them this entry point does the same
+ * work - quantise N rows of f32 activations (row stride in bytes), then the Q5_0/Q8_0 product - with the
+ * scratch held in a fixed device array that is part of this library's image (b200_static_scratch_bytes()
+ * bytes, resident on every GPU that loads the library until the process exits).  It calls no allocator.
+ *  - N*K + 4*N*K/32 bytes (plus padding to 256) must fit; otherwise B200_ERR_TOO_LARGE is returned and nothing
+ *    is launched.
+ *  - The first call on each device looks up the array's device address (with that device current); make that
+ *    first call outside any stream capture.
+ *  - All calls share the one array and it keeps the previous call's contents.  Every byte a call reads is
+ *    written by that same call first, so nothing needs clearing, but two calls that may overlap on the GPU
+ *    (different streams, no ordering between them) race on it. */
+#define B200_ERR_TOO_LARGE 10003
+int64_t b200_static_scratch_bytes(void);
+int b200_mul_mat_q_static(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                          const float * x, int64_t x_stride_bytes, int64_t N,
+                          float * dst, int64_t dst_stride, void * stream);
+
 /* mul_mat with F16 src0 (ggml_vec_dot_f16, ggml/src/ggml-cpu/vec.cpp:128-167): src1 is f32 (rounded
  * to f16 first, ggml-cpu.c:1329-1362) or f16.  Strides in bytes; src0 [K, M, ne02, ne03],
  * src1 [K, N, ne12, ne13] with ne12 % ne02 == 0, dst f32 contiguous [M, N, ne12, ne13]. */

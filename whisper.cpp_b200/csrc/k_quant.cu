@@ -5,6 +5,7 @@
 // (ggml/src/ggml-cpu/ggml-cpu-quants.c:49-55, 3076-3100, 3869-3886).
 #include "b200_common.cuh"
 #include <string.h>
+#include <stdio.h>
 
 std::atomic<int64_t> g_b200_launches{0};
 
@@ -530,4 +531,54 @@ extern "C" int b200_mul_mat_vec_q(int wtype, const void * w_planes, int64_t nb_t
                                   const float * x, int64_t x_stride_bytes, int64_t N,
                                   float * dst, int64_t dst_stride, void * stream) {
     return b200_mul_mat_vec_q_ep(wtype, w_planes, nb_total, M, K, x, x_stride_bytes, N, dst, dst_stride, nullptr, stream);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Product with the activation scratch in a fixed device array (for callers that cannot allocate).
+// ------------------------------------------------------------------------------------------------
+#define B200_STATIC_SCRATCH_BYTES (9 * 1024 * 1024)
+static __device__ __align__(256) unsigned char g_static_scratch[B200_STATIC_SCRATCH_BYTES];
+
+extern "C" int64_t b200_static_scratch_bytes(void) { return B200_STATIC_SCRATCH_BYTES; }
+
+// In host code the array's name is only a handle for the runtime, not a device address: the address each
+// device gave its copy is asked for once per device, with that device current.
+static int static_scratch_address(unsigned char ** out) {
+    static std::atomic<unsigned char *> addr[64];
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int) e;
+    if (dev < 0 || dev >= 64) return B200_ERR_ARG;
+    unsigned char * p = addr[dev].load(std::memory_order_acquire);
+    if (!p) {
+        void * sym = nullptr;
+        e = cudaGetSymbolAddress(&sym, g_static_scratch);
+        if (e != cudaSuccess) return (int) e;
+        p = (unsigned char *) sym;
+        addr[dev].store(p, std::memory_order_release);      // same value from every thread that races here
+    }
+    *out = p;
+    return 0;
+}
+
+extern "C" int b200_mul_mat_q_static(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                                     const float * x, int64_t x_stride_bytes, int64_t N,
+                                     float * dst, int64_t dst_stride, void * stream) {
+    if (K % 32 != 0 || M <= 0 || N <= 0 || K <= 0) return B200_ERR_ARG;
+    if (wtype != B200_TYPE_Q5_0 && wtype != B200_TYPE_Q8_0) return B200_ERR_ARG;
+    const int64_t q_bytes = N * K, d_bytes = N * (K / 32) * 4;
+    const int64_t q_pad = (q_bytes + 255) & ~(int64_t) 255;
+    if (q_pad + d_bytes > B200_STATIC_SCRATCH_BYTES) {
+        fprintf(stderr, "b200_mul_mat_q_static: %lld activation rows of %lld values need %lld bytes of scratch, the fixed array holds %d\n",
+                (long long) N, (long long) K, (long long) (q_pad + d_bytes), B200_STATIC_SCRATCH_BYTES);
+        return B200_ERR_TOO_LARGE;
+    }
+    unsigned char * scratch = nullptr;
+    int e = static_scratch_address(&scratch);
+    if (e) return e;
+    int8_t * xq = (int8_t *) scratch;
+    float *  xd = (float *) (scratch + q_pad);
+    e = b200_quantize_q8_0(x, N, K, x_stride_bytes, xq, xd, stream);
+    if (e) return e;
+    return b200_mul_mat_q(wtype, w_planes, nb_total, M, K, xq, xd, N, dst, dst_stride, stream);
 }
