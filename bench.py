@@ -149,8 +149,11 @@ def main():
     ap.add_argument("--wtype", default="q5_0")
     ap.add_argument("--clips", type=int, default=TOTAL_CLIPS, help="clips in the whole batch (all ranks)")
     ap.add_argument("--states", type=int, default=0, help="whisper_states (host threads / streams) per GPU; 0 = auto")
+    ap.add_argument("--n-new", type=int, default=N_NEW, help="greedy tokens per clip (224 = the benchmark workload; smaller only for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
+    global N_NEW
+    N_NEW = args.n_new
     pkg = load_pkg()
 
     if args.impl == "reference":
