@@ -140,6 +140,7 @@ def run_reference(args, pkg):
 
 
 def main():
+    global N_NEW
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
@@ -152,7 +153,6 @@ def main():
     ap.add_argument("--n-new", type=int, default=N_NEW, help="greedy tokens per clip (224 = the benchmark workload; smaller only for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    global N_NEW
     N_NEW = args.n_new
     pkg = load_pkg()
 
