@@ -87,6 +87,15 @@ int b200_mul_mat_vec_q_ep(int wtype, const void * w_planes, int64_t nb_total, in
                           const float * x, int64_t x_stride_bytes, int64_t N,
                           void * dst, int64_t dst_stride, const b200_epilogue * ep, void * stream);
 
+/* The same kernel with every column described on its own: column n reads x (K floats, 16-byte aligned), writes
+ * dst (M f32, or M f16 when store_f16) and adds add[s] (M floats) at epilogue step s when kind[s] == B200_EP_ADD.
+ * This is how single-token decode steps of several whisper_states that run in lock-step share one pass over
+ * the weights (up to 8 columns per launch).  No counterpart in the reference, which decodes state by state. */
+typedef struct { const float * x; void * dst; const float * add[4]; } b200_gemv_col;
+typedef struct { int n_steps; int kind[4]; float scalar[4]; int store_f16; } b200_gemv_ep;
+int b200_mul_mat_vec_q_cols(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                            const b200_gemv_col * cols, int n_cols, const b200_gemv_ep * ep, void * stream);
+
 /* NORM -> MUL(gamma) -> ADD(beta) in one pass (ops.cpp:3109-3158 followed by binary-ops.cpp:50-137), each of the
  * three roundings kept: y = ((x - mean) * rstd) * gamma + beta. */
 int b200_layer_norm(const float * x, const float * gamma, const float * beta, float * y, int64_t ne00, int64_t nrows,
@@ -130,9 +139,20 @@ int b200_flash_attn_ext(const float * q, int64_t nbq1, int64_t nbq2,
                         const void * mask, int64_t nbm1,
                         float * dst, int64_t n_q, int64_t n_kv, int64_t n_head, float scale, void * stream);
 
+/* The decode-shaped form of the above, one entry per query row (at most 32): each row has its own query, K/V
+ * views, mask row, output and key count, so rows of different whisper_states (different KV caches, different
+ * lengths) go out in one launch.  dst receives [n_head][64] f32 per row.  No counterpart in the reference. */
+typedef struct { const float * q; const void * k; const void * v; const void * mask; float * dst; int64_t n_kv; } b200_fa_row;
+int b200_flash_attn_decode_rows(const b200_fa_row * rows, int n_rows, int64_t n_head, int64_t nbq2, int64_t nbk1, int64_t nbk2,
+                                int64_t nbv1, int64_t nbv2, float scale, void * stream);
+
 /* ggml_compute_forward_norm_f32 (ops.cpp:3109-3158): rows of ne00 f32, row strides in bytes. */
 int b200_norm(const float * x, float * y, int64_t ne00, int64_t ne01, int64_t ne02, int64_t ne03,
               const int64_t * nbx, const int64_t * nby, float eps, void * stream);
+
+/* b200_layer_norm for rows that live at unrelated addresses (at most 64; rows of several decoder states). */
+typedef struct { const float * x; float * y; } b200_ln_row;
+int b200_layer_norm_rows(const b200_ln_row * rows, int n_rows, const float * gamma, const float * beta, int64_t ne00, float eps, void * stream);
 
 /* ADD (op 0) / MUL (op 1) with ggml broadcasting of src1 (ggml/src/ggml-cpu/binary-ops.cpp:50-137). */
 int b200_binary(int op, const float * a, const int64_t * nea, const int64_t * nba,

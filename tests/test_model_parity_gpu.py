@@ -79,3 +79,23 @@ def test_tiny_no_flash(pkg, model_dir, wtype):
 
 def test_base_q5_0_flash(pkg, model_dir):
     check(run_pair(pkg, model_dir, "base", "q5_0", True, n_new=16), "base q5_0 flash_attn")
+
+
+def test_concurrent_states_are_batched_and_match_the_oracle(pkg, model_dir):
+    """Several whisper_states decode at once; their steps are merged below graph_compute.  Every clip must still get
+    exactly the token ids the reference CPU backend produces for it alone."""
+    from whisper_cpp_b200.host import backend_stat
+    path = os.path.join(model_dir, "tiny-q5_0.bin")
+    if not os.path.exists(path):
+        pkg.synth.write_model(path, "tiny", "q5_0", seed=0)
+    pcm = np.stack([pkg.synth.pcm_f32(pkg.synth.make_clip(40 + i)) for i in range(6)])
+    cpu = pkg.Whisper(path, use_gpu=False, flash_attn=True)
+    want, _ = cpu.greedy_batch(24, pcm=pcm, device_mel=False)
+    cpu.close()
+    gpu = pkg.Whisper(path, use_gpu=True, flash_attn=True, n_states=6, threads=1)
+    b0, g0 = backend_stat("b200_stat_batches"), backend_stat("b200_stat_batched_graphs")
+    got, _ = gpu.greedy_batch(24, pcm=pcm, device_mel=True)
+    b1, g1 = backend_stat("b200_stat_batches"), backend_stat("b200_stat_batched_graphs")
+    gpu.close()
+    assert np.array_equal(got, want), f"token ids differ under batching:\n{got}\n{want}"
+    assert g1 - g0 > b1 - b0 > 0, f"no decode steps were merged (batches {b1 - b0}, graphs {g1 - g0})"

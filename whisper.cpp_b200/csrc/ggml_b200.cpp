@@ -18,6 +18,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <condition_variable>
 #include <mutex>
 #include <string>
 #include <unordered_map>
@@ -47,9 +48,9 @@ static inline int64_t now_ns() { return std::chrono::duration_cast<std::chrono::
 // Optional per-operator timing (off by default): CUDA events recorded on the backend's own stream
 // around every launch group, summed per class after the graph finishes.  Used by the benchmark for
 // its roofline line; the extra event records and the sync make it unsuitable for throughput runs.
-enum b200_timing_class { TC_MMQ_VEC = 0, TC_MMQ_GEMM, TC_MM_F16, TC_FATTN, TC_NORM, TC_BINARY, TC_SCALE, TC_GELU, TC_CPY,
+enum b200_timing_class { TC_MMQ_VEC = 0, TC_MMQ_GEMM, TC_MM_F16, TC_FATTN, TC_FATTN_DEC, TC_NORM, TC_BINARY, TC_SCALE, TC_GELU, TC_CPY,
                          TC_GET_ROWS, TC_IM2COL, TC_SOFT_MAX, TC_CONCAT, TC_COUNT };
-static const char * const g_tc_names[TC_COUNT] = { "mul_mat_vec_q", "mul_mat_q", "mul_mat_f16", "flash_attn_ext", "norm", "binary",
+static const char * const g_tc_names[TC_COUNT] = { "mul_mat_vec_q", "mul_mat_q", "mul_mat_f16", "flash_attn_ext", "flash_attn_decode", "norm", "binary",
                                                    "scale", "gelu", "cpy", "get_rows", "im2col", "soft_max", "concat" };
 static std::atomic<int> g_timing_on{0};
 static std::mutex       g_timing_mu;
@@ -250,7 +251,11 @@ struct b200_backend_ctx {
     size_t       scratch_size = 0;
     std::string  name;
     std::vector<cudaEvent_t> events;       // timing mode only
+    std::atomic<int64_t> last_decode_ns{0};   // when this instance last submitted a decode-step graph
 };
+
+static void batcher_join(b200_backend_ctx * ctx);
+static void batcher_leave(b200_backend_ctx * ctx);
 
 static const char * b200_backend_get_name(ggml_backend_t backend) {
     return ((b200_backend_ctx *) backend->context)->name.c_str();
@@ -258,6 +263,7 @@ static const char * b200_backend_get_name(ggml_backend_t backend) {
 
 static void b200_backend_free(ggml_backend_t backend) {
     b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
+    batcher_leave(ctx);
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
@@ -379,9 +385,15 @@ static int compute_node(b200_backend_ctx * ctx, struct ggml_tensor * node) {
 }
 
 // ---------------------------------------------------------------------------------------------
-// node-sequence fusion.  A fused launch evaluates the same single-precision operations in the same
-// order as the node sequence it replaces, so the bits that reach memory do not change; what goes
-// away is the round trip of the intermediate through HBM and the extra launches.
+// Execution plan.  A graph is turned into a list of launch items; an item is either one node or a fused
+// node sequence (NORM->MUL->ADD, MUL_MAT(<= 8 columns)->ADD/SCALE/GELU/CPY).  A fused launch evaluates the
+// same single-precision operations in the same order as the nodes it replaces, so the bits that reach
+// memory do not change; what goes away is the round trip of the intermediates through HBM and the launches.
+//
+// Items refer to nodes by position, so one plan serves every graph with the same structure: the decode
+// graphs of several whisper_states differ only in addresses and in the number of cached keys.  That is what
+// the batcher below uses to run their steps together - one pass over the weights for up to 8 states per
+// launch, one launch of the attention / LayerNorm kernels for all of them.
 // ---------------------------------------------------------------------------------------------
 struct graph_info {
     std::unordered_map<const struct ggml_tensor *, int> index;   // node -> position
@@ -427,69 +439,163 @@ static bool only_feeds(const graph_info & gi, const struct ggml_tensor * t, int 
     return gi.uses[pos] == 1 && !(t->flags & GGML_TENSOR_FLAG_OUTPUT);
 }
 
-// NORM -> MUL(gamma) -> ADD(beta) starting at node i; returns the index of the ADD node or -1
-static int match_layer_norm(struct ggml_cgraph * g, const graph_info & gi, int i, const struct ggml_tensor ** gamma, const struct ggml_tensor ** beta) {
-    const int n = ggml_graph_n_nodes(g);
-    struct ggml_tensor * nrm = ggml_graph_node(g, i);
-    if (i + 2 >= n || !only_feeds(gi, nrm, i)) return -1;
-    struct ggml_tensor * mul = ggml_graph_node(g, i + 1);
-    struct ggml_tensor * add = ggml_graph_node(g, i + 2);
-    if (mul->op != GGML_OP_MUL || add->op != GGML_OP_ADD || mul->src[0] != nrm || add->src[0] != mul || !only_feeds(gi, mul, i + 1)) return -1;
-    const struct ggml_tensor * ga = mul->src[1], * be = add->src[1], * x = nrm->src[0];
-    auto vec_ok = [&](const struct ggml_tensor * v) {
-        return v->type == GGML_TYPE_F32 && v->ne[0] == x->ne[0] && v->ne[1] == 1 && v->ne[2] == 1 && v->ne[3] == 1 && v->nb[0] == 4;
-    };
-    if (!vec_ok(ga) || !vec_ok(be) || !ready_before(gi, ga, i) || !ready_before(gi, be, i)) return -1;
-    if (x->ne[2] != 1 || x->ne[3] != 1 || x->nb[0] != 4 || add->nb[0] != 4 || !ggml_are_same_shape(x, add)) return -1;
-    *gamma = ga; *beta = be;
-    return i + 2;
+enum plan_kind { PK_NODE = 0, PK_LAYER_NORM, PK_GEMV, PK_FA_DECODE };
+
+struct plan_item {
+    int kind;
+    int node;           // NORM / MUL_MAT / FLASH_ATTN_EXT / generic node
+    int last;           // node whose memory receives the result (== node when nothing is fused)
+    // PK_GEMV epilogue
+    int n_steps;
+    int step_kind[4];
+    int step_node[4];   // the ADD / SCALE / UNARY node of the step
+    int step_src[4];    // ADD: which src of that node is the added operand
+    int store_f16;
+};
+
+struct exec_plan {
+    std::vector<plan_item> items;
+    int n_nodes = 0;
+};
+
+static bool is_decode_attention(const struct ggml_tensor * node) {
+    return node->op == GGML_OP_FLASH_ATTN_EXT && node->src[0]->ne[1] <= 8;
 }
 
-// MUL_MAT (quantised weights, <= 8 columns) followed by ADD / SCALE / GELU nodes and an optional F32->F16 CPY.
-// Fills ep, *last = index of the last fused node, *out = tensor whose memory receives the result.
-static void match_vec_epilogue(struct ggml_cgraph * g, const graph_info & gi, int i, b200_epilogue * ep, int * last, struct ggml_tensor ** out,
-                               std::vector<char> & fused, const struct ggml_tensor ** operands) {
+static void build_plan(struct ggml_cgraph * g, exec_plan & plan, bool fuse) {
     const int n = ggml_graph_n_nodes(g);
-    struct ggml_tensor * cur = ggml_graph_node(g, i);
-    const int64_t M = cur->ne[0], N = cur->ne[1];
-    int cur_pos = i;
-    ep->n_steps = 0; ep->store_f16 = 0;
-    *last = i; *out = cur;
-    for (int j = i + 1; j < n && ep->n_steps < 4; ++j) {
-        struct ggml_tensor * t = ggml_graph_node(g, j);
-        if (is_view_op(t->op)) {
-            if (t->src[0] == cur || t->view_src == cur) break;      // someone looks at cur itself
-            continue;
+    plan.items.clear();
+    plan.n_nodes = n;
+    graph_info gi;
+    if (fuse) analyse_graph(g, gi);
+    std::vector<char> fused(n, 0);
+    for (int i = 0; i < n; ++i) {
+        struct ggml_tensor * node = ggml_graph_node(g, i);
+        if (is_view_op(node->op) || ggml_is_empty(node) || fused[i]) continue;
+        plan_item it;
+        memset(&it, 0, sizeof(it));
+        it.kind = PK_NODE; it.node = i; it.last = i;
+        if (fuse && node->op == GGML_OP_NORM && i + 2 < n && only_feeds(gi, node, i)) {
+            struct ggml_tensor * mul = ggml_graph_node(g, i + 1);
+            struct ggml_tensor * add = ggml_graph_node(g, i + 2);
+            const struct ggml_tensor * x = node->src[0];
+            auto vec_ok = [&](const struct ggml_tensor * v) {
+                return v->type == GGML_TYPE_F32 && v->ne[0] == x->ne[0] && v->ne[1] == 1 && v->ne[2] == 1 && v->ne[3] == 1 && v->nb[0] == 4;
+            };
+            if (mul->op == GGML_OP_MUL && add->op == GGML_OP_ADD && mul->src[0] == node && add->src[0] == mul && only_feeds(gi, mul, i + 1) &&
+                vec_ok(mul->src[1]) && vec_ok(add->src[1]) && ready_before(gi, mul->src[1], i) && ready_before(gi, add->src[1], i) &&
+                x->type == GGML_TYPE_F32 && x->ne[2] == 1 && x->ne[3] == 1 && x->nb[0] == 4 && add->nb[0] == 4 && ggml_are_same_shape(x, add)) {
+                it.kind = PK_LAYER_NORM; it.last = i + 2;
+                fused[i + 1] = 1; fused[i + 2] = 1;
+            }
+        } else if (node->op == GGML_OP_MUL_MAT && is_quant(node->src[0]->type) && node->src[1]->ne[1] <= 8) {
+            it.kind = PK_GEMV;
+            if (fuse) {
+                struct ggml_tensor * cur = node;
+                const int64_t M = node->ne[0], N = node->ne[1];
+                int cur_pos = i;
+                for (int j = i + 1; j < n && it.n_steps < 4; ++j) {
+                    struct ggml_tensor * t = ggml_graph_node(g, j);
+                    if (is_view_op(t->op)) {
+                        if (t->src[0] == cur || t->view_src == cur) break;      // someone looks at cur itself
+                        continue;
+                    }
+                    if (!only_feeds(gi, cur, cur_pos)) break;
+                    int kind = 0, src = 0;
+                    if (t->op == GGML_OP_ADD && (t->src[0] == cur || t->src[1] == cur) && t->type == GGML_TYPE_F32) {
+                        src = t->src[0] == cur ? 1 : 0;
+                        const struct ggml_tensor * o = t->src[src];
+                        if (o == cur || o->type != GGML_TYPE_F32 || o->nb[0] != 4 || o->ne[0] != M || o->ne[2] != 1 || o->ne[3] != 1) break;
+                        if (o->ne[1] != 1 && o->ne[1] != N) break;
+                        if (!ggml_are_same_shape(t, cur) || !ready_before(gi, o, i)) break;
+                        kind = B200_EP_ADD;
+                    } else if (t->op == GGML_OP_SCALE && t->src[0] == cur) {
+                        kind = B200_EP_SCALE;
+                    } else if (t->op == GGML_OP_UNARY && t->src[0] == cur && ggml_get_unary_op(t) == GGML_UNARY_OP_GELU) {
+                        kind = B200_EP_GELU;
+                    } else if (t->op == GGML_OP_CPY && t->src[0] == cur && t->type == GGML_TYPE_F16 && ggml_is_contiguous(t) &&
+                               ggml_nelements(t) == M * N && ggml_is_contiguous(cur)) {
+                        it.store_f16 = 1;
+                        fused[j] = 1;
+                        it.last = j;
+                        break;
+                    } else {
+                        break;
+                    }
+                    if (t->nb[0] != 4) break;
+                    it.step_kind[it.n_steps] = kind; it.step_node[it.n_steps] = j; it.step_src[it.n_steps] = src;
+                    it.n_steps++;
+                    fused[j] = 1;
+                    cur = t; cur_pos = j;
+                    it.last = j;
+                }
+            }
+        } else if (is_decode_attention(node)) {
+            it.kind = PK_FA_DECODE;
         }
-        if (!only_feeds(gi, cur, cur_pos)) break;
-        b200_ep_step st = {0, nullptr, 0, 0.0f};
-        if (t->op == GGML_OP_ADD && (t->src[0] == cur || t->src[1] == cur) && t->type == GGML_TYPE_F32) {
-            const struct ggml_tensor * o = t->src[0] == cur ? t->src[1] : t->src[0];
-            if (o == cur || o->type != GGML_TYPE_F32 || o->nb[0] != 4 || o->ne[0] != M || o->ne[2] != 1 || o->ne[3] != 1) break;
-            if (o->ne[1] != 1 && o->ne[1] != N) break;
-            if (!ggml_are_same_shape(t, cur) || !ready_before(gi, o, i)) break;
-            st.kind = B200_EP_ADD; st.ptr = (const float *) o->data; st.stride_n = (o->ne[1] == 1) ? 0 : (int64_t) o->nb[1] / 4;
-            operands[ep->n_steps] = o;
-        } else if (t->op == GGML_OP_SCALE && t->src[0] == cur) {
-            st.kind = B200_EP_SCALE;
-            memcpy(&st.scalar, t->op_params, sizeof(float));
-        } else if (t->op == GGML_OP_UNARY && t->src[0] == cur && ggml_get_unary_op(t) == GGML_UNARY_OP_GELU) {
-            st.kind = B200_EP_GELU;
-        } else if (t->op == GGML_OP_CPY && t->src[0] == cur && t->type == GGML_TYPE_F16 && ggml_is_contiguous(t) &&
-                   ggml_nelements(t) == M * N && ggml_is_contiguous(cur)) {
-            ep->store_f16 = 1;
-            fused[j] = 1;
-            *last = j; *out = t;
-            return;
-        } else {
-            break;
-        }
-        if (t->nb[0] != 4) break;
-        ep->step[ep->n_steps++] = st;
-        fused[j] = 1;
-        cur = t; cur_pos = j;
-        *last = j; *out = t;
+        plan.items.push_back(it);
     }
+}
+
+// Structure signature of a graph: operator, type and shape of every computing node, except the extents that only
+// depend on how many keys are cached (attention inputs, the mask copy).  Equal signature = same plan applies.
+static uint64_t graph_signature(struct ggml_cgraph * g) {
+    uint64_t h = 1469598103934665603ull;
+    auto mix = [&](uint64_t v) { h ^= v; h *= 1099511628211ull; };
+    const int n = ggml_graph_n_nodes(g);
+    mix((uint64_t) n);
+    for (int i = 0; i < n; ++i) {
+        const struct ggml_tensor * t = ggml_graph_node(g, i);
+        mix((uint64_t) t->op * 131 + (uint64_t) t->type);
+        if (is_view_op(t->op)) continue;
+        if (t->op == GGML_OP_CPY) { mix((uint64_t) t->src[0]->type); continue; }
+        mix((uint64_t) t->ne[0]); mix((uint64_t) t->ne[1]); mix((uint64_t) t->ne[2]);
+        if (t->src[0]) { mix((uint64_t) t->src[0]->type); mix((uint64_t) t->src[0]->ne[0]); }
+        if (t->src[1] && t->op != GGML_OP_FLASH_ATTN_EXT) { mix((uint64_t) t->src[1]->type); mix((uint64_t) t->src[1]->ne[0]); mix((uint64_t) t->src[1]->ne[1]); }
+    }
+    return h;
+}
+
+// Does graph g satisfy what the plan assumes (operators in place, supported, no aliasing hazard for fused items)?
+static bool graph_fits_plan(const exec_plan & plan, struct ggml_cgraph * g) {
+    if (ggml_graph_n_nodes(g) != plan.n_nodes) return false;
+    for (const plan_item & it : plan.items) {
+        struct ggml_tensor * node = ggml_graph_node(g, it.node);
+        if (!b200_op_supported(node)) return false;
+        if (it.kind == PK_LAYER_NORM) {
+            if (node->op != GGML_OP_NORM) return false;
+            struct ggml_tensor * mul = ggml_graph_node(g, it.node + 1), * out = ggml_graph_node(g, it.last);
+            if (mul->op != GGML_OP_MUL || out->op != GGML_OP_ADD || mul->src[0] != node || out->src[0] != mul) return false;
+            const struct ggml_tensor * x = node->src[0];
+            // rows are read and written by the same threads, so exact in-place is fine; a shifted overlap is not
+            if (overlaps(out, x) && !(out->data == x->data && out->nb[1] == x->nb[1])) return false;
+            if (!b200_op_supported(mul) || !b200_op_supported(out)) return false;
+        } else if (it.kind == PK_GEMV) {
+            if (node->op != GGML_OP_MUL_MAT || !is_quant(node->src[0]->type) || node->src[1]->ne[1] > 8) return false;
+            struct ggml_tensor * out = ggml_graph_node(g, it.last);
+            const struct ggml_tensor * cur = node;
+            for (int s = 0; s < it.n_steps; ++s) {
+                struct ggml_tensor * t = ggml_graph_node(g, it.step_node[s]);
+                if (it.step_kind[s] == B200_EP_ADD) {
+                    if (t->op != GGML_OP_ADD || t->src[1 - it.step_src[s]] != cur) return false;
+                    const struct ggml_tensor * o = t->src[it.step_src[s]];
+                    // an added tensor may share memory with the result only element for element
+                    if (overlaps(out, o) && !(o->data == out->data && o->nb[1] == out->nb[1])) return false;
+                } else if (it.step_kind[s] == B200_EP_SCALE) {
+                    if (t->op != GGML_OP_SCALE || t->src[0] != cur) return false;
+                } else {
+                    if (t->op != GGML_OP_UNARY || t->src[0] != cur) return false;
+                }
+                cur = t;
+            }
+            if (it.store_f16 && (out->op != GGML_OP_CPY || out->src[0] != cur || out->type != GGML_TYPE_F16)) return false;
+            // every CTA reads the activations for the whole kernel: the result must not land on them
+            if (it.last != it.node && overlaps(out, node->src[1])) return false;
+        } else if (it.kind == PK_FA_DECODE) {
+            if (!is_decode_attention(node)) return false;
+        }
+    }
+    return true;
 }
 
 // timing class of a node and its algorithmic work (bytes for memory-bound classes, FLOPs for contractions)
@@ -507,6 +613,10 @@ static int node_class(const struct ggml_tensor * node, double * work) {
             *work = 2.0 * (double) s0->ne[0] * (double) s0->ne[1] * (double) s1->ne[1] * (double) s1->ne[2] * (double) s1->ne[3];
             return TC_MM_F16;
         case GGML_OP_FLASH_ATTN_EXT:
+            if (s0->ne[1] <= 8) {   // decode: bound by streaming K and V once per query row
+                *work = 2.0 * 2.0 * 64.0 * (double) s0->ne[1] * (double) s0->ne[2] * (double) node->src[1]->ne[1];
+                return TC_FATTN_DEC;
+            }
             *work = 4.0 * 64.0 * (double) s0->ne[1] * (double) s0->ne[2] * (double) node->src[1]->ne[1];
             return TC_FATTN;
         case GGML_OP_NORM:     *work = 2.0 * out_bytes; return TC_NORM;
@@ -522,85 +632,363 @@ static int node_class(const struct ggml_tensor * node, double * work) {
     }
 }
 
+// Runs one plan item for all graphs in gs (same structure) on ctx's stream.  Returns 0 or an error code.
+static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cgraph * const * gs, int n_g) {
+    void * st = (void *) ctx->stream;
+    if (it.kind == PK_NODE) {
+        for (int g = 0; g < n_g; ++g) {
+            const int e = compute_node(ctx, ggml_graph_node(gs[g], it.node));
+            if (e) return e;
+        }
+        return 0;
+    }
+    if (it.kind == PK_LAYER_NORM) {
+        b200_ln_row rows[64];
+        int n_rows = 0;
+        struct ggml_tensor * n0 = ggml_graph_node(gs[0], it.node);
+        const float * gamma = (const float *) ggml_graph_node(gs[0], it.node + 1)->src[1]->data;
+        const float * beta  = (const float *) ggml_graph_node(gs[0], it.last)->src[1]->data;
+        float eps;
+        memcpy(&eps, n0->op_params, sizeof(float));
+        const int64_t ne00 = n0->src[0]->ne[0];
+        for (int g = 0; g < n_g; ++g) {
+            struct ggml_tensor * nrm = ggml_graph_node(gs[g], it.node), * out = ggml_graph_node(gs[g], it.last);
+            const struct ggml_tensor * x = nrm->src[0];
+            const float * ga = (const float *) ggml_graph_node(gs[g], it.node + 1)->src[1]->data;
+            const float * be = (const float *) out->src[1]->data;
+            if (ga != gamma || be != beta || x->ne[1] > 64 || ne00 > 2048) {     // other weights or a tall input: on its own
+                const int e = b200_layer_norm((const float *) x->data, ga, be, (float *) out->data, x->ne[0], x->ne[1], (int64_t) x->nb[1], (int64_t) out->nb[1], eps, st);
+                if (e) return e;
+                continue;
+            }
+            for (int64_t r = 0; r < x->ne[1]; ++r) {
+                if (n_rows == 64) {
+                    const int e = b200_layer_norm_rows(rows, n_rows, gamma, beta, ne00, eps, st);
+                    if (e) return e;
+                    n_rows = 0;
+                }
+                rows[n_rows].x = (const float *) ((const char *) x->data + r * x->nb[1]);
+                rows[n_rows].y = (float *) ((char *) out->data + r * out->nb[1]);
+                ++n_rows;
+            }
+        }
+        return n_rows ? b200_layer_norm_rows(rows, n_rows, gamma, beta, ne00, eps, st) : 0;
+    }
+    if (it.kind == PK_GEMV) {
+        struct ggml_tensor * n0 = ggml_graph_node(gs[0], it.node);
+        const struct ggml_tensor * w = n0->src[0];
+        const int64_t nb_total = (int64_t) (ggml_nbytes(w) / ggml_type_size(w->type));
+        b200_gemv_ep ep;
+        memset(&ep, 0, sizeof(ep));
+        ep.n_steps = it.n_steps; ep.store_f16 = it.store_f16;
+        for (int s = 0; s < it.n_steps; ++s) {
+            ep.kind[s] = it.step_kind[s];
+            if (it.step_kind[s] == B200_EP_SCALE) memcpy(&ep.scalar[s], ggml_graph_node(gs[0], it.step_node[s])->op_params, sizeof(float));
+        }
+        b200_gemv_col cols[8];
+        int n_cols = 0;
+        auto flush = [&]() -> int {
+            if (!n_cols) return 0;
+            const int e = b200_mul_mat_vec_q_cols((int) w->type, w->data, nb_total, w->ne[1], w->ne[0], cols, n_cols, &ep, st);
+            n_cols = 0;
+            return e;
+        };
+        for (int g = 0; g < n_g; ++g) {
+            struct ggml_tensor * mm = ggml_graph_node(gs[g], it.node), * out = ggml_graph_node(gs[g], it.last);
+            if (mm->src[0]->data != w->data) {            // a state of another model on the same device: its own launch
+                int e = flush();
+                if (e) return e;
+                struct ggml_cgraph * one[1] = { gs[g] };
+                // swap so that the recursive call sees this graph's weights as the reference
+                e = run_item(ctx, it, one, 1);
+                if (e) return e;
+                continue;
+            }
+            const struct ggml_tensor * x = mm->src[1];
+            const int64_t esz = it.store_f16 ? 2 : 4;
+            const int64_t out_stride = it.store_f16 ? mm->ne[0] * 2 : (int64_t) out->nb[1];
+            for (int64_t c = 0; c < x->ne[1]; ++c) {
+                if (n_cols == 8) { const int e = flush(); if (e) return e; }
+                b200_gemv_col & col = cols[n_cols];
+                memset(&col, 0, sizeof(col));
+                col.x = (const float *) ((const char *) x->data + c * x->nb[1]);
+                col.dst = (char *) out->data + c * out_stride;
+                (void) esz;
+                for (int s = 0; s < it.n_steps; ++s) {
+                    if (it.step_kind[s] != B200_EP_ADD) continue;
+                    const struct ggml_tensor * o = ggml_graph_node(gs[g], it.step_node[s])->src[it.step_src[s]];
+                    col.add[s] = (const float *) ((const char *) o->data + (o->ne[1] == 1 ? 0 : c * o->nb[1]));
+                }
+                ++n_cols;
+            }
+        }
+        return flush();
+    }
+    // PK_FA_DECODE
+    {
+        struct ggml_tensor * n0 = ggml_graph_node(gs[0], it.node);
+        const struct ggml_tensor * q0 = n0->src[0], * k0 = n0->src[1], * v0 = n0->src[2];
+        float scale;
+        memcpy(&scale, (const float *) n0->op_params + 0, sizeof(float));
+        b200_fa_row rows[32];
+        int n_rows = 0;
+        auto flush = [&]() -> int {
+            if (!n_rows) return 0;
+            const int e = b200_flash_attn_decode_rows(rows, n_rows, q0->ne[2], (int64_t) q0->nb[2], (int64_t) k0->nb[1], (int64_t) k0->nb[2],
+                                                      (int64_t) v0->nb[1], (int64_t) v0->nb[2], scale, st);
+            n_rows = 0;
+            return e;
+        };
+        for (int g = 0; g < n_g; ++g) {
+            struct ggml_tensor * fa = ggml_graph_node(gs[g], it.node);
+            const struct ggml_tensor * q = fa->src[0], * k = fa->src[1], * v = fa->src[2], * mask = fa->src[3];
+            float sc;
+            memcpy(&sc, (const float *) fa->op_params + 0, sizeof(float));
+            const bool same = q->nb[2] == q0->nb[2] && k->nb[1] == k0->nb[1] && k->nb[2] == k0->nb[2] && v->nb[1] == v0->nb[1] &&
+                              v->nb[2] == v0->nb[2] && sc == scale && q->ne[2] == q0->ne[2];
+            const bool fast = same && k->ne[1] <= 8192 && !((uintptr_t) k->data & 15) && !((uintptr_t) v->data & 15) && !(k->nb[1] & 15) &&
+                              !(k->nb[2] & 15) && !(v->nb[1] & 15) && !(v->nb[2] & 15);
+            if (!fast) {
+                int e = flush();
+                if (e) return e;
+                e = compute_node(ctx, fa);
+                if (e) return e;
+                continue;
+            }
+            for (int64_t r = 0; r < q->ne[1]; ++r) {
+                if (n_rows == 32) { const int e = flush(); if (e) return e; }
+                rows[n_rows].q    = (const float *) ((const char *) q->data + r * q->nb[1]);
+                rows[n_rows].k    = k->data;
+                rows[n_rows].v    = v->data;
+                rows[n_rows].mask = mask ? (const char *) mask->data + r * mask->nb[1] : nullptr;
+                rows[n_rows].dst  = (float *) ((char *) fa->data + r * fa->nb[2]);
+                rows[n_rows].n_kv = k->ne[1];
+                ++n_rows;
+            }
+        }
+        return flush();
+    }
+}
+
+static int run_plan(b200_backend_ctx * ctx, const exec_plan & plan, struct ggml_cgraph * const * gs, int n_g, bool timing,
+                    std::vector<int> * t_class, std::vector<double> * t_work, size_t * n_ev) {
+    auto next_event = [&]() -> cudaEvent_t {
+        if (*n_ev == ctx->events.size()) { cudaEvent_t e; cudaEventCreate(&e); ctx->events.push_back(e); }
+        return ctx->events[(*n_ev)++];
+    };
+    for (const plan_item & it : plan.items) {
+        if (timing) {
+            double work = 0;
+            struct ggml_tensor * node = ggml_graph_node(gs[0], it.node);
+            t_class->push_back(it.kind == PK_LAYER_NORM ? (node_class(node, &work), TC_NORM) : node_class(node, &work));
+            t_work->push_back(work * n_g);
+            cudaEventRecord(next_event(), ctx->stream);
+        }
+        const int e = run_item(ctx, it, gs, n_g);
+        if (timing) cudaEventRecord(next_event(), ctx->stream);
+        if (e != 0) {
+            struct ggml_tensor * node = ggml_graph_node(gs[0], it.node);
+            fprintf(stderr, "ggml-b200: node %d %s (%s) failed with code %d (%s)\n", it.node, node->name, ggml_op_name(node->op), e,
+                    e < 10000 ? cudaGetErrorString((cudaError_t) e) : "argument error");
+            return e;
+        }
+    }
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Cross-state batching of decode steps.  Every whisper_state owns a backend instance and a host thread; their
+// single-token decode graphs arrive here independently.  Threads that arrive within a short window hand their
+// graph to one of them (the leader), which launches every item once for the whole group on its own stream and
+// then lets the others' streams wait on an event.  Columns stay independent, so each state gets exactly the
+// bits it would get alone.  The wait is bounded (no thread ever waits on the GPU here, only on a host condition
+// variable with a timeout).
+// ---------------------------------------------------------------------------------------------
+struct batch_req {
+    b200_backend_ctx *   ctx;
+    struct ggml_cgraph * g;
+    uint64_t             sig;
+    int                  state;     // 0 waiting, 1 done (stream must wait on ev), 2 run it yourself, 3 failed
+    cudaEvent_t          ev;
+};
+
+struct device_batcher {
+    std::mutex              mu;
+    std::condition_variable cv;
+    std::vector<batch_req *> pending;
+    bool                    leader_active = false;
+    std::vector<cudaEvent_t> events;       // round-robin pool
+    size_t                  next_event = 0;
+    std::unordered_map<uint64_t, exec_plan> plans;      // by signature, fused
+    int                     alive = 0;                  // backend instances on this device
+    std::vector<b200_backend_ctx *> members;            // live backend instances on this device
+};
+
+static device_batcher g_batchers[B200_MAX_DEVICES];
+
+static void batcher_join(b200_backend_ctx * ctx) {
+    device_batcher & B = g_batchers[ctx->device];
+    std::lock_guard<std::mutex> lk(B.mu);
+    B.members.push_back(ctx);
+    B.alive = (int) B.members.size();
+}
+static void batcher_leave(b200_backend_ctx * ctx) {
+    device_batcher & B = g_batchers[ctx->device];
+    std::lock_guard<std::mutex> lk(B.mu);
+    for (size_t i = 0; i < B.members.size(); ++i) if (B.members[i] == ctx) { B.members.erase(B.members.begin() + i); break; }
+    B.alive = (int) B.members.size();
+}
+static std::atomic<int64_t> g_batched_graphs{0}, g_batches{0};
+extern "C" int64_t b200_stat_batched_graphs(void) { return g_batched_graphs.load(); }
+extern "C" int64_t b200_stat_batches(void)        { return g_batches.load(); }
+
+static bool is_decode_graph(struct ggml_cgraph * g) {
+    const int n = ggml_graph_n_nodes(g);
+    for (int i = 0; i < n; ++i) {
+        const struct ggml_tensor * t = ggml_graph_node(g, i);
+        if (is_view_op(t->op)) continue;
+        return t->op == GGML_OP_GET_ROWS && t->src[1]->ne[0] <= 8 && n > 64;     // decoder graphs start with the token embedding
+    }
+    return false;
+}
+
+static enum ggml_status finish_status(int e) {
+    if (e == 0) return GGML_STATUS_SUCCESS;
+    return e == (int) cudaErrorMemoryAllocation ? GGML_STATUS_ALLOC_FAILED : GGML_STATUS_FAILED;
+}
+
 static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struct ggml_cgraph * cgraph) {
     b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
     if (cudaSetDevice(ctx->device) != cudaSuccess) return GGML_STATUS_FAILED;
     const int64_t t_enter = now_ns();
-    const int n_nodes = ggml_graph_n_nodes(cgraph);
-    int64_t done = 0;
+    static const bool fuse     = getenv("GGML_B200_NO_FUSION") == nullptr;
+    static const bool batching = getenv("GGML_B200_NO_BATCHING") == nullptr;
+    static const int  window_us = getenv("GGML_B200_BATCH_WINDOW_US") ? atoi(getenv("GGML_B200_BATCH_WINDOW_US")) : 300;
     const bool timing = g_timing_on.load() != 0;
-    std::vector<int>    t_class;
-    std::vector<double> t_work;
-    size_t n_ev = 0;
-    auto next_event = [&]() -> cudaEvent_t {
-        if (n_ev == ctx->events.size()) { cudaEvent_t e; cudaEventCreate(&e); ctx->events.push_back(e); }
-        return ctx->events[n_ev++];
-    };
-    static const bool fuse = getenv("GGML_B200_NO_FUSION") == nullptr;
-    graph_info gi;
-    std::vector<char> fused(n_nodes, 0);
-    if (fuse) analyse_graph(cgraph, gi);
+    device_batcher & B = g_batchers[ctx->device];
+
+    const int n_nodes = ggml_graph_n_nodes(cgraph);
+    int64_t n_compute = 0;
     for (int i = 0; i < n_nodes; ++i) {
         struct ggml_tensor * node = ggml_graph_node(cgraph, i);
         if (is_view_op(node->op) || ggml_is_empty(node)) continue;
-        if (fused[i]) { ++done; continue; }
         if (!b200_op_supported(node)) {
             fprintf(stderr, "ggml-b200: unsupported node %s (%s) reached graph_compute\n", node->name, ggml_op_name(node->op));
             return GGML_STATUS_FAILED;
         }
-        if (timing) {
-            double work = 0;
-            t_class.push_back(node_class(node, &work));
-            t_work.push_back(work);
-            cudaEventRecord(next_event(), ctx->stream);
-        }
-        int e = -1;
-        if (fuse && node->op == GGML_OP_NORM) {
-            const struct ggml_tensor * ga = nullptr, * be = nullptr;
-            const int last = match_layer_norm(cgraph, gi, i, &ga, &be);
-            struct ggml_tensor * out = last > 0 ? ggml_graph_node(cgraph, last) : nullptr;
-            const struct ggml_tensor * x = node->src[0];
-            // rows are read and written by the same lanes, so exact in-place is fine; a shifted overlap is not
-            const bool alias_ok = out && (!overlaps(out, x) || (out->data == x->data && out->nb[1] == x->nb[1]));
-            if (last > 0 && alias_ok && b200_op_supported(ggml_graph_node(cgraph, i + 1)) && b200_op_supported(out)) {
-                float eps;
-                memcpy(&eps, node->op_params, sizeof(float));
-                e = b200_layer_norm((const float *) x->data, (const float *) ga->data, (const float *) be->data, (float *) out->data,
-                                    x->ne[0], x->ne[1], (int64_t) x->nb[1], (int64_t) out->nb[1], eps, (void *) ctx->stream);
-                fused[i + 1] = 1; fused[last] = 1;
-            }
-        } else if (fuse && node->op == GGML_OP_MUL_MAT && is_quant(node->src[0]->type) && node->src[1]->ne[1] <= 8) {
-            b200_epilogue ep;
-            int last = i;
-            struct ggml_tensor * out = node;
-            const struct ggml_tensor * operands[4] = {nullptr, nullptr, nullptr, nullptr};
-            match_vec_epilogue(cgraph, gi, i, &ep, &last, &out, fused, operands);
-            const struct ggml_tensor * s0 = node->src[0], * s1 = node->src[1];
-            bool hazard = out != node && overlaps(out, s1);
-            for (int k = 0; k < ep.n_steps; ++k) {
-                // an added tensor may share memory with the result only element for element (same thread reads then writes)
-                if (operands[k] && overlaps(out, operands[k]) && !(operands[k]->data == out->data && operands[k]->nb[1] == out->nb[1])) hazard = true;
-            }
-            if (hazard) {
-                // the allocator placed the final tensor over the activations, which every CTA still reads: run unfused
-                for (int j = i + 1; j <= last; ++j) fused[j] = 0;
-                ep.n_steps = 0; ep.store_f16 = 0; out = node;
-            }
-            const int64_t nb_total = (int64_t) (ggml_nbytes(s0) / ggml_type_size(s0->type));
-            const int64_t ldd = ep.store_f16 ? node->ne[0] : (int64_t) out->nb[1] / 4;
-            e = b200_mul_mat_vec_q_ep((int) s0->type, s0->data, nb_total, s0->ne[1], s0->ne[0], (const float *) s1->data, (int64_t) s1->nb[1],
-                                      s1->ne[1], out->data, ldd, &ep, (void *) ctx->stream);
-        }
-        if (e == -1) e = compute_node(ctx, node);
-        if (timing) cudaEventRecord(next_event(), ctx->stream);
-        if (e != 0) {
-            fprintf(stderr, "ggml-b200: node %d %s (%s) failed with code %d (%s)\n", i, node->name, ggml_op_name(node->op), e,
-                    e < 10000 ? cudaGetErrorString((cudaError_t) e) : "argument error");
-            return e == (int) cudaErrorMemoryAllocation ? GGML_STATUS_ALLOC_FAILED : GGML_STATUS_FAILED;
-        }
-        ++done;
+        ++n_compute;
     }
-    g_nodes_computed += done;
+
+    // ---- batched path -------------------------------------------------------------------------
+    if (batching && fuse && !timing && B.alive > 1 && is_decode_graph(cgraph)) {
+        batch_req req = { ctx, cgraph, graph_signature(cgraph), 0, nullptr };
+        ctx->last_decode_ns = now_ns();
+        std::unique_lock<std::mutex> lk(B.mu);
+        B.pending.push_back(&req);
+        if (B.leader_active) {
+            B.cv.notify_all();                                   // the leader may be waiting for this arrival
+            B.cv.wait(lk, [&] { return req.state != 0; });
+            lk.unlock();
+            if (req.state == 1) {
+                if (!cuda_ok(cudaStreamWaitEvent(ctx->stream, req.ev, 0), "cudaStreamWaitEvent")) return GGML_STATUS_FAILED;
+                g_nodes_computed += n_compute;
+                g_graphs_computed += 1;
+                g_host_ns_compute += now_ns() - t_enter;
+                return GGML_STATUS_SUCCESS;
+            }
+            if (req.state == 3) return GGML_STATUS_FAILED;
+            // state 2: structure or aliasing did not fit the group's plan - run alone below
+        } else {
+            B.leader_active = true;
+            // how many states are decoding right now?  those that sent a decode graph within the last 20 ms
+            int expected = 0;
+            const int64_t now = now_ns();
+            for (b200_backend_ctx * c : B.members) if (now - c->last_decode_ns < 20 * 1000 * 1000) ++expected;
+            const auto deadline = std::chrono::steady_clock::now() + std::chrono::microseconds(window_us);
+            B.cv.wait_until(lk, deadline, [&] { return (int) B.pending.size() >= expected; });
+            std::vector<batch_req *> mine;
+            mine.swap(B.pending);
+            B.leader_active = false;                              // later arrivals elect their own leader
+            cudaEvent_t ev = nullptr;
+            if (B.events.size() < 64) { cudaEvent_t e; cudaEventCreateWithFlags(&e, cudaEventDisableTiming); B.events.push_back(e); }
+            ev = B.events[B.next_event++ % B.events.size()];
+            // plan of the leader's structure (cached by signature)
+            exec_plan * plan = nullptr;
+            auto pit = B.plans.find(req.sig);
+            if (pit == B.plans.end()) {
+                if (B.plans.size() > 256) B.plans.clear();
+                plan = &B.plans[req.sig];
+                build_plan(cgraph, *plan, true);
+            } else {
+                plan = &pit->second;
+            }
+            const exec_plan plan_copy = *plan;                    // the map may change once the lock is dropped
+            lk.unlock();
+
+            std::vector<struct ggml_cgraph *> gs;
+            std::vector<batch_req *> served;
+            int rc = 0;
+            if (graph_fits_plan(plan_copy, cgraph)) {
+                gs.push_back(cgraph);
+                for (batch_req * r : mine) {
+                    if (r == &req) continue;
+                    if (r->sig == req.sig && graph_fits_plan(plan_copy, r->g)) { gs.push_back(r->g); served.push_back(r); }
+                }
+                size_t n_ev = 0;
+                rc = run_plan(ctx, plan_copy, gs.data(), (int) gs.size(), false, nullptr, nullptr, &n_ev);
+                if (rc == 0 && !served.empty()) rc = cudaEventRecord(ev, ctx->stream) == cudaSuccess ? 0 : (int) cudaGetLastError();
+                g_batched_graphs += (int64_t) gs.size();
+                g_batches += 1;
+            } else {
+                rc = -1;                                          // leader's own graph does not fit: everybody runs alone
+            }
+            lk.lock();
+            for (batch_req * r : mine) {
+                if (r == &req) continue;
+                bool was_served = false;
+                for (batch_req * s : served) if (s == r) was_served = true;
+                if (was_served) { r->ev = ev; r->state = rc == 0 ? 1 : 3; }
+                else r->state = 2;
+            }
+            lk.unlock();
+            B.cv.notify_all();
+            if (rc == 0) {
+                g_nodes_computed += n_compute;
+                g_graphs_computed += 1;
+                g_host_ns_compute += now_ns() - t_enter;
+                return GGML_STATUS_SUCCESS;
+            }
+            if (rc > 0) return finish_status(rc);
+            // rc == -1: fall through to the plain path
+        }
+    }
+
+    // ---- plain path: this graph alone ------------------------------------------------------------
+    exec_plan plan;
+    {
+        // plans are cached by structure signature (building one walks the graph with a hash map)
+        const uint64_t sig = graph_signature(cgraph) ^ (fuse ? 0 : 0x9e3779b97f4a7c15ull);
+        bool have = false;
+        {
+            std::lock_guard<std::mutex> lk(B.mu);
+            auto pit = B.plans.find(sig);
+            if (pit != B.plans.end()) { plan = pit->second; have = true; }
+        }
+        if (!have) {
+            build_plan(cgraph, plan, fuse);
+            std::lock_guard<std::mutex> lk(B.mu);
+            if (B.plans.size() > 256) B.plans.clear();
+            B.plans[sig] = plan;
+        }
+    }
+    if (fuse && !graph_fits_plan(plan, cgraph)) build_plan(cgraph, plan, false);     // aliasing hazard somewhere: node by node
+    std::vector<int>    t_class;
+    std::vector<double> t_work;
+    size_t n_ev = 0;
+    struct ggml_cgraph * one[1] = { cgraph };
+    const int e = run_plan(ctx, plan, one, 1, timing, &t_class, &t_work, &n_ev);
+    if (e != 0) return finish_status(e);
+    g_nodes_computed += n_compute;
     g_graphs_computed += 1;
     g_host_ns_compute += now_ns() - t_enter;
     if (timing && !t_class.empty()) {
@@ -667,6 +1055,7 @@ static ggml_backend_t b200_dev_init_backend(ggml_backend_dev_t dev, const char *
     ctx->device = dctx->device;
     ctx->name   = dctx->name;
     if (!cuda_ok(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking), "cudaStreamCreate")) { delete ctx; return nullptr; }
+    batcher_join(ctx);
     return new ggml_backend{ b200_guid(), b200_backend_iface, dev, ctx };
 }
 
@@ -796,6 +1185,8 @@ static void * b200_reg_get_proc_address(ggml_backend_reg_t, const char * name) {
     if (strcmp(name, "b200_stat_d2h") == 0)    return (void *) b200_stat_d2h;
     if (strcmp(name, "b200_stat_host_ns_compute") == 0) return (void *) b200_stat_host_ns_compute;
     if (strcmp(name, "b200_stat_host_ns_sync") == 0)    return (void *) b200_stat_host_ns_sync;
+    if (strcmp(name, "b200_stat_batched_graphs") == 0)  return (void *) b200_stat_batched_graphs;
+    if (strcmp(name, "b200_stat_batches") == 0)         return (void *) b200_stat_batches;
     if (strcmp(name, "b200_launch_count") == 0) return (void *) b200_launch_count;
     if (strcmp(name, "b200_timing_enable") == 0)  return (void *) b200_timing_enable;
     if (strcmp(name, "b200_timing_reset") == 0)   return (void *) b200_timing_reset;

@@ -190,35 +190,54 @@ k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
 }
 
 
-// Few query rows (token-by-token decode, beams): one CTA per (query row, head).  The work of the kernel above is
-// split by role so that the sequential part is as short as possible: all threads score the keys, a block scan gives
-// every key the running maximum it meets, exp() runs in parallel, then 64 threads (one per output dim) replay the
-// F16 accumulation key by key while one more thread replays the running sum.
+// Few query rows (token-by-token decode, beams, several decoder states stepping together): one CTA per
+// (query row, head).  The work of the kernel above is split by role so that the sequential part is as short as
+// possible: all threads score the keys, a block scan gives every key the running maximum it meets, exp() runs in
+// parallel, then 64 threads (one per output dim) replay the F16 accumulation key by key while one more thread
+// replays the running sum.  Every query row carries its own K/V/mask/output pointers and key count.
 #define FA_DEC_THREADS 256
 #define FA_DEC_MAX_KV  8192
 #define FA_DEC_CHUNK   256
+#define FA_DEC_MAX_ROWS 32
+struct FaRow {
+    const char * q;        // 64 f32 per head, head stride nbq2
+    const char * k;        // f16 [64, n_kv, H], strides nbk1, nbk2
+    const char * v;
+    const char * mask;     // f16 row of this query (n_kv entries) or NULL
+    float *      dst;      // [H][64] f32 of this query row
+    int          n_kv;
+};
+struct FaRows {
+    FaRow r[FA_DEC_MAX_ROWS];
+    int64_t nbq2, nbk1, nbk2, nbv1, nbv2;
+    float scale;
+};
+
 template <bool S_FMA>
 __global__ void __launch_bounds__(FA_DEC_THREADS)
-k_flash_attn_decode(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
-                    const char * __restrict__ k, int64_t nbk1, int64_t nbk2,
-                    const char * __restrict__ v, int64_t nbv1, int64_t nbv2,
-                    const char * __restrict__ mask, int64_t nbm1,
-                    float * __restrict__ dst, int64_t n_q, int n_kv, int64_t n_head, float scale) {
+k_flash_attn_decode(FaRows rows, int max_kv) {
     extern __shared__ __align__(16) float fa_smem[];
+    const FaRow & R = rows.r[blockIdx.x];
+    const int n_kv = R.n_kv;
     float * Qs  = fa_smem;                 // [64]
-    float * sc  = Qs + 64;                 // [n_kv] scores, later vs
-    float * msv = sc + n_kv;               // [n_kv] ms (1 unless a new maximum), < 0 marks a skipped key
+    float * sc  = Qs + 64;                 // [n_kv] scores, later vs (-0.0f marks a skipped key)
+    float * msv = sc + max_kv;             // [n_kv] ms (1 unless a new maximum)
+    unsigned char * evt = (unsigned char *) (msv + max_kv);                 // [n_kv/8] group contains a new maximum
+    __half * Vs = (__half *) (fa_smem + ((64 + 2 * max_kv + (max_kv + 31) / 32 + 3) & ~3));   // [2][FA_DEC_CHUNK][64], 16-byte aligned
     __shared__ float seg_max[FA_DEC_THREADS];
     __shared__ float s_S;
     const int tid = threadIdx.x;
-    const int64_t iq1 = blockIdx.x, h = blockIdx.y;
+    const int64_t h = blockIdx.y;
+    const int64_t nbk1 = rows.nbk1, nbv1 = rows.nbv1;
+    const float scale = rows.scale;
 
-    if (tid < 64) Qs[tid] = round_f16(*(const float *) (q + iq1 * nbq1 + h * nbq2 + tid * 4));
+    if (tid < 64) Qs[tid] = round_f16(*(const float *) (R.q + h * rows.nbq2 + tid * 4));
+    for (int g = tid; g < (n_kv + 7) / 8; g += FA_DEC_THREADS) evt[g] = 0;
     __syncthreads();
 
-    const char * kh = k + h * nbk2;
-    const char * vh = v + h * nbv2;
-    const __half * mp = mask ? (const __half *) (mask + iq1 * nbm1) : nullptr;
+    const char * kh = R.k + h * rows.nbk2;
+    const char * vh = R.v + h * rows.nbv2;
+    const __half * mp = (const __half *) R.mask;
 
     // scores
 #pragma unroll 2
@@ -226,7 +245,7 @@ k_flash_attn_decode(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
         float mv = 0.0f;
         if (mp) mv = __half2float(mp[ic]);
         float s = -INFINITY;
-        bool skip = (mv == -INFINITY);
+        const bool skip = (mv == -INFINITY);
         if (!skip) {
             float acc[32];
             const uint4 * kp = (const uint4 *) (kh + (int64_t) ic * nbk1);
@@ -266,18 +285,18 @@ k_flash_attn_decode(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
             s = __fadd_rn(s, mv);
         }
         sc[ic]  = s;                       // -inf for skipped keys: never a new maximum
-        msv[ic] = skip ? -1.0f : 1.0f;
+        msv[ic] = skip ? -1.0f : 1.0f;     // temporary skip mark
     }
     __syncthreads();
 
     // contiguous segment per thread: segment maxima, exclusive block scan, then the per-key pass
     const int seg = (n_kv + FA_DEC_THREADS - 1) / FA_DEC_THREADS;
-    const int i0 = tid * seg, i1 = min(n_kv, i0 + seg);
+    const int i0 = min(n_kv, tid * seg), i1 = min(n_kv, i0 + seg);
     float m = -INFINITY;
     for (int i = i0; i < i1; ++i) m = fmaxf(m, sc[i]);
     seg_max[tid] = m;
     __syncthreads();
-    if (tid < 32) {                        // exclusive prefix maximum over the 256 segment maxima
+    if (tid < 32) {                        // exclusive prefix maximum over the segment maxima
         float carry = -INFINITY;
         for (int base = 0; base < FA_DEC_THREADS; base += 32) {
             const float x = seg_max[base + tid];
@@ -297,9 +316,9 @@ k_flash_attn_decode(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
     {
         float M = seg_max[tid];
         for (int i = i0; i < i1; ++i) {
-            if (msv[i] < 0.0f) continue;
+            if (msv[i] < 0.0f) { msv[i] = 1.0f; sc[i] = -0.0f; continue; }      // skipped: ms = 1, vs = -0
             const float s = sc[i];
-            if (s > M) { msv[i] = expf_glibc(__fadd_rn(M, -s)); sc[i] = 1.0f; M = s; }
+            if (s > M) { msv[i] = expf_glibc(__fadd_rn(M, -s)); sc[i] = 1.0f; M = s; evt[i >> 3] = 1; }
             else       { sc[i] = expf_glibc(__fadd_rn(s, -M)); }
         }
     }
@@ -307,9 +326,9 @@ k_flash_attn_decode(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
 
     // V is streamed through shared memory in chunks of FA_DEC_CHUNK keys, double buffered: warps 3..7 fetch chunk c+1
     // while warps 0..1 (one thread per output dim) replay the F16 accumulation over chunk c and one thread of
-    // warp 2 replays the running sum.
+    // warp 2 replays the running sum.  Keys are taken eight at a time with all operands in registers; only groups that
+    // contain a new maximum take the path that rescales the accumulator.
     {
-        __half * Vs = (__half *) (fa_smem + ((64 + 2 * n_kv + 3) & ~3));   // [2][FA_DEC_CHUNK][64], 16-byte aligned
         const int n_chunks = (n_kv + FA_DEC_CHUNK - 1) / FA_DEC_CHUNK;
         auto fetch = [&](int c) {
             const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
@@ -326,21 +345,44 @@ k_flash_attn_decode(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
                 if (c + 1 < n_chunks) fetch(c + 1);
             } else if (tid < 64) {
                 const __half * vb = Vs + (size_t) (c & 1) * FA_DEC_CHUNK * 64 + tid;
-#pragma unroll 8
-                for (int i = 0; i < kn; ++i) {
-                    const float ms = msv[k0 + i], vs = sc[k0 + i];
-                    const float vv = __half2float(vb[i * 64]);
-                    if (ms >= 0.0f) {
-                        if (ms != 1.0f) a = round_f16(__fmul_rn(a, ms));
-                        a = round_f16(__fmaf_rn(vv, vs, a));
+                int i = 0;
+                for (; i + 8 <= kn; i += 8) {
+                    float vs[8], vv[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        vs[u] = sc[k0 + i + u];
+                        vv[u] = __half2float(vb[(i + u) * 64]);
+                        if (__float_as_uint(vs[u]) == 0x80000000u) vv[u] = 0.0f;     // skipped key: exact no-op whatever V holds
+                    }
+                    if (!evt[(k0 + i) >> 3]) {
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) a = round_f16(__fmaf_rn(vv[u], vs[u], a));
+                    } else {
+#pragma unroll
+                        for (int u = 0; u < 8; ++u) {
+                            const float ms = msv[k0 + i + u];
+                            if (ms != 1.0f) a = round_f16(__fmul_rn(a, ms));
+                            a = round_f16(__fmaf_rn(vv[u], vs[u], a));
+                        }
                     }
                 }
-            } else if (tid == 64) {
-#pragma unroll 8
-                for (int i = 0; i < kn; ++i) {
-                    const float ms = msv[k0 + i];
-                    if (ms >= 0.0f) S = S_FMA ? __fmaf_rn(S, ms, sc[k0 + i]) : __fadd_rn(__fmul_rn(S, ms), sc[k0 + i]);
+                for (; i < kn; ++i) {
+                    const float ms = msv[k0 + i], vs1 = sc[k0 + i];
+                    float vv1 = __half2float(vb[i * 64]);
+                    if (__float_as_uint(vs1) == 0x80000000u) vv1 = 0.0f;
+                    if (ms != 1.0f) a = round_f16(__fmul_rn(a, ms));
+                    a = round_f16(__fmaf_rn(vv1, vs1, a));
                 }
+            } else if (tid == 64) {
+                int i = 0;
+                for (; i + 8 <= kn; i += 8) {
+                    float ms[8], vs[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) { ms[u] = msv[k0 + i + u]; vs[u] = sc[k0 + i + u]; }
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) S = S_FMA ? __fmaf_rn(S, ms[u], vs[u]) : __fadd_rn(__fmul_rn(S, ms[u]), vs[u]);
+                }
+                for (; i < kn; ++i) S = S_FMA ? __fmaf_rn(S, msv[k0 + i], sc[k0 + i]) : __fadd_rn(__fmul_rn(S, msv[k0 + i]), sc[k0 + i]);
             }
             __syncthreads();
         }
@@ -348,11 +390,52 @@ k_flash_attn_decode(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
         if (tid == 64) s_S = S;
     }
     __syncthreads();
-    if (tid < 64) dst[(iq1 * n_head + h) * 64 + tid] = __fmul_rn(Qs[tid], __fdiv_rn(1.0f, s_S));
+    if (tid < 64) R.dst[h * 64 + tid] = __fmul_rn(Qs[tid], __fdiv_rn(1.0f, s_S));
+}
+
+static size_t fa_dec_smem(int max_kv) {
+    return (size_t) ((64 + 2 * max_kv + (max_kv + 31) / 32 + 3) & ~3) * sizeof(float) + 2 * FA_DEC_CHUNK * 64 * sizeof(__half);
+}
+
+static bool g_fa_s_fma = true;
+
+static int launch_fa_decode(const FaRows & rows, int n_rows, int64_t n_head, cudaStream_t st) {
+    int max_kv = 1;
+    for (int i = 0; i < n_rows; ++i) max_kv = max(max_kv, rows.r[i].n_kv);
+    max_kv = (max_kv + 7) & ~7;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaFuncSetAttribute(k_flash_attn_decode<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) fa_dec_smem(FA_DEC_MAX_KV));
+        cudaFuncSetAttribute(k_flash_attn_decode<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) fa_dec_smem(FA_DEC_MAX_KV));
+        attr_done[dev] = true;
+    }
+    dim3 grid((unsigned) n_rows, (unsigned) n_head);
+    if (g_fa_s_fma) k_flash_attn_decode<true><<<grid, FA_DEC_THREADS, fa_dec_smem(max_kv), st>>>(rows, max_kv);
+    else            k_flash_attn_decode<false><<<grid, FA_DEC_THREADS, fa_dec_smem(max_kv), st>>>(rows, max_kv);
+    B200_RETURN_LAST();
+}
+
+extern "C" int b200_flash_attn_decode_rows(const b200_fa_row * rows, int n_rows, int64_t n_head, int64_t nbq2, int64_t nbk1, int64_t nbk2,
+                                           int64_t nbv1, int64_t nbv2, float scale, void * stream) {
+    if (n_rows <= 0) return 0;
+    if (n_rows > FA_DEC_MAX_ROWS || n_head <= 0 || n_head > 65535) return B200_ERR_ARG;
+    if ((nbk1 & 15) || (nbk2 & 15) || (nbv1 & 15) || (nbv2 & 15) || (nbq2 & 3)) return B200_ERR_ARG;
+    ensure_exp_table();
+    FaRows r;
+    memset(&r, 0, sizeof(r));
+    r.nbq2 = nbq2; r.nbk1 = nbk1; r.nbk2 = nbk2; r.nbv1 = nbv1; r.nbv2 = nbv2; r.scale = scale;
+    for (int i = 0; i < n_rows; ++i) {
+        if (rows[i].n_kv <= 0 || rows[i].n_kv > FA_DEC_MAX_KV) return B200_ERR_ARG;
+        if (((uintptr_t) rows[i].k & 15) || ((uintptr_t) rows[i].v & 15) || ((uintptr_t) rows[i].q & 3)) return B200_ERR_ARG;
+        r.r[i].q = (const char *) rows[i].q; r.r[i].k = (const char *) rows[i].k; r.r[i].v = (const char *) rows[i].v;
+        r.r[i].mask = (const char *) rows[i].mask; r.r[i].dst = rows[i].dst; r.r[i].n_kv = (int) rows[i].n_kv;
+    }
+    return launch_fa_decode(r, n_rows, n_head, as_stream(stream));
 }
 
 // The host compiler of the reference contracts "S*ms + vs" into one FMA (GNU mode, -mfma).
-static bool g_fa_s_fma = true;
 extern "C" void b200_set_fa_sum_fma(int on) { g_fa_s_fma = on != 0; }
 
 extern "C" int b200_flash_attn_ext(const float * q, int64_t nbq1, int64_t nbq2,
@@ -365,24 +448,16 @@ extern "C" int b200_flash_attn_ext(const float * q, int64_t nbq1, int64_t nbq2,
     if (((uintptr_t) k & 15) || (nbk1 & 15) || (nbk2 & 15) || ((uintptr_t) v & 3) || (nbv1 & 3) || (nbv2 & 3)) return B200_ERR_ARG;
     if (((uintptr_t) q & 3) || (nbq1 & 3) || (nbq2 & 3) || ((uintptr_t) dst & 7)) return B200_ERR_ARG;
     ensure_exp_table();
-    if (n_q <= 16 && n_kv <= FA_DEC_MAX_KV && !((uintptr_t) v & 15) && !(nbv1 & 15) && !(nbv2 & 15)) {
-        dim3 dgrid((unsigned) n_q, (unsigned) n_head);
-        const size_t smem = (size_t) ((64 + 2 * n_kv + 3) & ~(int64_t) 3) * sizeof(float) + 2 * FA_DEC_CHUNK * 64 * sizeof(__half);
-        static bool attr_done[64] = {false};
-        int dev = 0;
-        cudaGetDevice(&dev);
-        if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-            cudaFuncSetAttribute(k_flash_attn_decode<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (64 + 2 * FA_DEC_MAX_KV + 4) * 4 + 2 * FA_DEC_CHUNK * 64 * 2);
-            cudaFuncSetAttribute(k_flash_attn_decode<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (64 + 2 * FA_DEC_MAX_KV + 4) * 4 + 2 * FA_DEC_CHUNK * 64 * 2);
-            attr_done[dev] = true;
+    if (n_q <= FA_DEC_MAX_ROWS && n_kv <= FA_DEC_MAX_KV && !((uintptr_t) v & 15) && !(nbv1 & 15) && !(nbv2 & 15)) {
+        FaRows r;
+        memset(&r, 0, sizeof(r));
+        r.nbq2 = nbq2; r.nbk1 = nbk1; r.nbk2 = nbk2; r.nbv1 = nbv1; r.nbv2 = nbv2; r.scale = scale;
+        for (int i = 0; i < (int) n_q; ++i) {
+            r.r[i].q = (const char *) q + i * nbq1; r.r[i].k = (const char *) k; r.r[i].v = (const char *) v;
+            r.r[i].mask = mask ? (const char *) mask + i * nbm1 : nullptr;
+            r.r[i].dst = dst + (int64_t) i * n_head * 64; r.r[i].n_kv = (int) n_kv;
         }
-        if (g_fa_s_fma)
-            k_flash_attn_decode<true><<<dgrid, FA_DEC_THREADS, smem, as_stream(stream)>>>((const char *) q, nbq1, nbq2, (const char *) k, nbk1, nbk2,
-                (const char *) v, nbv1, nbv2, (const char *) mask, nbm1, dst, n_q, (int) n_kv, n_head, scale);
-        else
-            k_flash_attn_decode<false><<<dgrid, FA_DEC_THREADS, smem, as_stream(stream)>>>((const char *) q, nbq1, nbq2, (const char *) k, nbk1, nbk2,
-                (const char *) v, nbv1, nbv2, (const char *) mask, nbm1, dst, n_q, (int) n_kv, n_head, scale);
-        B200_RETURN_LAST();
+        return launch_fa_decode(r, (int) n_q, n_head, as_stream(stream));
     }
     dim3 grid((unsigned) ((n_q + 3) / 4), (unsigned) n_head);
     if (g_fa_s_fma)

@@ -72,14 +72,14 @@ k_layer_norm(const char * __restrict__ x, const float * __restrict__ gamma, cons
 }
 
 // few rows (decode): one CTA of 256 threads per row, row held in registers
+struct LnRows { const float * x[64]; float * y[64]; };
 __global__ void __launch_bounds__(256)
-k_layer_norm_row(const char * __restrict__ x, const float * __restrict__ gamma, const float * __restrict__ beta, char * __restrict__ y,
-                 int ne00, int64_t xs, int64_t ys, float eps) {
+k_layer_norm_row(LnRows rows, const float * __restrict__ gamma, const float * __restrict__ beta, int ne00, float eps) {
     __shared__ double red[8];
     __shared__ float s_mean, s_scale;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const float * xp = (const float *) (x + (int64_t) blockIdx.x * xs);
-    float *       yp = (float *)       (y + (int64_t) blockIdx.x * ys);
+    const float * xp = rows.x[blockIdx.x];
+    float *       yp = rows.y[blockIdx.x];
     float v[8];
     double sum = 0.0;
 #pragma unroll
@@ -129,12 +129,25 @@ extern "C" int b200_layer_norm(const float * x, const float * gamma, const float
                                int64_t x_row_stride_bytes, int64_t y_row_stride_bytes, float eps, void * stream) {
     if (nrows <= 0 || ne00 <= 0) return 0;
     if (nrows <= 64 && ne00 <= 2048) {
-        k_layer_norm_row<<<(unsigned) nrows, 256, 0, as_stream(stream)>>>((const char *) x, gamma, beta, (char *) y, (int) ne00,
-            x_row_stride_bytes, y_row_stride_bytes, eps);
+        LnRows r;
+        for (int i = 0; i < (int) nrows; ++i) {
+            r.x[i] = (const float *) ((const char *) x + i * x_row_stride_bytes);
+            r.y[i] = (float *) ((char *) y + i * y_row_stride_bytes);
+        }
+        k_layer_norm_row<<<(unsigned) nrows, 256, 0, as_stream(stream)>>>(r, gamma, beta, (int) ne00, eps);
         B200_RETURN_LAST();
     }
     k_layer_norm<<<(unsigned) ((nrows + 3) / 4), 128, 0, as_stream(stream)>>>((const char *) x, gamma, beta, (char *) y, ne00, nrows,
         x_row_stride_bytes, y_row_stride_bytes, eps);
+    B200_RETURN_LAST();
+}
+
+extern "C" int b200_layer_norm_rows(const b200_ln_row * rows, int n_rows, const float * gamma, const float * beta, int64_t ne00, float eps, void * stream) {
+    if (n_rows <= 0) return 0;
+    if (n_rows > 64 || ne00 <= 0 || ne00 > 2048) return B200_ERR_ARG;
+    LnRows r;
+    for (int i = 0; i < n_rows; ++i) { r.x[i] = rows[i].x; r.y[i] = rows[i].y; }
+    k_layer_norm_row<<<(unsigned) n_rows, 256, 0, as_stream(stream)>>>(r, gamma, beta, (int) ne00, eps);
     B200_RETURN_LAST();
 }
 

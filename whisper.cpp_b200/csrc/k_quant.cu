@@ -307,33 +307,37 @@ extern "C" int b200_mul_mat_q(int wtype, const void * w_planes, int64_t nb_total
 // integer lane sums for 32 blocks in parallel, then eight threads per column replay the FMA chain in
 // block order.  Activations are quantised by the CTA itself.
 // ------------------------------------------------------------------------------------------------
-struct EpDev {
+// Per-column operands: every activation column may live anywhere (columns of one tensor, or single columns of
+// several decoder states that step together), and so may its result and the tensors its epilogue adds.
+struct GemvCols {
+    const float * x[8];
+    void *        dst[8];
+    const float * add[4][8];      // add[s][n]: operand of epilogue step s for column n (ADD steps only)
+};
+struct GemvEp {
     int n_steps;
     int kind[4];
-    const float * ptr[4];
-    int64_t stride_n[4];
     float scalar[4];
     int store_f16;
     const uint16_t * gelu_table;
 };
 
-__device__ __forceinline__ void ep_store(const EpDev & ep, void * dst, int64_t ldd, int64_t n, int64_t m, float v) {
+__device__ __forceinline__ void ep_store(const GemvEp & ep, const GemvCols & c, int n, int64_t m, float v) {
     for (int s = 0; s < ep.n_steps; ++s) {
-        if (ep.kind[s] == B200_EP_ADD)        v = __fadd_rn(v, ep.ptr[s][m + n * ep.stride_n[s]]);
+        if (ep.kind[s] == B200_EP_ADD)        v = __fadd_rn(v, c.add[s][n][m]);
         else if (ep.kind[s] == B200_EP_SCALE) v = __fmul_rn(v, ep.scalar[s]);
         else {
             if (v <= -10.0f)     v = 0.0f;
             else if (v < 10.0f)  v = __half2float(__ushort_as_half(ep.gelu_table[__half_as_ushort(__float2half_rn(v))]));
         }
     }
-    if (ep.store_f16) ((__half *) dst)[n * ldd + m] = __float2half_rn(v);
-    else              ((float *) dst)[n * ldd + m] = v;
+    if (ep.store_f16) ((__half *) c.dst[n])[m] = __float2half_rn(v);
+    else              ((float *) c.dst[n])[m] = v;
 }
 
 template <int TYPE, int N>
 __global__ void __launch_bounds__(128)
-k_mul_mat_vec_q(QPlanes w, int64_t M, int64_t nbk, const float * __restrict__ x, int64_t x_stride,
-                void * __restrict__ dst, int64_t ldd, int rows_per_warp, EpDev ep) {
+k_mul_mat_vec_q(QPlanes w, int64_t M, int64_t nbk, GemvCols cols, int rows_per_warp, GemvEp ep) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int PSTR = 32 * 8 + 8;                 // padded per-column stride of P
     const int K = (int) nbk * 32;
@@ -347,42 +351,13 @@ k_mul_mat_vec_q(QPlanes w, int64_t M, int64_t nbk, const float * __restrict__ x,
     float * P   = sDw + 32;                                          // [N][PSTR]
     float * D   = P + N * PSTR;                                      // [N][32]
 
-    // quantise the activation columns (whole CTA): every thread fetches float4 pieces up front (all loads in
-    // flight at once), eight consecutive lanes hold one 32-block and share its maximum by shuffles.
-    for (int n = 0; n < N; ++n) {
-        const float * xr = (const float *) ((const char *) x + (size_t) n * x_stride);
-        for (int base = 0; base < K; base += 128 * 4 * 8) {
-            float4 v[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int e = base + (u * 128 + threadIdx.x) * 4;
-                v[u] = e < K ? *(const float4 *) (xr + e) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int e = base + (u * 128 + threadIdx.x) * 4;
-                float amax = fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w)));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-                if (e < K) {
-                    const float id = (amax != 0.0f) ? __fdiv_rn(127.f, amax) : 0.0f;
-                    const int q0 = __float2int_rn(__fmul_rn(v[u].x, id)), q1 = __float2int_rn(__fmul_rn(v[u].y, id));
-                    const int q2 = __float2int_rn(__fmul_rn(v[u].z, id)), q3 = __float2int_rn(__fmul_rn(v[u].w, id));
-                    Xq[(size_t) n * (K / 4) + (e >> 2)] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
-                    if ((threadIdx.x & 7) == 0) Xd[n * nbk + (e >> 5)] = round_f16(__fdiv_rn(amax, 127.f));
-                }
-            }
-        }
-    }
-    __syncthreads();
-
     const int j = lane & 7, bsub = lane >> 3, cn = lane >> 3;
     const int64_t row0 = ((int64_t) blockIdx.x * 4 + warp) * rows_per_warp;
     const int n_chunks = ((int) nbk + 31) / 32;
     const int64_t rows_here = min((int64_t) rows_per_warp, M - row0);
 
-    // weight blocks are fetched one (row, chunk) ahead of the arithmetic
+    // weight blocks are fetched one (row, chunk) ahead of the arithmetic; the first fetch overlaps the
+    // activation quantisation below
     uint4 pa = make_uint4(0, 0, 0, 0), pb = make_uint4(0, 0, 0, 0);
     uint32_t pqh = 0;
     float pdw = 0.0f;
@@ -397,6 +372,40 @@ k_mul_mat_vec_q(QPlanes w, int64_t M, int64_t nbk, const float * __restrict__ x,
         }
     };
     if (rows_here > 0) prefetch(row0, 0);
+
+    // quantise the activation columns (whole CTA): every thread fetches float4 pieces up front (four loads in
+    // flight per column), eight consecutive lanes hold one 32-block and share its maximum by shuffles.
+    const int n_it = (K + 511) / 512;
+#pragma unroll
+    for (int n = 0; n < N; ++n) {
+        const float * xr = cols.x[n];
+        for (int u0 = 0; u0 < n_it; u0 += 4) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int e = ((u0 + u) * 128 + threadIdx.x) * 4;
+                v[u] = e < K ? *(const float4 *) (xr + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int e = ((u0 + u) * 128 + threadIdx.x) * 4;
+                if (u0 + u < n_it) {            // uniform over the CTA
+                    float amax = fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w)));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                    amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                    if (e < K) {
+                        const float id = (amax != 0.0f) ? __fdiv_rn(127.f, amax) : 0.0f;
+                        const int q0 = __float2int_rn(__fmul_rn(v[u].x, id)), q1 = __float2int_rn(__fmul_rn(v[u].y, id));
+                        const int q2 = __float2int_rn(__fmul_rn(v[u].z, id)), q3 = __float2int_rn(__fmul_rn(v[u].w, id));
+                        Xq[(size_t) n * (K / 4) + (e >> 2)] = (q0 & 0xff) | ((q1 & 0xff) << 8) | ((q2 & 0xff) << 16) | ((q3 & 0xff) << 24);
+                        if ((threadIdx.x & 7) == 0) Xd[n * nbk + (e >> 5)] = round_f16(__fdiv_rn(amax, 127.f));
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
 
     for (int r = 0; r < rows_here; ++r) {
         const int64_t m = row0 + r;
@@ -456,14 +465,14 @@ k_mul_mat_vec_q(QPlanes w, int64_t M, int64_t nbk, const float * __restrict__ x,
             acc1 = __fadd_rn(acc1, __shfl_xor_sync(0xffffffffu, acc1, o));
         }
         if (j == 0) {
-            if (cn < N) ep_store(ep, dst, ldd, cn, m, acc0);
-            if (N > 4 && cn + 4 < N) ep_store(ep, dst, ldd, cn + 4, m, acc1);
+            if (cn < N) ep_store(ep, cols, cn, m, acc0);
+            if (N > 4 && cn + 4 < N) ep_store(ep, cols, cn + 4, m, acc1);
         }
     }
 }
 
 template <int TYPE, int N>
-static int launch_vec(const QPlanes & w, int64_t M, int64_t nbk, const float * x, int64_t xs, void * dst, int64_t ldd, const EpDev & ep, cudaStream_t st) {
+static int launch_vec(const QPlanes & w, int64_t M, int64_t nbk, const GemvCols & cols, const GemvEp & ep, cudaStream_t st) {
     constexpr int PSTR = 32 * 8 + 8;
     const size_t smem = (((size_t) N * nbk * 32 + (size_t) N * nbk * 4 + 15) & ~(size_t) 15) + 4 * (size_t) ((32 * 12 + 32 + N * PSTR + N * 32) * 4);
     static bool attr_done[64] = {false};   // per instantiation and device; benign race (idempotent call)
@@ -474,57 +483,97 @@ static int launch_vec(const QPlanes & w, int64_t M, int64_t nbk, const float * x
         attr_done[dev] = true;
     }
     if (smem > 200 * 1024) return B200_ERR_ARG;
-    // rows per warp: keep at least ~4 CTAs per SM worth of blocks when M allows it
+    // rows per warp: one wave of CTAs when M allows it (148 SMs x several CTAs), more rows per warp for tall matrices
     int rpw = 1;
     while (rpw < 8 && (M + 4 * (rpw * 2) - 1) / (4 * (rpw * 2)) >= 148 * 4) rpw *= 2;
     const int64_t rows_per_cta = 4 * rpw;
-    k_mul_mat_vec_q<TYPE, N><<<(unsigned) ((M + rows_per_cta - 1) / rows_per_cta), 128, smem, st>>>(w, M, nbk, x, xs, dst, ldd, rpw, ep);
+    k_mul_mat_vec_q<TYPE, N><<<(unsigned) ((M + rows_per_cta - 1) / rows_per_cta), 128, smem, st>>>(w, M, nbk, cols, rpw, ep);
     B200_RETURN_LAST();
 }
 
 template <int TYPE>
-static int launch_vec_n(int N, const QPlanes & w, int64_t M, int64_t nbk, const float * x, int64_t xs, void * dst, int64_t ldd, const EpDev & ep, cudaStream_t st) {
+static int launch_vec_n(int N, const QPlanes & w, int64_t M, int64_t nbk, const GemvCols & cols, const GemvEp & ep, cudaStream_t st) {
     switch (N) {
-        case 1: return launch_vec<TYPE, 1>(w, M, nbk, x, xs, dst, ldd, ep, st);
-        case 2: return launch_vec<TYPE, 2>(w, M, nbk, x, xs, dst, ldd, ep, st);
-        case 3: return launch_vec<TYPE, 3>(w, M, nbk, x, xs, dst, ldd, ep, st);
-        case 4: return launch_vec<TYPE, 4>(w, M, nbk, x, xs, dst, ldd, ep, st);
-        case 5: return launch_vec<TYPE, 5>(w, M, nbk, x, xs, dst, ldd, ep, st);
-        case 6: return launch_vec<TYPE, 6>(w, M, nbk, x, xs, dst, ldd, ep, st);
-        case 7: return launch_vec<TYPE, 7>(w, M, nbk, x, xs, dst, ldd, ep, st);
-        case 8: return launch_vec<TYPE, 8>(w, M, nbk, x, xs, dst, ldd, ep, st);
+        case 1: return launch_vec<TYPE, 1>(w, M, nbk, cols, ep, st);
+        case 2: return launch_vec<TYPE, 2>(w, M, nbk, cols, ep, st);
+        case 3: return launch_vec<TYPE, 3>(w, M, nbk, cols, ep, st);
+        case 4: return launch_vec<TYPE, 4>(w, M, nbk, cols, ep, st);
+        case 5: return launch_vec<TYPE, 5>(w, M, nbk, cols, ep, st);
+        case 6: return launch_vec<TYPE, 6>(w, M, nbk, cols, ep, st);
+        case 7: return launch_vec<TYPE, 7>(w, M, nbk, cols, ep, st);
+        case 8: return launch_vec<TYPE, 8>(w, M, nbk, cols, ep, st);
     }
     return B200_ERR_ARG;
 }
 
 const uint16_t * b200_gelu_table_device(int * err);
 
-extern "C" int b200_mul_mat_vec_q_ep(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
-                                     const float * x, int64_t x_stride_bytes, int64_t N,
-                                     void * dst, int64_t dst_stride, const b200_epilogue * ep, void * stream) {
-    if (K % 32 != 0 || M <= 0 || N < 1 || N > 8) return B200_ERR_ARG;
-    if (((uintptr_t) w_planes & 15) != 0 || ((uintptr_t) x & 15) != 0 || (x_stride_bytes & 15) != 0) return B200_ERR_ARG;
-    const int64_t nbk = K / 32;
-    if (M * nbk > nb_total) return B200_ERR_ARG;
-    EpDev e;
+static int fill_ep(GemvEp & e, int n_steps, const int * kind, const float * scalar, int store_f16) {
     memset(&e, 0, sizeof(e));
-    if (ep) {
-        if (ep->n_steps < 0 || ep->n_steps > 4) return B200_ERR_ARG;
-        e.n_steps = ep->n_steps;
-        e.store_f16 = ep->store_f16;
-        for (int s = 0; s < ep->n_steps; ++s) {
-            e.kind[s] = ep->step[s].kind; e.ptr[s] = ep->step[s].ptr; e.stride_n[s] = ep->step[s].stride_n; e.scalar[s] = ep->step[s].scalar;
-            if (e.kind[s] == B200_EP_GELU && !e.gelu_table) {
+    if (n_steps < 0 || n_steps > 4) return B200_ERR_ARG;
+    e.n_steps = n_steps;
+    e.store_f16 = store_f16;
+    for (int s = 0; s < n_steps; ++s) {
+        e.kind[s] = kind[s]; e.scalar[s] = scalar[s];
+        if (e.kind[s] == B200_EP_GELU) {
+            if (!e.gelu_table) {
                 int err = 0;
                 e.gelu_table = b200_gelu_table_device(&err);
                 if (err) return err;
-            } else if (e.kind[s] != B200_EP_ADD && e.kind[s] != B200_EP_SCALE && e.kind[s] != B200_EP_GELU) return B200_ERR_ARG;
+            }
+        } else if (e.kind[s] != B200_EP_ADD && e.kind[s] != B200_EP_SCALE) return B200_ERR_ARG;
+    }
+    return 0;
+}
+
+extern "C" int b200_mul_mat_vec_q_cols(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                                       const b200_gemv_col * cols, int n_cols, const b200_gemv_ep * ep, void * stream) {
+    if (K % 32 != 0 || M <= 0 || n_cols < 1 || n_cols > 8 || !cols) return B200_ERR_ARG;
+    if (((uintptr_t) w_planes & 15) != 0) return B200_ERR_ARG;
+    const int64_t nbk = K / 32;
+    if (M * nbk > nb_total) return B200_ERR_ARG;
+    GemvEp e;
+    static const int   no_kind[4]   = {0, 0, 0, 0};
+    static const float no_scalar[4] = {0, 0, 0, 0};
+    int rc = ep ? fill_ep(e, ep->n_steps, ep->kind, ep->scalar, ep->store_f16) : fill_ep(e, 0, no_kind, no_scalar, 0);
+    if (rc) return rc;
+    GemvCols c;
+    memset(&c, 0, sizeof(c));
+    for (int n = 0; n < n_cols; ++n) {
+        if (((uintptr_t) cols[n].x & 15) != 0 || !cols[n].dst) return B200_ERR_ARG;
+        c.x[n] = cols[n].x; c.dst[n] = cols[n].dst;
+        for (int s = 0; s < e.n_steps; ++s) {
+            c.add[s][n] = cols[n].add[s];
+            if (e.kind[s] == B200_EP_ADD && !c.add[s][n]) return B200_ERR_ARG;
         }
     }
     const QPlanes w = q_planes(wtype, w_planes, nb_total);
-    if (wtype == B200_TYPE_Q5_0) return launch_vec_n<B200_TYPE_Q5_0>((int) N, w, M, nbk, x, x_stride_bytes, dst, dst_stride, e, as_stream(stream));
-    if (wtype == B200_TYPE_Q8_0) return launch_vec_n<B200_TYPE_Q8_0>((int) N, w, M, nbk, x, x_stride_bytes, dst, dst_stride, e, as_stream(stream));
+    if (wtype == B200_TYPE_Q5_0) return launch_vec_n<B200_TYPE_Q5_0>(n_cols, w, M, nbk, c, e, as_stream(stream));
+    if (wtype == B200_TYPE_Q8_0) return launch_vec_n<B200_TYPE_Q8_0>(n_cols, w, M, nbk, c, e, as_stream(stream));
     return B200_ERR_ARG;
+}
+
+extern "C" int b200_mul_mat_vec_q_ep(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                                     const float * x, int64_t x_stride_bytes, int64_t N,
+                                     void * dst, int64_t dst_stride, const b200_epilogue * ep, void * stream) {
+    if (N < 1 || N > 8 || (x_stride_bytes & 15) != 0) return B200_ERR_ARG;
+    b200_gemv_col cols[8];
+    b200_gemv_ep  e;
+    memset(&e, 0, sizeof(e));
+    memset(cols, 0, sizeof(cols));
+    if (ep) {
+        if (ep->n_steps < 0 || ep->n_steps > 4) return B200_ERR_ARG;
+        e.n_steps = ep->n_steps; e.store_f16 = ep->store_f16;
+        for (int s = 0; s < ep->n_steps; ++s) { e.kind[s] = ep->step[s].kind; e.scalar[s] = ep->step[s].scalar; }
+    }
+    const int64_t esz = (ep && ep->store_f16) ? 2 : 4;
+    for (int n = 0; n < (int) N; ++n) {
+        cols[n].x   = (const float *) ((const char *) x + n * x_stride_bytes);
+        cols[n].dst = (char *) dst + n * dst_stride * esz;
+        for (int s = 0; ep && s < ep->n_steps; ++s)
+            cols[n].add[s] = ep->step[s].ptr ? ep->step[s].ptr + n * ep->step[s].stride_n : nullptr;
+    }
+    return b200_mul_mat_vec_q_cols(wtype, w_planes, nb_total, M, K, cols, (int) N, &e, stream);
 }
 
 extern "C" int b200_mul_mat_vec_q(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
