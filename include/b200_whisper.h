@@ -87,6 +87,11 @@ int b200_mul_mat_vec_q_ep(int wtype, const void * w_planes, int64_t nb_total, in
                           const float * x, int64_t x_stride_bytes, int64_t N,
                           void * dst, int64_t dst_stride, const b200_epilogue * ep, void * stream);
 
+/* b200_mul_mat_q with the same epilogue steps applied to every product value (encoder and prompt path). */
+int b200_mul_mat_q_ep(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                      const int8_t * xq, const float * xd, int64_t N,
+                      void * dst, int64_t dst_stride, const b200_epilogue * ep, void * stream);
+
 /* The same kernel with every column described on its own: column n reads x (K floats, 16-byte aligned), writes
  * dst (M f32, or M f16 when store_f16) and adds add[s] (M floats) at epilogue step s when kind[s] == B200_EP_ADD.
  * This is how single-token decode steps of several whisper_states that run in lock-step share one pass over

@@ -439,7 +439,7 @@ static bool only_feeds(const graph_info & gi, const struct ggml_tensor * t, int 
     return gi.uses[pos] == 1 && !(t->flags & GGML_TENSOR_FLAG_OUTPUT);
 }
 
-enum plan_kind { PK_NODE = 0, PK_LAYER_NORM, PK_GEMV, PK_FA_DECODE };
+enum plan_kind { PK_NODE = 0, PK_LAYER_NORM, PK_GEMV, PK_FA_DECODE, PK_GEMM };
 
 struct plan_item {
     int kind;
@@ -488,8 +488,8 @@ static void build_plan(struct ggml_cgraph * g, exec_plan & plan, bool fuse) {
                 it.kind = PK_LAYER_NORM; it.last = i + 2;
                 fused[i + 1] = 1; fused[i + 2] = 1;
             }
-        } else if (node->op == GGML_OP_MUL_MAT && is_quant(node->src[0]->type) && node->src[1]->ne[1] <= 8) {
-            it.kind = PK_GEMV;
+        } else if (node->op == GGML_OP_MUL_MAT && is_quant(node->src[0]->type)) {
+            it.kind = node->src[1]->ne[1] <= 8 ? PK_GEMV : PK_GEMM;
             if (fuse) {
                 struct ggml_tensor * cur = node;
                 const int64_t M = node->ne[0], N = node->ne[1];
@@ -570,8 +570,8 @@ static bool graph_fits_plan(const exec_plan & plan, struct ggml_cgraph * g) {
             // rows are read and written by the same threads, so exact in-place is fine; a shifted overlap is not
             if (overlaps(out, x) && !(out->data == x->data && out->nb[1] == x->nb[1])) return false;
             if (!b200_op_supported(mul) || !b200_op_supported(out)) return false;
-        } else if (it.kind == PK_GEMV) {
-            if (node->op != GGML_OP_MUL_MAT || !is_quant(node->src[0]->type) || node->src[1]->ne[1] > 8) return false;
+        } else if (it.kind == PK_GEMV || it.kind == PK_GEMM) {
+            if (node->op != GGML_OP_MUL_MAT || !is_quant(node->src[0]->type) || (node->src[1]->ne[1] > 8) != (it.kind == PK_GEMM)) return false;
             struct ggml_tensor * out = ggml_graph_node(g, it.last);
             const struct ggml_tensor * cur = node;
             for (int s = 0; s < it.n_steps; ++s) {
@@ -589,8 +589,9 @@ static bool graph_fits_plan(const exec_plan & plan, struct ggml_cgraph * g) {
                 cur = t;
             }
             if (it.store_f16 && (out->op != GGML_OP_CPY || out->src[0] != cur || out->type != GGML_TYPE_F16)) return false;
-            // every CTA reads the activations for the whole kernel: the result must not land on them
-            if (it.last != it.node && overlaps(out, node->src[1])) return false;
+            // GEMV: every CTA reads the activations for the whole kernel, the result must not land on them
+            // (the GEMM path reads a quantised copy made before the product starts)
+            if (it.kind == PK_GEMV && it.last != it.node && overlaps(out, node->src[1])) return false;
         } else if (it.kind == PK_FA_DECODE) {
             if (!is_decode_attention(node)) return false;
         }
@@ -723,6 +724,38 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
             }
         }
         return flush();
+    }
+    if (it.kind == PK_GEMM) {
+        for (int g = 0; g < n_g; ++g) {
+            struct ggml_tensor * mm = ggml_graph_node(gs[g], it.node), * out = ggml_graph_node(gs[g], it.last);
+            const struct ggml_tensor * w = mm->src[0], * x = mm->src[1];
+            const int64_t K = w->ne[0], M = w->ne[1], N = x->ne[1];
+            const int64_t nb_total = (int64_t) (ggml_nbytes(w) / ggml_type_size(w->type));
+            b200_epilogue ep;
+            memset(&ep, 0, sizeof(ep));
+            ep.n_steps = it.n_steps; ep.store_f16 = it.store_f16;
+            for (int s = 0; s < it.n_steps; ++s) {
+                struct ggml_tensor * t = ggml_graph_node(gs[g], it.step_node[s]);
+                ep.step[s].kind = it.step_kind[s];
+                if (it.step_kind[s] == B200_EP_SCALE) memcpy(&ep.step[s].scalar, t->op_params, sizeof(float));
+                if (it.step_kind[s] == B200_EP_ADD) {
+                    const struct ggml_tensor * o = t->src[it.step_src[s]];
+                    ep.step[s].ptr = (const float *) o->data;
+                    ep.step[s].stride_n = o->ne[1] == 1 ? 0 : (int64_t) o->nb[1] / 4;
+                }
+            }
+            const size_t q_bytes = (size_t) N * K, d_bytes = (size_t) N * (K / 32) * 4;
+            const size_t q_pad = (q_bytes + 255) & ~(size_t) 255;
+            if (!ensure_scratch(ctx, q_pad + d_bytes)) return (int) cudaErrorMemoryAllocation;
+            int8_t * xq = (int8_t *) ctx->scratch;
+            float *  xd = (float *) ((char *) ctx->scratch + q_pad);
+            int e = b200_quantize_q8_0((const float *) x->data, N, K, (int64_t) x->nb[1], xq, xd, st);
+            if (e) return e;
+            const int64_t ldd = it.store_f16 ? M : (int64_t) out->nb[1] / 4;
+            e = b200_mul_mat_q_ep((int) w->type, w->data, nb_total, M, K, xq, xd, N, out->data, ldd, &ep, st);
+            if (e) return e;
+        }
+        return 0;
     }
     // PK_FA_DECODE
     {

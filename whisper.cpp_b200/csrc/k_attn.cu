@@ -61,134 +61,176 @@ __device__ __forceinline__ float expf_glibc(float x) {
 }
 
 // ---- flash attention ------------------------------------------------------------------------
-// One warp per (query row, head).  Per 32 keys: every lane computes one score with the exact
-// reduction tree, a prefix maximum tells each key the running maximum it meets, exp() runs in
-// parallel, and the 64-wide F16 accumulator (two dims per lane) is then updated key by key.
-template <bool S_FMA>
+// Many query rows (encoder, prompts): a warp owns FA_R consecutive query rows of one head.  Per 32 keys: every lane
+// loads one key row once and scores it against the FA_R queries with the exact reduction tree, a prefix maximum per
+// query tells each key the running maximum it meets, exp() runs in parallel, then the 64-wide F16 accumulators
+// (two dims per lane, FA_R independent chains) are updated key by key.  HAS_SKIP = a mask is present or the key count
+// is not a multiple of 32; without it the per-key "skipped" handling is compiled out.
+#define FA_R 4
+template <bool S_FMA, bool HAS_SKIP>
 __global__ void __launch_bounds__(128)
 k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
                  const char * __restrict__ k, int64_t nbk1, int64_t nbk2,
                  const char * __restrict__ v, int64_t nbv1, int64_t nbv2,
                  const char * __restrict__ mask, int64_t nbm1,
                  float * __restrict__ dst, int64_t n_q, int64_t n_kv, int64_t n_head, float scale) {
-    __shared__ __align__(16) float Qs[4][64];
+    __shared__ __align__(16) float Qs[4][FA_R][64];
+    __shared__ __align__(16) float MS[4][FA_R][32];
+    __shared__ __align__(16) float VS[4][FA_R][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int64_t iq1 = (int64_t) blockIdx.x * 4 + warp;
-    const int64_t h   = blockIdx.y;
-    if (iq1 >= n_q) return;
+    const int64_t row0 = ((int64_t) blockIdx.x * 4 + warp) * FA_R;
+    const int64_t h    = blockIdx.y;
+    if (row0 >= n_q) return;
+    const int n_rows = (int) min((int64_t) FA_R, n_q - row0);
 
-    {
-        const float * qp = (const float *) (q + iq1 * nbq1 + h * nbq2);
-        Qs[warp][lane]      = round_f16(qp[lane]);
-        Qs[warp][lane + 32] = round_f16(qp[lane + 32]);
+#pragma unroll
+    for (int r = 0; r < FA_R; ++r) {
+        const int64_t iq = min(row0 + r, n_q - 1);             // rows past the end repeat the last one and are not stored
+        const float * qp = (const float *) (q + iq * nbq1 + h * nbq2);
+        Qs[warp][r][lane]      = round_f16(qp[lane]);
+        Qs[warp][r][lane + 32] = round_f16(qp[lane + 32]);
     }
     __syncwarp();
 
     const char * kh = k + h * nbk2;
     const char * vh = v + h * nbv2;
-    const __half * mp = mask ? (const __half *) (mask + iq1 * nbm1) : nullptr;
 
-    float M = -INFINITY, S = 0.0f;
-    float a0 = 0.0f, a1 = 0.0f;      // F16 accumulator values for dims 2*lane, 2*lane+1
+    float M[FA_R], S[FA_R], a0[FA_R], a1[FA_R];
+#pragma unroll
+    for (int r = 0; r < FA_R; ++r) { M[r] = -INFINITY; S[r] = 0.0f; a0[r] = 0.0f; a1[r] = 0.0f; }
 
     for (int64_t ic0 = 0; ic0 < n_kv; ic0 += 32) {
         const int64_t ic = ic0 + lane;
-        const bool valid = ic < n_kv;
-        float mv = 0.0f;
-        if (mp && valid) mv = __half2float(mp[ic]);
-        const bool skip = !valid || (mv == -INFINITY);
-
-        float s = -INFINITY;
-        if (!skip) {
-            float acc[32];
+        const bool valid = !HAS_SKIP || ic < n_kv;
+        uint4 kreg[8];
+        if (valid) {
             const uint4 * kp = (const uint4 *) (kh + ic * nbk1);
 #pragma unroll
-            for (int step = 0; step < 2; ++step) {
+            for (int c = 0; c < 8; ++c) kreg[c] = kp[c];
+        } else {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint4 kv = kp[step * 4 + c];
-                    const float4 qa = *(const float4 *) &Qs[warp][step * 32 + c * 8];
-                    const float4 qb = *(const float4 *) &Qs[warp][step * 32 + c * 8 + 4];
-                    const float2 k0 = __half22float2(*(const __half2 *) &kv.x);
-                    const float2 k1 = __half22float2(*(const __half2 *) &kv.y);
-                    const float2 k2 = __half22float2(*(const __half2 *) &kv.z);
-                    const float2 k3 = __half22float2(*(const __half2 *) &kv.w);
-                    float * a = &acc[c * 8];
-                    if (step == 0) {
-                        a[0] = __fmaf_rn(k0.x, qa.x, 0.0f); a[1] = __fmaf_rn(k0.y, qa.y, 0.0f);
-                        a[2] = __fmaf_rn(k1.x, qa.z, 0.0f); a[3] = __fmaf_rn(k1.y, qa.w, 0.0f);
-                        a[4] = __fmaf_rn(k2.x, qb.x, 0.0f); a[5] = __fmaf_rn(k2.y, qb.y, 0.0f);
-                        a[6] = __fmaf_rn(k3.x, qb.z, 0.0f); a[7] = __fmaf_rn(k3.y, qb.w, 0.0f);
-                    } else {
-                        a[0] = __fmaf_rn(k0.x, qa.x, a[0]); a[1] = __fmaf_rn(k0.y, qa.y, a[1]);
-                        a[2] = __fmaf_rn(k1.x, qa.z, a[2]); a[3] = __fmaf_rn(k1.y, qa.w, a[3]);
-                        a[4] = __fmaf_rn(k2.x, qb.x, a[4]); a[5] = __fmaf_rn(k2.y, qb.y, a[5]);
-                        a[6] = __fmaf_rn(k3.x, qb.z, a[6]); a[7] = __fmaf_rn(k3.y, qb.w, a[7]);
+            for (int c = 0; c < 8; ++c) kreg[c] = make_uint4(0, 0, 0, 0);
+        }
+        unsigned evt_any = 0;
+#pragma unroll
+        for (int r = 0; r < FA_R; ++r) {
+            float mv = 0.0f;
+            bool skip = !valid;
+            if (HAS_SKIP && mask && valid) {
+                const int64_t iq = min(row0 + r, n_q - 1);
+                mv = __half2float(((const __half *) (mask + iq * nbm1))[ic]);
+                skip = (mv == -INFINITY);
+            }
+            float s = -INFINITY;
+            if (!skip) {
+                float acc[32];
+#pragma unroll
+                for (int step = 0; step < 2; ++step) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const uint4 kv = kreg[step * 4 + c];
+                        const float4 qa = *(const float4 *) &Qs[warp][r][step * 32 + c * 8];
+                        const float4 qb = *(const float4 *) &Qs[warp][r][step * 32 + c * 8 + 4];
+                        const float2 k0 = __half22float2(*(const __half2 *) &kv.x);
+                        const float2 k1 = __half22float2(*(const __half2 *) &kv.y);
+                        const float2 k2 = __half22float2(*(const __half2 *) &kv.z);
+                        const float2 k3 = __half22float2(*(const __half2 *) &kv.w);
+                        float * a = &acc[c * 8];
+                        if (step == 0) {
+                            a[0] = __fmaf_rn(k0.x, qa.x, 0.0f); a[1] = __fmaf_rn(k0.y, qa.y, 0.0f);
+                            a[2] = __fmaf_rn(k1.x, qa.z, 0.0f); a[3] = __fmaf_rn(k1.y, qa.w, 0.0f);
+                            a[4] = __fmaf_rn(k2.x, qb.x, 0.0f); a[5] = __fmaf_rn(k2.y, qb.y, 0.0f);
+                            a[6] = __fmaf_rn(k3.x, qb.z, 0.0f); a[7] = __fmaf_rn(k3.y, qb.w, 0.0f);
+                        } else {
+                            a[0] = __fmaf_rn(k0.x, qa.x, a[0]); a[1] = __fmaf_rn(k0.y, qa.y, a[1]);
+                            a[2] = __fmaf_rn(k1.x, qa.z, a[2]); a[3] = __fmaf_rn(k1.y, qa.w, a[3]);
+                            a[4] = __fmaf_rn(k2.x, qb.x, a[4]); a[5] = __fmaf_rn(k2.y, qb.y, a[5]);
+                            a[6] = __fmaf_rn(k3.x, qb.z, a[6]); a[7] = __fmaf_rn(k3.y, qb.w, a[7]);
+                        }
                     }
                 }
+                float y[8];
+#pragma unroll
+                for (int p = 0; p < 8; ++p)
+                    y[p] = __fadd_rn(__fadd_rn(acc[p], acc[16 + p]), __fadd_rn(acc[8 + p], acc[24 + p]));
+                const float t0 = __fadd_rn(y[0], y[4]), t1 = __fadd_rn(y[1], y[5]);
+                const float t2 = __fadd_rn(y[2], y[6]), t3 = __fadd_rn(y[3], y[7]);
+                s = __fadd_rn(__fadd_rn(t0, t1), __fadd_rn(t2, t3));
+                s = __fmul_rn(s, scale);
+                s = __fadd_rn(s, mv);
             }
-            float y[8];
+            // running maximum seen by each key (exclusive prefix over non-skipped keys; skipped keys carry -inf)
+            float pm = s;
 #pragma unroll
-            for (int p = 0; p < 8; ++p)
-                y[p] = __fadd_rn(__fadd_rn(acc[p], acc[16 + p]), __fadd_rn(acc[8 + p], acc[24 + p]));
-            const float t0 = __fadd_rn(y[0], y[4]), t1 = __fadd_rn(y[1], y[5]);
-            const float t2 = __fadd_rn(y[2], y[6]), t3 = __fadd_rn(y[3], y[7]);
-            s = __fadd_rn(__fadd_rn(t0, t1), __fadd_rn(t2, t3));
-            s = __fmul_rn(s, scale);
-            s = __fadd_rn(s, mv);
+            for (int o = 1; o < 32; o <<= 1) {
+                const float t = __shfl_up_sync(0xffffffffu, pm, o);
+                if (lane >= o) pm = fmaxf(pm, t);
+            }
+            float ex = __shfl_up_sync(0xffffffffu, pm, 1);
+            if (lane == 0) ex = -INFINITY;
+            const float Mprev  = fmaxf(M[r], ex);
+            const bool  newmax = !skip && (s > Mprev);
+            float e = 1.0f;
+            if (!skip) e = expf_glibc(newmax ? __fadd_rn(Mprev, -s) : __fadd_rn(s, -Mprev));
+            MS[warp][r][lane] = newmax ? e : 1.0f;
+            VS[warp][r][lane] = skip ? -0.0f : (newmax ? 1.0f : e);
+            if (__ballot_sync(0xffffffffu, newmax)) evt_any |= 1u << r;
+            M[r] = fmaxf(M[r], __shfl_sync(0xffffffffu, pm, 31));
         }
+        __syncwarp();
 
-        // running maximum seen by each key (exclusive prefix over non-skipped keys)
-        float pm = s;   // skipped keys carry -inf
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const float t = __shfl_up_sync(0xffffffffu, pm, o);
-            if (lane >= o) pm = fmaxf(pm, t);
-        }
-        float ex = __shfl_up_sync(0xffffffffu, pm, 1);
-        if (lane == 0) ex = -INFINITY;
-        const float Mprev  = fmaxf(M, ex);
-        const bool  newmax = !skip && (s > Mprev);
-        float e = 1.0f;
-        if (!skip) e = expf_glibc(newmax ? __fadd_rn(Mprev, -s) : __fadd_rn(s, -Mprev));
-        const float ms_l = newmax ? e : 1.0f;
-        const float vs_l = newmax ? 1.0f : e;
-        const unsigned skipmask = __ballot_sync(0xffffffffu, skip);
-        M = fmaxf(M, __shfl_sync(0xffffffffu, pm, 31));
-
-        const int nk = (int) min((int64_t) 32, n_kv - ic0);
+        // V rows of the 32 keys (two dims per lane), shared by the FA_R chains; reuse the key registers
         __half2 vraw[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-            if (i < nk && !((skipmask >> i) & 1u))
-                vraw[i] = *(const __half2 *) (vh + (ic0 + i) * nbv1 + lane * 4);
-            else
-                vraw[i] = __floats2half2_rn(0.0f, 0.0f);
+            if (!HAS_SKIP || ic0 + i < n_kv) vraw[i] = *(const __half2 *) (vh + (ic0 + i) * nbv1 + lane * 4);
+            else                             vraw[i] = __floats2half2_rn(0.0f, 0.0f);
         }
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const float ms = __shfl_sync(0xffffffffu, ms_l, i);
-            const float vs = __shfl_sync(0xffffffffu, vs_l, i);
-            if (i < nk && !((skipmask >> i) & 1u)) {
-                if (ms != 1.0f) {
-                    a0 = round_f16(__fmul_rn(a0, ms));
-                    a1 = round_f16(__fmul_rn(a1, ms));
+        for (int i0 = 0; i0 < 32; i0 += 4) {
+            float4 vs4[FA_R], ms4[FA_R];
+#pragma unroll
+            for (int r = 0; r < FA_R; ++r) {
+                vs4[r] = *(const float4 *) &VS[warp][r][i0];
+                ms4[r] = *(const float4 *) &MS[warp][r][i0];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float2 vf = __half22float2(vraw[i0 + u]);
+#pragma unroll
+                for (int r = 0; r < FA_R; ++r) {
+                    const float vs = u == 0 ? vs4[r].x : u == 1 ? vs4[r].y : u == 2 ? vs4[r].z : vs4[r].w;
+                    const float ms = u == 0 ? ms4[r].x : u == 1 ? ms4[r].y : u == 2 ? ms4[r].z : ms4[r].w;
+                    float vx = vf.x, vy = vf.y;
+                    if (HAS_SKIP && __float_as_uint(vs) == 0x80000000u) { vx = 0.0f; vy = 0.0f; }    // skipped key: exact no-op
+                    if ((evt_any >> r) & 1u) {
+                        if (ms != 1.0f) {
+                            a0[r] = round_f16(__fmul_rn(a0[r], ms));
+                            a1[r] = round_f16(__fmul_rn(a1[r], ms));
+                        }
+                        S[r] = S_FMA ? __fmaf_rn(S[r], ms, vs) : __fadd_rn(__fmul_rn(S[r], ms), vs);
+                    } else {
+                        S[r] = __fadd_rn(S[r], vs);          // ms == 1: fma(S, 1, vs) == S + vs
+                    }
+                    a0[r] = round_f16(__fmaf_rn(vx, vs, a0[r]));
+                    a1[r] = round_f16(__fmaf_rn(vy, vs, a1[r]));
                 }
-                const float2 vf = __half22float2(vraw[i]);
-                a0 = round_f16(__fmaf_rn(vf.x, vs, a0));
-                a1 = round_f16(__fmaf_rn(vf.y, vs, a1));
-                S = S_FMA ? __fmaf_rn(S, ms, vs) : __fadd_rn(__fmul_rn(S, ms), vs);
             }
         }
+        __syncwarp();
     }
 
-    const float S_inv = __fdiv_rn(1.0f, S);
-    float2 o;
-    o.x = __fmul_rn(a0, S_inv);
-    o.y = __fmul_rn(a1, S_inv);
-    *(float2 *) (dst + (iq1 * n_head + h) * 64 + lane * 2) = o;
+#pragma unroll
+    for (int r = 0; r < FA_R; ++r) {
+        if (r < n_rows) {
+            const float S_inv = __fdiv_rn(1.0f, S[r]);
+            float2 o;
+            o.x = __fmul_rn(a0[r], S_inv);
+            o.y = __fmul_rn(a1[r], S_inv);
+            *(float2 *) (dst + ((row0 + r) * n_head + h) * 64 + lane * 2) = o;
+        }
+    }
 }
-
 
 // Few query rows (token-by-token decode, beams, several decoder states stepping together): one CTA per
 // (query row, head).  The work of the kernel above is split by role so that the sequential part is as short as
@@ -459,13 +501,13 @@ extern "C" int b200_flash_attn_ext(const float * q, int64_t nbq1, int64_t nbq2,
         }
         return launch_fa_decode(r, (int) n_q, n_head, as_stream(stream));
     }
-    dim3 grid((unsigned) ((n_q + 3) / 4), (unsigned) n_head);
-    if (g_fa_s_fma)
-        k_flash_attn_ext<true><<<grid, 128, 0, as_stream(stream)>>>((const char *) q, nbq1, nbq2, (const char *) k, nbk1, nbk2,
-            (const char *) v, nbv1, nbv2, (const char *) mask, nbm1, dst, n_q, n_kv, n_head, scale);
-    else
-        k_flash_attn_ext<false><<<grid, 128, 0, as_stream(stream)>>>((const char *) q, nbq1, nbq2, (const char *) k, nbk1, nbk2,
-            (const char *) v, nbv1, nbv2, (const char *) mask, nbm1, dst, n_q, n_kv, n_head, scale);
+    dim3 grid((unsigned) ((n_q + 4 * FA_R - 1) / (4 * FA_R)), (unsigned) n_head);
+    const bool has_skip = mask != nullptr || (n_kv % 32) != 0;
+#define FA_LAUNCH(SF, HS) k_flash_attn_ext<SF, HS><<<grid, 128, 0, as_stream(stream)>>>((const char *) q, nbq1, nbq2, (const char *) k, nbk1, nbk2, \
+            (const char *) v, nbv1, nbv2, (const char *) mask, nbm1, dst, n_q, n_kv, n_head, scale)
+    if (g_fa_s_fma) { if (has_skip) FA_LAUNCH(true, true); else FA_LAUNCH(true, false); }
+    else            { if (has_skip) FA_LAUNCH(false, true); else FA_LAUNCH(false, false); }
+#undef FA_LAUNCH
     B200_RETURN_LAST();
 }
 

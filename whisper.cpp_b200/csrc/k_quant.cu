@@ -161,10 +161,33 @@ extern "C" int b200_quantize_q8_0(const float * x, int64_t n_rows, int64_t k, in
 #define MAGIC_I 0x4B400000          // bits of 12582912.0f: integer adds to it stay exact floats
 #define MAGIC_F 12582912.0f
 
+struct GemmEp {
+    int n_steps;
+    int kind[4];
+    const float * ptr[4];
+    int64_t stride_n[4];
+    float scalar[4];
+    int store_f16;
+    const uint16_t * gelu_table;
+};
+
+__device__ __forceinline__ void gemm_ep_store(const GemmEp & ep, void * dst, int64_t ldd, int64_t n, int64_t m, float v) {
+    for (int s = 0; s < ep.n_steps; ++s) {
+        if (ep.kind[s] == B200_EP_ADD)        v = __fadd_rn(v, ep.ptr[s][m + n * ep.stride_n[s]]);
+        else if (ep.kind[s] == B200_EP_SCALE) v = __fmul_rn(v, ep.scalar[s]);
+        else {
+            if (v <= -10.0f)     v = 0.0f;
+            else if (v < 10.0f)  v = __half2float(__ushort_as_half(ep.gelu_table[__half_as_ushort(__float2half_rn(v))]));
+        }
+    }
+    if (ep.store_f16) ((__half *) dst)[n * ldd + m] = __float2half_rn(v);
+    else              ((float *) dst)[n * ldd + m] = v;
+}
+
 template <int TYPE>
 __global__ void __launch_bounds__(256, 2)
 k_mul_mat_q(QPlanes w, int64_t M, int64_t nbk, const int8_t * __restrict__ xq, const float * __restrict__ xd,
-            int64_t N, float * __restrict__ dst, int64_t ldd) {
+            int64_t N, void * __restrict__ dst, int64_t ldd, GemmEp ep) {
     constexpr int BM = 64, BN = 32, KC = 4;
     __shared__ __align__(16) int   Ws[KC][8][BM + 4];
     __shared__ __align__(16) int   Xs[KC][8][BN + 4];
@@ -277,29 +300,51 @@ k_mul_mat_q(QPlanes w, int64_t M, int64_t nbk, const int8_t * __restrict__ xq, c
 #pragma unroll
                 for (int b = 0; b < 8; ++b) {
                     const int64_t n = n0 + gn * 8 + b;
-                    if (n < N) dst[n * ldd + m] = acc[a][b];
+                    if (n < N) gemm_ep_store(ep, dst, ldd, n, m, acc[a][b]);
                 }
             }
         }
     }
 }
 
-extern "C" int b200_mul_mat_q(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
-                              const int8_t * xq, const float * xd, int64_t N,
-                              float * dst, int64_t dst_stride, void * stream) {
+const uint16_t * b200_gelu_table_device(int * err);
+
+extern "C" int b200_mul_mat_q_ep(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                                 const int8_t * xq, const float * xd, int64_t N,
+                                 void * dst, int64_t dst_stride, const b200_epilogue * ep, void * stream) {
     if (K % 32 != 0 || M <= 0 || N <= 0) return B200_ERR_ARG;
     if (((uintptr_t) xq & 15) != 0 || ((uintptr_t) w_planes & 15) != 0) return B200_ERR_ARG;
     const int64_t nbk = K / 32;
     if (M * nbk > nb_total) return B200_ERR_ARG;
+    GemmEp e;
+    memset(&e, 0, sizeof(e));
+    if (ep) {
+        if (ep->n_steps < 0 || ep->n_steps > 4) return B200_ERR_ARG;
+        e.n_steps = ep->n_steps; e.store_f16 = ep->store_f16;
+        for (int s = 0; s < ep->n_steps; ++s) {
+            e.kind[s] = ep->step[s].kind; e.ptr[s] = ep->step[s].ptr; e.stride_n[s] = ep->step[s].stride_n; e.scalar[s] = ep->step[s].scalar;
+            if (e.kind[s] == B200_EP_GELU) {
+                if (!e.gelu_table) { int err = 0; e.gelu_table = b200_gelu_table_device(&err); if (err) return err; }
+            } else if (e.kind[s] == B200_EP_ADD) {
+                if (!e.ptr[s]) return B200_ERR_ARG;
+            } else if (e.kind[s] != B200_EP_SCALE) return B200_ERR_ARG;
+        }
+    }
     dim3 grid((unsigned) ((M + 63) / 64), (unsigned) ((N + 31) / 32));
     const QPlanes w = q_planes(wtype, w_planes, nb_total);
     if (wtype == B200_TYPE_Q5_0)
-        k_mul_mat_q<B200_TYPE_Q5_0><<<grid, 256, 0, as_stream(stream)>>>(w, M, nbk, xq, xd, N, dst, dst_stride);
+        k_mul_mat_q<B200_TYPE_Q5_0><<<grid, 256, 0, as_stream(stream)>>>(w, M, nbk, xq, xd, N, dst, dst_stride, e);
     else if (wtype == B200_TYPE_Q8_0)
-        k_mul_mat_q<B200_TYPE_Q8_0><<<grid, 256, 0, as_stream(stream)>>>(w, M, nbk, xq, xd, N, dst, dst_stride);
+        k_mul_mat_q<B200_TYPE_Q8_0><<<grid, 256, 0, as_stream(stream)>>>(w, M, nbk, xq, xd, N, dst, dst_stride, e);
     else
         return B200_ERR_ARG;
     B200_RETURN_LAST();
+}
+
+extern "C" int b200_mul_mat_q(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                              const int8_t * xq, const float * xd, int64_t N,
+                              float * dst, int64_t dst_stride, void * stream) {
+    return b200_mul_mat_q_ep(wtype, w_planes, nb_total, M, K, xq, xd, N, dst, dst_stride, nullptr, stream);
 }
 
 // ------------------------------------------------------------------------------------------------
