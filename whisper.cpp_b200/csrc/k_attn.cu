@@ -205,15 +205,15 @@ k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
                     if (HAS_SKIP && __float_as_uint(vs) == 0x80000000u) { vx = 0.0f; vy = 0.0f; }    // skipped key: exact no-op
                     if ((evt_any >> r) & 1u) {
                         if (ms != 1.0f) {
-                            a0[r] = round_f16(__fmul_rn(a0[r], ms));
-                            a1[r] = round_f16(__fmul_rn(a1[r], ms));
+                            const float2 t = __half22float2(__floats2half2_rn(__fmul_rn(a0[r], ms), __fmul_rn(a1[r], ms)));
+                            a0[r] = t.x; a1[r] = t.y;
                         }
                         S[r] = S_FMA ? __fmaf_rn(S[r], ms, vs) : __fadd_rn(__fmul_rn(S[r], ms), vs);
                     } else {
                         S[r] = __fadd_rn(S[r], vs);          // ms == 1: fma(S, 1, vs) == S + vs
                     }
-                    a0[r] = round_f16(__fmaf_rn(vx, vs, a0[r]));
-                    a1[r] = round_f16(__fmaf_rn(vy, vs, a1[r]));
+                    const float2 t = __half22float2(__floats2half2_rn(__fmaf_rn(vx, vs, a0[r]), __fmaf_rn(vy, vs, a1[r])));
+                    a0[r] = t.x; a1[r] = t.y;
                 }
             }
         }

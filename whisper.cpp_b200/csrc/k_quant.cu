@@ -171,17 +171,19 @@ struct GemmEp {
     const uint16_t * gelu_table;
 };
 
-__device__ __forceinline__ void gemm_ep_store(const GemmEp & ep, void * dst, int64_t ldd, int64_t n, int64_t m, float v) {
-    for (int s = 0; s < ep.n_steps; ++s) {
-        if (ep.kind[s] == B200_EP_ADD)        v = __fadd_rn(v, ep.ptr[s][m + n * ep.stride_n[s]]);
-        else if (ep.kind[s] == B200_EP_SCALE) v = __fmul_rn(v, ep.scalar[s]);
-        else {
-            if (v <= -10.0f)     v = 0.0f;
-            else if (v < 10.0f)  v = __half2float(__ushort_as_half(ep.gelu_table[__half_as_ushort(__float2half_rn(v))]));
+__device__ __forceinline__ float gemm_ep_apply(const GemmEp & ep, int64_t n, int64_t m, float v) {
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+        if (s < ep.n_steps) {
+            if (ep.kind[s] == B200_EP_ADD)        v = __fadd_rn(v, ep.ptr[s][m + n * ep.stride_n[s]]);
+            else if (ep.kind[s] == B200_EP_SCALE) v = __fmul_rn(v, ep.scalar[s]);
+            else {
+                if (v <= -10.0f)     v = 0.0f;
+                else if (v < 10.0f)  v = __half2float(__ushort_as_half(ep.gelu_table[__half_as_ushort(__float2half_rn(v))]));
+            }
         }
     }
-    if (ep.store_f16) ((__half *) dst)[n * ldd + m] = __float2half_rn(v);
-    else              ((float *) dst)[n * ldd + m] = v;
+    return v;
 }
 
 template <int TYPE>
@@ -189,10 +191,12 @@ __global__ void __launch_bounds__(256, 2)
 k_mul_mat_q(QPlanes w, int64_t M, int64_t nbk, const int8_t * __restrict__ xq, const float * __restrict__ xd,
             int64_t N, void * __restrict__ dst, int64_t ldd, GemmEp ep) {
     constexpr int BM = 64, BN = 32, KC = 4;
-    __shared__ __align__(16) int   Ws[KC][8][BM + 4];
-    __shared__ __align__(16) int   Xs[KC][8][BN + 4];
+    constexpr int WS_WORDS = KC * 8 * (BM + 4), XS_WORDS = KC * 8 * (BN + 4);
+    __shared__ __align__(16) int   smem_i[WS_WORDS + XS_WORDS];
     __shared__ __align__(16) float dWs[KC][BM];
     __shared__ __align__(16) float dXs[KC][BN];
+    int (*Ws)[8][BM + 4] = (int (*)[8][BM + 4]) smem_i;
+    int (*Xs)[8][BN + 4] = (int (*)[8][BN + 4]) (smem_i + WS_WORDS);
 
     const int tid = threadIdx.x;
     const int j   = tid & 7;
@@ -213,52 +217,57 @@ k_mul_mat_q(QPlanes w, int64_t M, int64_t nbk, const int8_t * __restrict__ xq, c
     const int     xc  = tid & 31;      // X staging: column in tile
     const int     xkb = (tid >> 5) & 3;
 
-    for (int64_t kb0 = 0; kb0 < nbk; kb0 += KC) {
-        {   // stage W (dequantised to int8 lane words)
-            int   wv[8];
-            float dw = 0.0f;
-#pragma unroll
-            for (int t = 0; t < 8; ++t) wv[t] = 0;
+    // the next chunk's blocks travel in registers while the current chunk is multiplied
+    uint4 pwa = make_uint4(0, 0, 0, 0), pwb = make_uint4(0, 0, 0, 0), pxa = make_uint4(0, 0, 0, 0), pxb = make_uint4(0, 0, 0, 0);
+    uint32_t pqh = 0;
+    float pdw = 0.0f, pdx = 0.0f;
+    auto fetch = [&](int64_t kb0) {
+        pwa = make_uint4(0, 0, 0, 0); pwb = pwa; pqh = 0; pdw = 0.0f;
+        {
             const int64_t m = m0 + sr, ib = kb0 + skb;
             if (m < M && ib < nbk) {
                 const int64_t blk = m * nbk + ib;
-                if (TYPE == B200_TYPE_Q5_0) {
-                    const uint4    q  = ((const uint4 *) w.qs)[blk];
-                    const uint32_t qh = w.qh[blk];
-                    const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-                    for (int t = 0; t < 8; ++t) wv[t] = q5_lane_word(qw[t & 3], qh, t);
-                } else {
-                    const uint4 a = ((const uint4 *) w.qs)[blk * 2], b = ((const uint4 *) w.qs)[blk * 2 + 1];
-                    wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w;
-                    wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
-                }
-                dw = __half2float(w.d[blk]);
+                if (TYPE == B200_TYPE_Q5_0) { pwa = ((const uint4 *) w.qs)[blk]; pqh = w.qh[blk]; }
+                else { pwa = ((const uint4 *) w.qs)[blk * 2]; pwb = ((const uint4 *) w.qs)[blk * 2 + 1]; }
+                pdw = __half2float(w.d[blk]);
             }
-#pragma unroll
-            for (int t = 0; t < 8; ++t) Ws[skb][t][sr] = wv[t];
-            dWs[skb][sr] = dw;
         }
-        if (tid < 128) {   // stage X
-            int   xv[8];
-            float dx = 0.0f;
-#pragma unroll
-            for (int t = 0; t < 8; ++t) xv[t] = 0;
+        if (tid < 128) {
+            pxa = make_uint4(0, 0, 0, 0); pxb = pxa; pdx = 0.0f;
             const int64_t n = n0 + xc, ib = kb0 + xkb;
             if (n < N && ib < nbk) {
                 const uint4 * p = (const uint4 *) (xq + (n * nbk + ib) * 32);
-                const uint4 a = p[0], b = p[1];
-                xv[0] = a.x; xv[1] = a.y; xv[2] = a.z; xv[3] = a.w;
-                xv[4] = b.x; xv[5] = b.y; xv[6] = b.z; xv[7] = b.w;
-                dx = xd[n * nbk + ib];
+                pxa = p[0]; pxb = p[1];
+                pdx = xd[n * nbk + ib];
+            }
+        }
+    };
+    fetch(0);
+
+    for (int64_t kb0 = 0; kb0 < nbk; kb0 += KC) {
+        {   // publish W (dequantised to int8 lane words) and X
+            int wv[8];
+            if (TYPE == B200_TYPE_Q5_0) {
+                const uint32_t qw[4] = {pwa.x, pwa.y, pwa.z, pwa.w};
+#pragma unroll
+                for (int t = 0; t < 8; ++t) wv[t] = q5_lane_word(qw[t & 3], pqh, t);
+            } else {
+                wv[0] = pwa.x; wv[1] = pwa.y; wv[2] = pwa.z; wv[3] = pwa.w;
+                wv[4] = pwb.x; wv[5] = pwb.y; wv[6] = pwb.z; wv[7] = pwb.w;
             }
 #pragma unroll
-            for (int t = 0; t < 8; ++t) Xs[xkb][t][xc] = xv[t];
-            dXs[xkb][xc] = dx;
+            for (int t = 0; t < 8; ++t) Ws[skb][t][sr] = wv[t];
+            dWs[skb][sr] = pdw;
+            if (tid < 128) {
+                Xs[xkb][0][xc] = pxa.x; Xs[xkb][1][xc] = pxa.y; Xs[xkb][2][xc] = pxa.z; Xs[xkb][3][xc] = pxa.w;
+                Xs[xkb][4][xc] = pxb.x; Xs[xkb][5][xc] = pxb.y; Xs[xkb][6][xc] = pxb.z; Xs[xkb][7][xc] = pxb.w;
+                dXs[xkb][xc] = pdx;
+            }
         }
         __syncthreads();
+        if (kb0 + KC < nbk) fetch(kb0 + KC);
 
-#pragma unroll
+#pragma unroll 2
         for (int kb = 0; kb < KC; ++kb) {
             int wv[8], xv[8];
             float dw[8], dx[8];
@@ -281,7 +290,7 @@ k_mul_mat_q(QPlanes w, int64_t M, int64_t nbk, const int8_t * __restrict__ xq, c
         __syncthreads();
     }
 
-    // hsum_float_8: (l0+l4, l1+l5, l2+l6, l3+l7) -> (+2) -> (+1)
+    // hsum_float_8: (l0+l4, l1+l5, l2+l6, l3+l7) -> (+2) -> (+1); afterwards all eight lanes hold the sum
 #pragma unroll
     for (int a = 0; a < 8; ++a)
 #pragma unroll
@@ -292,15 +301,28 @@ k_mul_mat_q(QPlanes w, int64_t M, int64_t nbk, const int8_t * __restrict__ xq, c
             v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
             acc[a][b] = v;
         }
+    // the tile goes through shared memory so that the epilogue reads and writes global memory in full rows
+    float (*Cs)[BM + 1] = (float (*)[BM + 1]) smem_i;          // [BN][BM+1], fits in the W staging area
 #pragma unroll
     for (int a = 0; a < 8; ++a) {
         if (a == j) {
-            const int64_t m = m0 + gm * 8 + a;
-            if (m < M) {
 #pragma unroll
-                for (int b = 0; b < 8; ++b) {
-                    const int64_t n = n0 + gn * 8 + b;
-                    if (n < N) gemm_ep_store(ep, dst, ldd, n, m, acc[a][b]);
+            for (int b = 0; b < 8; ++b) Cs[gn * 8 + b][gm * 8 + a] = acc[a][b];
+        }
+    }
+    __syncthreads();
+    {
+        const int ml = tid & 63;
+        const int64_t m = m0 + ml;
+        if (m < M) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int nl = (tid >> 6) + 4 * i;
+                const int64_t n = n0 + nl;
+                if (n < N) {
+                    const float v = gemm_ep_apply(ep, n, m, Cs[nl][ml]);
+                    if (ep.store_f16) ((__half *) dst)[n * ldd + m] = __float2half_rn(v);
+                    else              ((float *) dst)[n * ldd + m] = v;
                 }
             }
         }
