@@ -101,6 +101,15 @@ typedef struct { int n_steps; int kind[4]; float scalar[4]; int store_f16; } b20
 int b200_mul_mat_vec_q_cols(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
                             const b200_gemv_col * cols, int n_cols, const b200_gemv_ep * ep, void * stream);
 
+/* Up to 32 columns per launch, quantised beforehand: b200_quantize_cols gathers columns that live at unrelated
+ * addresses (K floats each) into xq[n_cols][K] / xd[n_cols][K/32]; b200_mul_mat_cols_q multiplies them with the
+ * weights (cols[n].x is ignored, dst/add as above).  A CTA keeps a few weight rows in shared memory for all
+ * columns, so the weights are read once for the whole group.  No counterpart in the reference. */
+int b200_quantize_cols(const float * const * x_cols, int n_cols, int64_t K, int8_t * xq, float * xd, void * stream);
+int b200_mul_mat_cols_q(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                        const int8_t * xq, const float * xd, const b200_gemv_col * cols, int n_cols,
+                        const b200_gemv_ep * ep, void * stream);
+
 /* NORM -> MUL(gamma) -> ADD(beta) in one pass (ops.cpp:3109-3158 followed by binary-ops.cpp:50-137), each of the
  * three roundings kept: y = ((x - mean) * rstd) * gamma + beta. */
 int b200_layer_norm(const float * x, const float * gamma, const float * beta, float * y, int64_t ne00, int64_t nrows,

@@ -212,3 +212,85 @@ def test_log_mel(K, pkg, n_mel, seconds):
     # that can flip an isolated value by one ulp.  Tolerance: at most 1e-5 of the values, each within 1 f32 ulp.
     assert mism <= max(1, out.size // 100000), f"{mism} of {out.size} mel values differ"
     assert np.abs(out - ref).max() <= 2.4e-7 * max(1.0, np.abs(ref).max())
+
+
+@pytest.mark.parametrize("wtype", [6, 8])
+@pytest.mark.parametrize("Kd,M,N", [(1280, 200, 1), (384, 70, 2), (1280, 1280, 3), (512, 96, 7), (1280, 130, 16), (5120, 72, 13), (1280, 333, 32)])
+def test_mul_mat_cols_q_scattered_columns(K, pkg, wtype, Kd, M, N):
+    """Columns that live at unrelated addresses (as single-token steps of different decoder states do) are quantised
+    together and multiplied in one launch; each column must equal the product computed for it alone."""
+    w, x = rnd(30, M, Kd, scale=0.02), rnd(31, N, Kd)
+    blocks, planes, nb = planes_of(K, pkg, wtype, w)
+    ref = O.mul_mat_q(wtype, blocks, M, Kd, x)
+    d_planes = dev(planes)
+    big = torch.zeros((N, 3, Kd), device="cuda")            # columns spread out in memory
+    big[:, 1, :] = dev(x)
+    outs = torch.zeros((N, 2, M), device="cuda")
+    bias = dev(rnd(32, M))
+
+    class Col(C.Structure):
+        _fields_ = [("x", vp), ("dst", vp), ("add", vp * 4)]
+
+    class Ep(C.Structure):
+        _fields_ = [("n_steps", C.c_int), ("kind", C.c_int * 4), ("scalar", C.c_float * 4), ("store_f16", C.c_int)]
+
+    cols = (Col * N)()
+    xs = (vp * N)()
+    for n in range(N):
+        cols[n].x = big[n, 1].data_ptr()
+        cols[n].dst = outs[n, 1].data_ptr()
+        cols[n].add[0] = bias.data_ptr()
+        xs[n] = big[n, 1].data_ptr()
+    ep = Ep(2, (C.c_int * 4)(1, 2, 0, 0), (C.c_float * 4)(0, 0.5, 0, 0), 0)     # + bias, then * 0.5
+    xq = torch.empty((N, Kd), dtype=torch.int8, device="cuda")
+    xd = torch.empty((N, Kd // 32), device="cuda")
+    sync_ok(K.b200_quantize_cols(xs, N, i64(Kd), ptr(xq), ptr(xd), None))
+    sync_ok(K.b200_mul_mat_cols_q(wtype, ptr(d_planes), i64(nb), i64(M), i64(Kd), ptr(xq), ptr(xd), cols, N, C.byref(ep), None))
+    want = (ref + bias.cpu().numpy()[None, :]) * np.float32(0.5)
+    assert bits_equal(outs[:, 1].cpu().numpy(), want)
+    if N <= 8:     # the f32-column entry point gives the same bits
+        outs.zero_()
+        sync_ok(K.b200_mul_mat_vec_q_cols(wtype, ptr(d_planes), i64(nb), i64(M), i64(Kd), cols, N, C.byref(ep), None))
+        assert bits_equal(outs[:, 1].cpu().numpy(), want)
+
+
+def test_decode_rows_attention_and_layer_norm_rows(K):
+    """Row-descriptor entry points: every row has its own buffers and key count."""
+    H, d = 3, 192
+    rng = np.random.default_rng(33)
+
+    class Row(C.Structure):
+        _fields_ = [("q", vp), ("k", vp), ("v", vp), ("mask", vp), ("dst", vp), ("n_kv", C.c_int64)]
+
+    rows = (Row * 3)()
+    keep, want = [], []
+    for i, n_kv in enumerate((37, 1536, 5)):
+        q = (rng.standard_normal((H, 64)) * 0.5).astype(np.float32)
+        k = (rng.standard_normal((n_kv, H, 64)) * 0.5).astype(np.float16)
+        v = rng.standard_normal((n_kv, H, 64)).astype(np.float16)
+        mask = None
+        if i == 0:
+            mask = np.zeros((1, n_kv), np.float16)
+            mask[0, rng.random(n_kv) < 0.4] = -np.inf
+            mask[0, 0] = 0
+        dq, dk, dv, dd = dev(q), dev(k), dev(v), torch.zeros((H, 64), device="cuda")
+        dm = dev(mask) if mask is not None else None
+        keep += [dq, dk, dv, dd, dm]
+        rows[i].q, rows[i].k, rows[i].v, rows[i].dst, rows[i].n_kv = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dd.data_ptr(), n_kv
+        rows[i].mask = dm.data_ptr() if dm is not None else None
+        want.append(O.flash_attn(q[None], k, v, mask, 0.125)[0])
+    sync_ok(K.b200_flash_attn_decode_rows(rows, 3, i64(H), i64(64 * 4), i64(d * 2), i64(128), i64(d * 2), i64(128), C.c_float(0.125), None))
+    for i in range(3):
+        assert bits_equal(keep[5 * i + 3].cpu().numpy(), want[i]), f"row {i}"
+
+    class LnRow(C.Structure):
+        _fields_ = [("x", vp), ("y", vp)]
+
+    x = rnd(34, 5, 1280) * 2 + 0.1
+    gamma, beta = rnd(35, 1280), rnd(36, 1280)
+    dx, dy, dg, db = dev(x), torch.zeros((5, 1280), device="cuda"), dev(gamma), dev(beta)
+    lr = (LnRow * 5)()
+    for i in range(5):
+        lr[i].x, lr[i].y = dx[i].data_ptr(), dy[4 - i].data_ptr()
+    sync_ok(K.b200_layer_norm_rows(lr, 5, ptr(dg), ptr(db), i64(1280), C.c_float(1e-5), None))
+    assert bits_equal(dy.cpu().numpy()[::-1], O.norm(x) * gamma + beta)

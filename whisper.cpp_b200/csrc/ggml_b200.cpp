@@ -252,7 +252,14 @@ struct b200_backend_ctx {
     std::string  name;
     std::vector<cudaEvent_t> events;       // timing mode only
     std::atomic<int64_t> last_decode_ns{0};   // when this instance last submitted a decode-step graph
+    // quantised activation columns of the decode path (up to 32 columns of up to COLQ_MAX_K values)
+    void *       colq = nullptr;
+    std::vector<const float *> colq_ptrs;    // columns currently held in colq ...
+    int64_t      colq_K = 0;
+    int64_t      colq_seq = -2;              // ... written (or reused) by the item with this sequence number
+    int64_t      item_seq = 0;
 };
+#define COLQ_MAX_K 8192
 
 static void batcher_join(b200_backend_ctx * ctx);
 static void batcher_leave(b200_backend_ctx * ctx);
@@ -267,6 +274,7 @@ static void b200_backend_free(ggml_backend_t backend) {
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
+    if (ctx->colq) cudaFree(ctx->colq);
     for (cudaEvent_t e : ctx->events) cudaEventDestroy(e);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -678,6 +686,7 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
     if (it.kind == PK_GEMV) {
         struct ggml_tensor * n0 = ggml_graph_node(gs[0], it.node);
         const struct ggml_tensor * w = n0->src[0];
+        const int64_t K = w->ne[0], M = w->ne[1];
         const int64_t nb_total = (int64_t) (ggml_nbytes(w) / ggml_type_size(w->type));
         b200_gemv_ep ep;
         memset(&ep, 0, sizeof(ep));
@@ -686,35 +695,60 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
             ep.kind[s] = it.step_kind[s];
             if (it.step_kind[s] == B200_EP_SCALE) memcpy(&ep.scalar[s], ggml_graph_node(gs[0], it.step_node[s])->op_params, sizeof(float));
         }
-        b200_gemv_col cols[8];
+        b200_gemv_col cols[32];
+        const float * xs[32];
         int n_cols = 0;
+        int8_t * xq = (int8_t *) ctx->colq;
+        float *  xd = (float *) ((char *) ctx->colq + (size_t) 32 * COLQ_MAX_K);
         auto flush = [&]() -> int {
             if (!n_cols) return 0;
-            const int e = b200_mul_mat_vec_q_cols((int) w->type, w->data, nb_total, w->ne[1], w->ne[0], cols, n_cols, &ep, st);
+            int e = 0;
+            if (K <= COLQ_MAX_K) {
+                // the columns are quantised once and stay valid for the products that follow immediately on the same
+                // activations (the K, V and Q projections of a layer)
+                const bool reuse = ctx->colq_seq + 1 == ctx->item_seq && ctx->colq_K == K && (int) ctx->colq_ptrs.size() == n_cols &&
+                                   memcmp(ctx->colq_ptrs.data(), xs, sizeof(xs[0]) * n_cols) == 0;
+                if (!reuse) {
+                    e = b200_quantize_cols(xs, n_cols, K, xq, xd, st);
+                    if (e) return e;
+                    ctx->colq_ptrs.assign(xs, xs + n_cols);
+                    ctx->colq_K = K;
+                }
+                ctx->colq_seq = ctx->item_seq;
+                // shared memory holds the quantised columns next to the weight rows: fewer columns per launch for long rows
+                const int cap = K > 2560 ? 16 : 32;
+                for (int c0 = 0; c0 < n_cols && !e; c0 += cap)
+                    e = b200_mul_mat_cols_q((int) w->type, w->data, nb_total, M, K, xq + (size_t) c0 * K, xd + (size_t) c0 * (K / 32), cols + c0,
+                                            n_cols - c0 < cap ? n_cols - c0 : cap, &ep, st);
+            } else {
+                for (int c0 = 0; c0 < n_cols && !e; c0 += 8)
+                    e = b200_mul_mat_vec_q_cols((int) w->type, w->data, nb_total, M, K, cols + c0, n_cols - c0 < 8 ? n_cols - c0 : 8, &ep, st);
+            }
             n_cols = 0;
             return e;
         };
+        int n_flushes = 0;
         for (int g = 0; g < n_g; ++g) {
             struct ggml_tensor * mm = ggml_graph_node(gs[g], it.node), * out = ggml_graph_node(gs[g], it.last);
             if (mm->src[0]->data != w->data) {            // a state of another model on the same device: its own launch
                 int e = flush();
                 if (e) return e;
                 struct ggml_cgraph * one[1] = { gs[g] };
-                // swap so that the recursive call sees this graph's weights as the reference
+                ctx->colq_seq = -2;
                 e = run_item(ctx, it, one, 1);
                 if (e) return e;
+                ctx->colq_seq = -2;
                 continue;
             }
             const struct ggml_tensor * x = mm->src[1];
-            const int64_t esz = it.store_f16 ? 2 : 4;
             const int64_t out_stride = it.store_f16 ? mm->ne[0] * 2 : (int64_t) out->nb[1];
             for (int64_t c = 0; c < x->ne[1]; ++c) {
-                if (n_cols == 8) { const int e = flush(); if (e) return e; }
+                if (n_cols == 32) { const int e = flush(); if (e) return e; ++n_flushes; ctx->colq_seq = -2; }
                 b200_gemv_col & col = cols[n_cols];
                 memset(&col, 0, sizeof(col));
                 col.x = (const float *) ((const char *) x->data + c * x->nb[1]);
+                xs[n_cols] = col.x;
                 col.dst = (char *) out->data + c * out_stride;
-                (void) esz;
                 for (int s = 0; s < it.n_steps; ++s) {
                     if (it.step_kind[s] != B200_EP_ADD) continue;
                     const struct ggml_tensor * o = ggml_graph_node(gs[g], it.step_node[s])->src[it.step_src[s]];
@@ -723,7 +757,9 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
                 ++n_cols;
             }
         }
-        return flush();
+        const int e = flush();
+        if (n_flushes) ctx->colq_seq = -2;      // more than one group went through the buffer: nothing to reuse
+        return e;
     }
     if (it.kind == PK_GEMM) {
         for (int g = 0; g < n_g; ++g) {
@@ -809,7 +845,9 @@ static int run_plan(b200_backend_ctx * ctx, const exec_plan & plan, struct ggml_
         if (*n_ev == ctx->events.size()) { cudaEvent_t e; cudaEventCreate(&e); ctx->events.push_back(e); }
         return ctx->events[(*n_ev)++];
     };
+    ctx->colq_seq = -2;                      // activations of an earlier graph never carry over
     for (const plan_item & it : plan.items) {
+        ctx->item_seq++;
         if (timing) {
             double work = 0;
             struct ggml_tensor * node = ggml_graph_node(gs[0], it.node);
@@ -1088,6 +1126,9 @@ static ggml_backend_t b200_dev_init_backend(ggml_backend_dev_t dev, const char *
     ctx->device = dctx->device;
     ctx->name   = dctx->name;
     if (!cuda_ok(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking), "cudaStreamCreate")) { delete ctx; return nullptr; }
+    if (!cuda_ok(cudaMalloc(&ctx->colq, (size_t) 32 * COLQ_MAX_K + (size_t) 32 * (COLQ_MAX_K / 32) * 4), "cudaMalloc(colq)")) {
+        cudaStreamDestroy(ctx->stream); delete ctx; return nullptr;
+    }
     batcher_join(ctx);
     return new ggml_backend{ b200_guid(), b200_backend_iface, dev, ctx };
 }

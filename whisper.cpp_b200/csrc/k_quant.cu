@@ -650,6 +650,198 @@ extern "C" int b200_mul_mat_vec_q(int wtype, const void * w_planes, int64_t nb_t
 }
 
 // ------------------------------------------------------------------------------------------------
+// Skinny product for up to 32 activation columns that were quantised beforehand (columns of one tensor or single
+// columns of many decoder states).  A CTA owns R weight rows for the whole K: the rows are dequantised to int8 lane
+// words in shared memory once, the quantised columns are copied next to them, and then every thread replays the
+// FMA chain of lane j for one row and CT columns, block after block.  Same sums, same order as the kernels above.
+// ------------------------------------------------------------------------------------------------
+struct GemvCols32 {
+    void *        dst[32];
+    const float * add[4][32];
+};
+
+__device__ __forceinline__ void ep_store32(const GemvEp & ep, const GemvCols32 & c, int n, int64_t m, float v) {
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+        if (s < ep.n_steps) {
+            if (ep.kind[s] == B200_EP_ADD)        v = __fadd_rn(v, c.add[s][n][m]);
+            else if (ep.kind[s] == B200_EP_SCALE) v = __fmul_rn(v, ep.scalar[s]);
+            else {
+                if (v <= -10.0f)     v = 0.0f;
+                else if (v < 10.0f)  v = __half2float(__ushort_as_half(ep.gelu_table[__half_as_ushort(__float2half_rn(v))]));
+            }
+        }
+    }
+    if (ep.store_f16) ((__half *) c.dst[n])[m] = __float2half_rn(v);
+    else              ((float *) c.dst[n])[m] = v;
+}
+
+template <int TYPE, int R, int CT>
+__global__ void __launch_bounds__(256)
+k_gemv_skinny(QPlanes w, int64_t M, int nbk, const int8_t * __restrict__ xq, const float * __restrict__ xd, int n_cols,
+              GemvCols32 cols, GemvEp ep) {
+    extern __shared__ __align__(16) unsigned char sk_smem[];
+    constexpr int CG = 32 / R;
+    const int RS   = nbk * 8 + ((8 - (nbk * 8) % 32 + 32) % 32);      // row stride in words, == 8 mod 32
+    const int XS   = nbk * 8;                                         // words per column
+    int *   Wsm = (int *) sk_smem;                                    // [R][RS]
+    int *   Xsm = Wsm + R * RS;                                       // [n_cols][XS]
+    float * dW  = (float *) (Xsm + n_cols * XS);                      // [R][nbk]
+    float * dX  = dW + R * nbk;                                       // [n_cols][nbk]
+    const int tid = threadIdx.x;
+    const int64_t row0 = (int64_t) blockIdx.x * R;
+
+    for (int it = tid; it < R * nbk; it += 256) {                     // weight rows: one (row, block) per thread and pass
+        const int r = it / nbk, ib = it - r * nbk;
+        const int64_t m = row0 + r;
+        int wv[8];
+        float dw = 0.0f;
+#pragma unroll
+        for (int t = 0; t < 8; ++t) wv[t] = 0;
+        if (m < M) {
+            const int64_t blk = m * nbk + ib;
+            if (TYPE == B200_TYPE_Q5_0) {
+                const uint4    q  = __ldg(((const uint4 *) w.qs) + blk);
+                const uint32_t qh = __ldg(w.qh + blk);
+                const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int t = 0; t < 8; ++t) wv[t] = q5_lane_word(qw[t & 3], qh, t);
+            } else {
+                const uint4 a = __ldg(((const uint4 *) w.qs) + blk * 2), b = __ldg(((const uint4 *) w.qs) + blk * 2 + 1);
+                wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w;
+                wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
+            }
+            dw = __half2float(w.d[blk]);
+        }
+        *(int4 *) &Wsm[r * RS + ib * 8]     = make_int4(wv[0], wv[1], wv[2], wv[3]);
+        *(int4 *) &Wsm[r * RS + ib * 8 + 4] = make_int4(wv[4], wv[5], wv[6], wv[7]);
+        dW[r * nbk + ib] = dw;
+    }
+    {
+        const uint4 * src = (const uint4 *) xq;
+        uint4 * dstv = (uint4 *) Xsm;
+        const int n16 = n_cols * XS / 4;
+        for (int it = tid; it < n16; it += 256) dstv[it] = src[it];
+        for (int it = tid; it < n_cols * nbk; it += 256) dX[it] = xd[it];
+    }
+    __syncthreads();
+
+    const int j = tid & 7, grp = tid >> 3;
+    const int r = grp % R, cg = grp / R;
+    const int c0 = cg * CT;
+    float acc[CT];
+#pragma unroll
+    for (int c = 0; c < CT; ++c) acc[c] = 0.0f;
+    const int *   wrow = Wsm + r * RS + j;
+    const float * dwr  = dW + r * nbk;
+#pragma unroll 4
+    for (int ib = 0; ib < nbk; ++ib) {
+        const int   wv = wrow[ib * 8];
+        const float dw = dwr[ib];
+#pragma unroll
+        for (int c = 0; c < CT; ++c) {
+            const int col = min(c0 + c, n_cols - 1);
+            const int   xv = Xsm[col * XS + ib * 8 + j];
+            const float q  = __fadd_rn(__int_as_float(__dp4a(wv, xv, MAGIC_I)), -MAGIC_F);
+            acc[c] = __fmaf_rn(__fmul_rn(dw, dX[col * nbk + ib]), q, acc[c]);
+        }
+    }
+#pragma unroll
+    for (int c = 0; c < CT; ++c) {
+        float v = acc[c];
+        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
+        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+        v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+        acc[c] = v;
+    }
+    const int64_t m = row0 + r;
+    if (j == 0 && m < M) {
+#pragma unroll
+        for (int c = 0; c < CT; ++c) if (c0 + c < n_cols) ep_store32(ep, cols, c0 + c, m, acc[c]);
+    }
+}
+
+template <int TYPE, int R, int CT>
+static int launch_skinny(const QPlanes & w, int64_t M, int nbk, const int8_t * xq, const float * xd, int n_cols, const GemvCols32 & cols,
+                         const GemvEp & ep, cudaStream_t st) {
+    const int RS = nbk * 8 + ((8 - (nbk * 8) % 32 + 32) % 32);
+    const size_t smem = ((size_t) R * RS + (size_t) n_cols * nbk * 8 + (size_t) R * nbk + (size_t) n_cols * nbk) * 4;
+    if (smem > 220 * 1024) return B200_ERR_ARG;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaFuncSetAttribute(k_gemv_skinny<TYPE, R, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        attr_done[dev] = true;
+    }
+    k_gemv_skinny<TYPE, R, CT><<<(unsigned) ((M + R - 1) / R), 256, smem, st>>>(w, M, nbk, xq, xd, n_cols, cols, ep);
+    B200_RETURN_LAST();
+}
+
+template <int TYPE>
+static int launch_skinny_n(const QPlanes & w, int64_t M, int nbk, const int8_t * xq, const float * xd, int n_cols, const GemvCols32 & cols,
+                           const GemvEp & ep, cudaStream_t st) {
+    if (n_cols == 1)  return launch_skinny<TYPE, 32, 1>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
+    if (n_cols == 2)  return launch_skinny<TYPE, 16, 1>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
+    if (n_cols <= 4)  return launch_skinny<TYPE, 8, 1>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
+    if (n_cols <= 8)  return launch_skinny<TYPE, 8, 2>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
+    if (n_cols <= 16) return launch_skinny<TYPE, 8, 4>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
+    return launch_skinny<TYPE, 8, 8>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
+}
+
+struct ColPtrs32 { const float * x[32]; };
+__global__ void k_quantize_cols(ColPtrs32 cols, int n_cols, int nbk, int8_t * __restrict__ qs, float * __restrict__ d) {
+    const int lane = threadIdx.x & 31;
+    const int blk  = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (blk >= n_cols * nbk) return;
+    const int c = blk / nbk, ib = blk - c * nbk;
+    const float v = cols.x[c][ib * 32 + lane];
+    int8_t q; float dd;
+    quantize_block_q8_0(v, lane, q, dd);
+    qs[(size_t) blk * 32 + lane] = q;
+    if (lane == 0) d[blk] = dd;
+}
+
+extern "C" int b200_quantize_cols(const float * const * x_cols, int n_cols, int64_t K, int8_t * xq, float * xd, void * stream) {
+    if (n_cols < 1 || n_cols > 32 || K % 32 != 0 || K <= 0) return B200_ERR_ARG;
+    ColPtrs32 c;
+    memset(&c, 0, sizeof(c));
+    for (int i = 0; i < n_cols; ++i) { if (!x_cols[i]) return B200_ERR_ARG; c.x[i] = x_cols[i]; }
+    const int nbk = (int) (K / 32);
+    const int nblk = n_cols * nbk;
+    k_quantize_cols<<<(unsigned) ((nblk + 7) / 8), 256, 0, as_stream(stream)>>>(c, n_cols, nbk, xq, xd);
+    B200_RETURN_LAST();
+}
+
+extern "C" int b200_mul_mat_cols_q(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                                   const int8_t * xq, const float * xd, const b200_gemv_col * cols, int n_cols,
+                                   const b200_gemv_ep * ep, void * stream) {
+    if (K % 32 != 0 || M <= 0 || n_cols < 1 || n_cols > 32 || !cols) return B200_ERR_ARG;
+    if (((uintptr_t) w_planes & 15) != 0 || ((uintptr_t) xq & 15) != 0) return B200_ERR_ARG;
+    const int64_t nbk = K / 32;
+    if (M * nbk > nb_total) return B200_ERR_ARG;
+    GemvEp e;
+    static const int   no_kind[4]   = {0, 0, 0, 0};
+    static const float no_scalar[4] = {0, 0, 0, 0};
+    int rc = ep ? fill_ep(e, ep->n_steps, ep->kind, ep->scalar, ep->store_f16) : fill_ep(e, 0, no_kind, no_scalar, 0);
+    if (rc) return rc;
+    GemvCols32 c;
+    memset(&c, 0, sizeof(c));
+    for (int n = 0; n < n_cols; ++n) {
+        if (!cols[n].dst) return B200_ERR_ARG;
+        c.dst[n] = cols[n].dst;
+        for (int s = 0; s < e.n_steps; ++s) {
+            c.add[s][n] = cols[n].add[s];
+            if (e.kind[s] == B200_EP_ADD && !c.add[s][n]) return B200_ERR_ARG;
+        }
+    }
+    const QPlanes w = q_planes(wtype, w_planes, nb_total);
+    if (wtype == B200_TYPE_Q5_0) return launch_skinny_n<B200_TYPE_Q5_0>(w, M, (int) nbk, xq, xd, n_cols, c, e, as_stream(stream));
+    if (wtype == B200_TYPE_Q8_0) return launch_skinny_n<B200_TYPE_Q8_0>(w, M, (int) nbk, xq, xd, n_cols, c, e, as_stream(stream));
+    return B200_ERR_ARG;
+}
+
+// ------------------------------------------------------------------------------------------------
 // Product with the activation scratch in a fixed device array (for callers that cannot allocate).
 // ------------------------------------------------------------------------------------------------
 #define B200_STATIC_SCRATCH_BYTES (9 * 1024 * 1024)
