@@ -257,6 +257,7 @@ struct b200_backend_ctx {
     std::vector<const float *> colq_ptrs;    // columns currently held in colq ...
     int64_t      colq_K = 0;
     int64_t      colq_seq = -2;              // ... written (or reused) by the item with this sequence number
+    std::atomic<int64_t> served_ns{0};       // when a leader last enqueued a step for this instance (0: not in a batch)
     int64_t      item_seq = 0;
 };
 #define COLQ_MAX_K 8192
@@ -892,6 +893,8 @@ struct device_batcher {
     size_t                  next_event = 0;
     std::unordered_map<uint64_t, exec_plan> plans;      // by signature, fused
     int                     alive = 0;                  // backend instances on this device
+    double                  step_ns_ema = 0;            // typical time from "step enqueued" to "next step arrives"
+
     std::vector<b200_backend_ctx *> members;            // live backend instances on this device
 };
 
@@ -909,7 +912,10 @@ static void batcher_leave(b200_backend_ctx * ctx) {
     for (size_t i = 0; i < B.members.size(); ++i) if (B.members[i] == ctx) { B.members.erase(B.members.begin() + i); break; }
     B.alive = (int) B.members.size();
 }
-static std::atomic<int64_t> g_batched_graphs{0}, g_batches{0};
+static std::atomic<int64_t> g_batched_graphs{0}, g_batches{0}, g_ns_lead_wait{0}, g_ns_lead_prep{0}, g_ns_lead_launch{0};
+extern "C" int64_t b200_stat_ns_lead_wait(void)   { return g_ns_lead_wait.load(); }
+extern "C" int64_t b200_stat_ns_lead_prep(void)   { return g_ns_lead_prep.load(); }
+extern "C" int64_t b200_stat_ns_lead_launch(void) { return g_ns_lead_launch.load(); }
 extern "C" int64_t b200_stat_batched_graphs(void) { return g_batched_graphs.load(); }
 extern "C" int64_t b200_stat_batches(void)        { return g_batches.load(); }
 
@@ -953,8 +959,16 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
     // ---- batched path -------------------------------------------------------------------------
     if (batching && fuse && !timing && B.alive > 1 && is_decode_graph(cgraph)) {
         batch_req req = { ctx, cgraph, graph_signature(cgraph), 0, nullptr };
-        ctx->last_decode_ns = now_ns();
+        const int64_t t_arrive = now_ns();
+        ctx->last_decode_ns = t_arrive;
         std::unique_lock<std::mutex> lk(B.mu);
+        {
+            const int64_t t_served = ctx->served_ns.exchange(0);
+            if (t_served) {     // one full turn of this state: device time of the step plus the host work between steps
+                const double turn = (double) (t_arrive - t_served);
+                B.step_ns_ema = B.step_ns_ema == 0 ? turn : 0.8 * B.step_ns_ema + 0.2 * turn;
+            }
+        }
         B.pending.push_back(&req);
         if (B.leader_active) {
             B.cv.notify_all();                                   // the leader may be waiting for this arrival
@@ -975,8 +989,20 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
             int expected = 0;
             const int64_t now = now_ns();
             for (b200_backend_ctx * c : B.members) if (now - c->last_decode_ns < 20 * 1000 * 1000) ++expected;
-            const auto deadline = std::chrono::steady_clock::now() + std::chrono::microseconds(window_us);
+            // States that were served by an earlier batch come back one turn later.  Waiting for them merges the groups:
+            // while they are away the device is busy with their step anyway, so the wait costs nothing when the device
+            // is the bottleneck, and one merged group needs one pass over the weights instead of one per group.
+            int64_t wait_us = window_us;
+            if (B.step_ns_ema > 0) {
+                const int64_t turn_us = (int64_t) (1.25 * B.step_ns_ema / 1000.0);
+                if (turn_us > wait_us) wait_us = turn_us;
+                if (wait_us > 20000) wait_us = 20000;
+            }
+            const auto deadline = std::chrono::steady_clock::now() + std::chrono::microseconds(wait_us);
+            const int64_t t_w0 = now_ns();
             B.cv.wait_until(lk, deadline, [&] { return (int) B.pending.size() >= expected; });
+            g_ns_lead_wait += now_ns() - t_w0;
+            const int64_t t_p0 = now_ns();
             std::vector<batch_req *> mine;
             mine.swap(B.pending);
             B.leader_active = false;                              // later arrivals elect their own leader
@@ -1006,7 +1032,10 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
                     if (r->sig == req.sig && graph_fits_plan(plan_copy, r->g)) { gs.push_back(r->g); served.push_back(r); }
                 }
                 size_t n_ev = 0;
+                g_ns_lead_prep += now_ns() - t_p0;
+                const int64_t t_l0 = now_ns();
                 rc = run_plan(ctx, plan_copy, gs.data(), (int) gs.size(), false, nullptr, nullptr, &n_ev);
+                g_ns_lead_launch += now_ns() - t_l0;
                 if (rc == 0 && !served.empty()) rc = cudaEventRecord(ev, ctx->stream) == cudaSuccess ? 0 : (int) cudaGetLastError();
                 g_batched_graphs += (int64_t) gs.size();
                 g_batches += 1;
@@ -1014,11 +1043,13 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
                 rc = -1;                                          // leader's own graph does not fit: everybody runs alone
             }
             lk.lock();
+            const int64_t t_done = now_ns();
+            if (rc == 0) ctx->served_ns = t_done;
             for (batch_req * r : mine) {
                 if (r == &req) continue;
                 bool was_served = false;
                 for (batch_req * s : served) if (s == r) was_served = true;
-                if (was_served) { r->ev = ev; r->state = rc == 0 ? 1 : 3; }
+                if (was_served) { r->ev = ev; r->state = rc == 0 ? 1 : 3; if (rc == 0) r->ctx->served_ns = t_done; }
                 else r->state = 2;
             }
             lk.unlock();
@@ -1261,6 +1292,9 @@ static void * b200_reg_get_proc_address(ggml_backend_reg_t, const char * name) {
     if (strcmp(name, "b200_stat_host_ns_sync") == 0)    return (void *) b200_stat_host_ns_sync;
     if (strcmp(name, "b200_stat_batched_graphs") == 0)  return (void *) b200_stat_batched_graphs;
     if (strcmp(name, "b200_stat_batches") == 0)         return (void *) b200_stat_batches;
+    if (strcmp(name, "b200_stat_ns_lead_wait") == 0)    return (void *) b200_stat_ns_lead_wait;
+    if (strcmp(name, "b200_stat_ns_lead_prep") == 0)    return (void *) b200_stat_ns_lead_prep;
+    if (strcmp(name, "b200_stat_ns_lead_launch") == 0)  return (void *) b200_stat_ns_lead_launch;
     if (strcmp(name, "b200_launch_count") == 0) return (void *) b200_launch_count;
     if (strcmp(name, "b200_timing_enable") == 0)  return (void *) b200_timing_enable;
     if (strcmp(name, "b200_timing_reset") == 0)   return (void *) b200_timing_reset;
