@@ -186,138 +186,159 @@ __device__ __forceinline__ float gemm_ep_apply(const GemmEp & ep, int64_t n, int
     return v;
 }
 
+// packed single-precision pairs (sm_100 fma/add/mul .f32x2): two independent IEEE operations per instruction
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ f32x2 pack2i(int lo, int hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float & lo, float & hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
+// 32 x 32 output tile per CTA, 256 threads, a thread owns a 2 x 2 block of outputs with all eight lane sums of each
+// (32 running sums as 16 register pairs), so the block scale d_w*d_x is formed once per output and the lane updates
+// go two at a time through the packed f32x2 pipe.  Per 32-block and output: q_j = dp4a (exact), acc_j = fma(d, q_j, acc_j).
 template <int TYPE>
 __global__ void __launch_bounds__(256, 2)
 k_mul_mat_q(QPlanes w, int64_t M, int64_t nbk, const int8_t * __restrict__ xq, const float * __restrict__ xd,
             int64_t N, void * __restrict__ dst, int64_t ldd, GemmEp ep) {
-    constexpr int BM = 64, BN = 32, KC = 4;
-    constexpr int WS_WORDS = KC * 8 * (BM + 4), XS_WORDS = KC * 8 * (BN + 4);
-    __shared__ __align__(16) int   smem_i[WS_WORDS + XS_WORDS];
+    constexpr int BM = 32, BN = 32, KC = 4, WSTR = 8, XSTR = 12;       // words per staged row / column (X padded: conflict-free LDS.128)
+    __shared__ __align__(16) int   Ws[KC][BM][WSTR];
+    __shared__ __align__(16) int   Xs[KC][BN][XSTR];
     __shared__ __align__(16) float dWs[KC][BM];
     __shared__ __align__(16) float dXs[KC][BN];
-    int (*Ws)[8][BM + 4] = (int (*)[8][BM + 4]) smem_i;
-    int (*Xs)[8][BN + 4] = (int (*)[8][BN + 4]) (smem_i + WS_WORDS);
+    __shared__ float Cs[BN][BM + 1];
 
     const int tid = threadIdx.x;
-    const int j   = tid & 7;
-    const int g   = tid >> 3;
-    const int gm  = g & 7;
-    const int gn  = g >> 3;
+    const int tx  = tid & 15;          // columns tx and tx + 16
+    const int ty  = tid >> 4;          // rows 2*ty, 2*ty + 1
     const int64_t m0 = (int64_t) blockIdx.x * BM;
     const int64_t n0 = (int64_t) blockIdx.y * BN;
 
-    float acc[8][8];
+    f32x2 acc[2][8];                   // [row][lane] = (column tx, column tx + 16)
 #pragma unroll
-    for (int a = 0; a < 8; ++a)
+    for (int r = 0; r < 2; ++r)
 #pragma unroll
-        for (int b = 0; b < 8; ++b) acc[a][b] = 0.0f;
+        for (int jj = 0; jj < 8; ++jj) acc[r][jj] = 0ull;
 
-    const int     sr  = tid & 63;      // W staging: row in tile
-    const int     skb = tid >> 6;      // W staging: block in chunk
-    const int     xc  = tid & 31;      // X staging: column in tile
-    const int     xkb = (tid >> 5) & 3;
-
-    // the next chunk's blocks travel in registers while the current chunk is multiplied
-    uint4 pwa = make_uint4(0, 0, 0, 0), pwb = make_uint4(0, 0, 0, 0), pxa = make_uint4(0, 0, 0, 0), pxb = make_uint4(0, 0, 0, 0);
+    // staging roles: threads 0..127 fetch one (row, block) of W, threads 128..255 one (column, block) of X
+    const int srow = tid & 31, skb = (tid >> 5) & 3;
+    const bool is_w = tid < 128;
+    uint4 pa = make_uint4(0, 0, 0, 0), pb = make_uint4(0, 0, 0, 0);
     uint32_t pqh = 0;
-    float pdw = 0.0f, pdx = 0.0f;
+    float pd = 0.0f;
     auto fetch = [&](int64_t kb0) {
-        pwa = make_uint4(0, 0, 0, 0); pwb = pwa; pqh = 0; pdw = 0.0f;
-        {
-            const int64_t m = m0 + sr, ib = kb0 + skb;
+        pa = make_uint4(0, 0, 0, 0); pb = pa; pqh = 0; pd = 0.0f;
+        const int64_t ib = kb0 + skb;
+        if (is_w) {
+            const int64_t m = m0 + srow;
             if (m < M && ib < nbk) {
                 const int64_t blk = m * nbk + ib;
-                if (TYPE == B200_TYPE_Q5_0) { pwa = ((const uint4 *) w.qs)[blk]; pqh = w.qh[blk]; }
-                else { pwa = ((const uint4 *) w.qs)[blk * 2]; pwb = ((const uint4 *) w.qs)[blk * 2 + 1]; }
-                pdw = __half2float(w.d[blk]);
+                if (TYPE == B200_TYPE_Q5_0) { pa = ((const uint4 *) w.qs)[blk]; pqh = w.qh[blk]; }
+                else { pa = ((const uint4 *) w.qs)[blk * 2]; pb = ((const uint4 *) w.qs)[blk * 2 + 1]; }
+                pd = __half2float(w.d[blk]);
             }
-        }
-        if (tid < 128) {
-            pxa = make_uint4(0, 0, 0, 0); pxb = pxa; pdx = 0.0f;
-            const int64_t n = n0 + xc, ib = kb0 + xkb;
+        } else {
+            const int64_t n = n0 + srow;
             if (n < N && ib < nbk) {
                 const uint4 * p = (const uint4 *) (xq + (n * nbk + ib) * 32);
-                pxa = p[0]; pxb = p[1];
-                pdx = xd[n * nbk + ib];
+                pa = p[0]; pb = p[1];
+                pd = xd[n * nbk + ib];
             }
         }
     };
     fetch(0);
 
+    const f32x2 neg_magic = pack2(-MAGIC_F, -MAGIC_F);
     for (int64_t kb0 = 0; kb0 < nbk; kb0 += KC) {
-        {   // publish W (dequantised to int8 lane words) and X
+        if (is_w) {
             int wv[8];
             if (TYPE == B200_TYPE_Q5_0) {
-                const uint32_t qw[4] = {pwa.x, pwa.y, pwa.z, pwa.w};
+                const uint32_t qw[4] = {pa.x, pa.y, pa.z, pa.w};
 #pragma unroll
                 for (int t = 0; t < 8; ++t) wv[t] = q5_lane_word(qw[t & 3], pqh, t);
             } else {
-                wv[0] = pwa.x; wv[1] = pwa.y; wv[2] = pwa.z; wv[3] = pwa.w;
-                wv[4] = pwb.x; wv[5] = pwb.y; wv[6] = pwb.z; wv[7] = pwb.w;
+                wv[0] = pa.x; wv[1] = pa.y; wv[2] = pa.z; wv[3] = pa.w;
+                wv[4] = pb.x; wv[5] = pb.y; wv[6] = pb.z; wv[7] = pb.w;
             }
-#pragma unroll
-            for (int t = 0; t < 8; ++t) Ws[skb][t][sr] = wv[t];
-            dWs[skb][sr] = pdw;
-            if (tid < 128) {
-                Xs[xkb][0][xc] = pxa.x; Xs[xkb][1][xc] = pxa.y; Xs[xkb][2][xc] = pxa.z; Xs[xkb][3][xc] = pxa.w;
-                Xs[xkb][4][xc] = pxb.x; Xs[xkb][5][xc] = pxb.y; Xs[xkb][6][xc] = pxb.z; Xs[xkb][7][xc] = pxb.w;
-                dXs[xkb][xc] = pdx;
-            }
+            *(int4 *) &Ws[skb][srow][0] = make_int4(wv[0], wv[1], wv[2], wv[3]);
+            *(int4 *) &Ws[skb][srow][4] = make_int4(wv[4], wv[5], wv[6], wv[7]);
+            dWs[skb][srow] = pd;
+        } else {
+            *(uint4 *) &Xs[skb][srow][0] = pa;
+            *(uint4 *) &Xs[skb][srow][4] = pb;
+            dXs[skb][srow] = pd;
         }
         __syncthreads();
         if (kb0 + KC < nbk) fetch(kb0 + KC);
 
 #pragma unroll 2
         for (int kb = 0; kb < KC; ++kb) {
-            int wv[8], xv[8];
-            float dw[8], dx[8];
-            *(int4 *) &wv[0] = *(const int4 *) &Ws[kb][j][gm * 8];
-            *(int4 *) &wv[4] = *(const int4 *) &Ws[kb][j][gm * 8 + 4];
-            *(int4 *) &xv[0] = *(const int4 *) &Xs[kb][j][gn * 8];
-            *(int4 *) &xv[4] = *(const int4 *) &Xs[kb][j][gn * 8 + 4];
-            *(float4 *) &dw[0] = *(const float4 *) &dWs[kb][gm * 8];
-            *(float4 *) &dw[4] = *(const float4 *) &dWs[kb][gm * 8 + 4];
-            *(float4 *) &dx[0] = *(const float4 *) &dXs[kb][gn * 8];
-            *(float4 *) &dx[4] = *(const float4 *) &dXs[kb][gn * 8 + 4];
+            int w0[8], w1[8], x0[8], x1[8];
+            *(int4 *) &w0[0] = *(const int4 *) &Ws[kb][2 * ty][0];
+            *(int4 *) &w0[4] = *(const int4 *) &Ws[kb][2 * ty][4];
+            *(int4 *) &w1[0] = *(const int4 *) &Ws[kb][2 * ty + 1][0];
+            *(int4 *) &w1[4] = *(const int4 *) &Ws[kb][2 * ty + 1][4];
+            *(int4 *) &x0[0] = *(const int4 *) &Xs[kb][tx][0];
+            *(int4 *) &x0[4] = *(const int4 *) &Xs[kb][tx][4];
+            *(int4 *) &x1[0] = *(const int4 *) &Xs[kb][tx + 16][0];
+            *(int4 *) &x1[4] = *(const int4 *) &Xs[kb][tx + 16][4];
+            const float dw0 = dWs[kb][2 * ty], dw1 = dWs[kb][2 * ty + 1];
+            const f32x2 dx = pack2(dXs[kb][tx], dXs[kb][tx + 16]);
+            const f32x2 d0 = mul2(pack2(dw0, dw0), dx);
+            const f32x2 d1 = mul2(pack2(dw1, dw1), dx);
 #pragma unroll
-            for (int a = 0; a < 8; ++a)
-#pragma unroll
-                for (int b = 0; b < 8; ++b) {
-                    const float q = __fadd_rn(__int_as_float(__dp4a(wv[a], xv[b], MAGIC_I)), -MAGIC_F);
-                    acc[a][b] = __fmaf_rn(__fmul_rn(dw[a], dx[b]), q, acc[a][b]);
-                }
+            for (int jj = 0; jj < 8; ++jj) {
+                const f32x2 q0 = add2(pack2i(__dp4a(w0[jj], x0[jj], MAGIC_I), __dp4a(w0[jj], x1[jj], MAGIC_I)), neg_magic);
+                const f32x2 q1 = add2(pack2i(__dp4a(w1[jj], x0[jj], MAGIC_I), __dp4a(w1[jj], x1[jj], MAGIC_I)), neg_magic);
+                acc[0][jj] = fma2(d0, q0, acc[0][jj]);
+                acc[1][jj] = fma2(d1, q1, acc[1][jj]);
+            }
         }
         __syncthreads();
     }
 
-    // hsum_float_8: (l0+l4, l1+l5, l2+l6, l3+l7) -> (+2) -> (+1); afterwards all eight lanes hold the sum
+    // hsum_float_8: (l0+l4, l1+l5, l2+l6, l3+l7) -> (+2) -> (+1), both columns at once
 #pragma unroll
-    for (int a = 0; a < 8; ++a)
-#pragma unroll
-        for (int b = 0; b < 8; ++b) {
-            float v = acc[a][b];
-            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
-            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
-            v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
-            acc[a][b] = v;
-        }
-    // the tile goes through shared memory so that the epilogue reads and writes global memory in full rows
-    float (*Cs)[BM + 1] = (float (*)[BM + 1]) smem_i;          // [BN][BM+1], fits in the W staging area
-#pragma unroll
-    for (int a = 0; a < 8; ++a) {
-        if (a == j) {
-#pragma unroll
-            for (int b = 0; b < 8; ++b) Cs[gn * 8 + b][gm * 8 + a] = acc[a][b];
-        }
+    for (int r = 0; r < 2; ++r) {
+        const f32x2 r0 = add2(acc[r][4], acc[r][0]), r1 = add2(acc[r][5], acc[r][1]);
+        const f32x2 r2 = add2(acc[r][6], acc[r][2]), r3 = add2(acc[r][7], acc[r][3]);
+        const f32x2 s  = add2(add2(r0, r2), add2(r1, r3));
+        float lo, hi;
+        unpack2(s, lo, hi);
+        Cs[tx][2 * ty + r]      = lo;
+        Cs[tx + 16][2 * ty + r] = hi;
     }
     __syncthreads();
-    {
-        const int ml = tid & 63;
+    {   // epilogue with full-row global accesses
+        const int ml = tid & 31;
         const int64_t m = m0 + ml;
         if (m < M) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int nl = (tid >> 6) + 4 * i;
+            for (int i = 0; i < 4; ++i) {
+                const int nl = (tid >> 5) + 8 * i;
                 const int64_t n = n0 + nl;
                 if (n < N) {
                     const float v = gemm_ep_apply(ep, n, m, Cs[nl][ml]);
@@ -352,7 +373,7 @@ extern "C" int b200_mul_mat_q_ep(int wtype, const void * w_planes, int64_t nb_to
             } else if (e.kind[s] != B200_EP_SCALE) return B200_ERR_ARG;
         }
     }
-    dim3 grid((unsigned) ((M + 63) / 64), (unsigned) ((N + 31) / 32));
+    dim3 grid((unsigned) ((M + 31) / 32), (unsigned) ((N + 31) / 32));
     const QPlanes w = q_planes(wtype, w_planes, nb_total);
     if (wtype == B200_TYPE_Q5_0)
         k_mul_mat_q<B200_TYPE_Q5_0><<<grid, 256, 0, as_stream(stream)>>>(w, M, nbk, xq, xd, N, dst, dst_stride, e);
