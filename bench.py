@@ -176,11 +176,11 @@ def main():
         torch.cuda.synchronize()
 
     cores = len(os.sched_getaffinity(0))
-    n_states = args.states or max(1, min(16, cores // max(1, world)))
+    n_states = args.states or min(32, max(1, args.clips // world))      # decode steps of concurrent states are merged in the plugin
     path = model_file(pkg, args.arch, args.wtype, rank, barrier)
     clips_rank = args.clips // world
     pcm = make_pcm(pkg, clips_rank, 1000 + rank * clips_rank)
-    w = pkg.Whisper(path, use_gpu=True, flash_attn=True, gpu_device=local, n_states=n_states, threads=max(1, cores // max(1, world)))
+    w = pkg.Whisper(path, use_gpu=True, flash_attn=True, gpu_device=local, n_states=n_states, threads=1)
     lib = w.lib
 
     def stat(name):

@@ -704,7 +704,9 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
         auto flush = [&]() -> int {
             if (!n_cols) return 0;
             int e = 0;
-            if (K <= COLQ_MAX_K) {
+            if (n_cols <= 4) {
+                e = b200_mul_mat_vec_q_cols((int) w->type, w->data, nb_total, M, K, cols, n_cols, &ep, st);
+            } else if (K <= COLQ_MAX_K) {
                 // the columns are quantised once and stay valid for the products that follow immediately on the same
                 // activations (the K, V and Q projections of a layer)
                 const bool reuse = ctx->colq_seq + 1 == ctx->item_seq && ctx->colq_K == K && (int) ctx->colq_ptrs.size() == n_cols &&

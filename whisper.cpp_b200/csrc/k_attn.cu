@@ -239,7 +239,7 @@ k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
 // replays the running sum.  Every query row carries its own K/V/mask/output pointers and key count.
 #define FA_DEC_THREADS 256
 #define FA_DEC_MAX_KV  8192
-#define FA_DEC_CHUNK   256
+#define FA_DEC_CHUNK   128
 #define FA_DEC_MAX_ROWS 32
 struct FaRow {
     const char * q;        // 64 f32 per head, head stride nbq2

@@ -802,6 +802,11 @@ static int launch_skinny(const QPlanes & w, int64_t M, int nbk, const int8_t * x
 template <int TYPE>
 static int launch_skinny_n(const QPlanes & w, int64_t M, int nbk, const int8_t * xq, const float * xd, int n_cols, const GemvCols32 & cols,
                            const GemvEp & ep, cudaStream_t st) {
+    if (M >= 16384 && n_cols > 4) {      // tall matrices (logits): more rows per CTA so that the columns are staged fewer times
+        if (n_cols <= 8)  return launch_skinny<TYPE, 32, 8>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
+        if (n_cols <= 16) return launch_skinny<TYPE, 32, 16>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
+        return launch_skinny<TYPE, 32, 32>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
+    }
     if (n_cols == 1)  return launch_skinny<TYPE, 32, 1>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
     if (n_cols == 2)  return launch_skinny<TYPE, 16, 1>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
     if (n_cols <= 4)  return launch_skinny<TYPE, 8, 1>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
