@@ -854,8 +854,14 @@ static int run_plan(b200_backend_ctx * ctx, const exec_plan & plan, struct ggml_
         if (timing) {
             double work = 0;
             struct ggml_tensor * node = ggml_graph_node(gs[0], it.node);
-            t_class->push_back(it.kind == PK_LAYER_NORM ? (node_class(node, &work), TC_NORM) : node_class(node, &work));
-            t_work->push_back(work * n_g);
+            const int cls = it.kind == PK_LAYER_NORM ? (node_class(node, &work), TC_NORM) : node_class(node, &work);
+            t_class->push_back(cls);
+            if (cls == TC_MMQ_VEC) {      // the weights cross HBM once per launch group, activations and results once per state
+                const double wbytes = (double) ggml_nbytes(node->src[0]);
+                t_work->push_back(wbytes + (work - wbytes) * n_g);
+            } else {
+                t_work->push_back(work * n_g);
+            }
             cudaEventRecord(next_event(), ctx->stream);
         }
         const int e = run_item(ctx, it, gs, n_g);
@@ -959,7 +965,7 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
     }
 
     // ---- batched path -------------------------------------------------------------------------
-    if (batching && fuse && !timing && B.alive > 1 && is_decode_graph(cgraph)) {
+    if (batching && fuse && B.alive > 1 && is_decode_graph(cgraph)) {
         batch_req req = { ctx, cgraph, graph_signature(cgraph), 0, nullptr };
         const int64_t t_arrive = now_ns();
         ctx->last_decode_ns = t_arrive;
@@ -1036,8 +1042,20 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
                 size_t n_ev = 0;
                 g_ns_lead_prep += now_ns() - t_p0;
                 const int64_t t_l0 = now_ns();
-                rc = run_plan(ctx, plan_copy, gs.data(), (int) gs.size(), false, nullptr, nullptr, &n_ev);
+                std::vector<int>    bt_class;
+                std::vector<double> bt_work;
+                rc = run_plan(ctx, plan_copy, gs.data(), (int) gs.size(), timing, &bt_class, &bt_work, &n_ev);
                 g_ns_lead_launch += now_ns() - t_l0;
+                if (rc == 0 && timing && !bt_class.empty() && cudaStreamSynchronize(ctx->stream) == cudaSuccess) {
+                    std::lock_guard<std::mutex> tl(g_timing_mu);
+                    for (size_t k = 0; k < bt_class.size(); ++k) {
+                        float ms = 0;
+                        cudaEventElapsedTime(&ms, ctx->events[2 * k], ctx->events[2 * k + 1]);
+                        g_tc_ms[bt_class[k]] += ms;
+                        g_tc_work[bt_class[k]] += bt_work[k];
+                        g_tc_count[bt_class[k]] += 1;
+                    }
+                }
                 if (rc == 0 && !served.empty()) rc = cudaEventRecord(ev, ctx->stream) == cudaSuccess ? 0 : (int) cudaGetLastError();
                 g_batched_graphs += (int64_t) gs.size();
                 g_batches += 1;
