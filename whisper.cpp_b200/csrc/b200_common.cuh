@@ -13,8 +13,10 @@ extern std::atomic<int64_t> g_b200_launches;
 
 static inline cudaStream_t as_stream(void * s) { return (cudaStream_t) s; }
 
-// f32 -> f16 round-to-nearest-even -> f32, the F16C round trip of GGML_FP32_TO_FP16 / GGML_FP16_TO_FP32
-__device__ __forceinline__ float round_f16(float x) { return __half2float(__float2half_rn(x)); }
+// f32 -> f16 round-to-nearest-even -> f32, the F16C round trip of GGML_FP32_TO_FP16 / GGML_FP16_TO_FP32.
+// The packed conversion (cvt.rn.f16x2.f32) is used on purpose: the scalar f32->f16 conversion issues to the
+// quarter-rate conversion unit, which throttles the sequential F16 accumulation of the attention kernels.
+__device__ __forceinline__ float round_f16(float x) { return __low2float(__floats2half2_rn(x, 0.0f)); }
 
 struct Dims4 { int64_t ne[4]; int64_t nb[4]; };
 

@@ -237,7 +237,7 @@ k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
 // possible: all threads score the keys, a block scan gives every key the running maximum it meets, exp() runs in
 // parallel, then 64 threads (one per output dim) replay the F16 accumulation key by key while one more thread
 // replays the running sum.  Every query row carries its own K/V/mask/output pointers and key count.
-#define FA_DEC_THREADS 256
+#define FA_DEC_THREADS 128
 #define FA_DEC_MAX_KV  8192
 #define FA_DEC_CHUNK   128
 #define FA_DEC_MAX_ROWS 32
@@ -259,7 +259,9 @@ template <bool S_FMA>
 __global__ void __launch_bounds__(FA_DEC_THREADS)
 k_flash_attn_decode(FaRows rows, int max_kv) {
     extern __shared__ __align__(16) float fa_smem[];
-    const FaRow & R = rows.r[blockIdx.x];
+    // heads of one query row are neighbours in launch order: they walk the same K/V rows (d_model wide, 128 bytes per
+    // head) at about the same time, which keeps the DRAM pages they share open
+    const FaRow & R = rows.r[blockIdx.y];
     const int n_kv = R.n_kv;
     float * Qs  = fa_smem;                 // [64]
     float * sc  = Qs + 64;                 // [n_kv] scores, later vs (-0.0f marks a skipped key)
@@ -269,7 +271,7 @@ k_flash_attn_decode(FaRows rows, int max_kv) {
     __shared__ float seg_max[FA_DEC_THREADS];
     __shared__ float s_S;
     const int tid = threadIdx.x;
-    const int64_t h = blockIdx.y;
+    const int64_t h = blockIdx.x;
     const int64_t nbk1 = rows.nbk1, nbv1 = rows.nbv1;
     const float scale = rows.scale;
 
@@ -366,26 +368,31 @@ k_flash_attn_decode(FaRows rows, int max_kv) {
     }
     __syncthreads();
 
-    // V is streamed through shared memory in chunks of FA_DEC_CHUNK keys, double buffered: warps 3..7 fetch chunk c+1
-    // while warps 0..1 (one thread per output dim) replay the F16 accumulation over chunk c and one thread of
-    // warp 2 replays the running sum.  Keys are taken eight at a time with all operands in registers; only groups that
+    // V is streamed through shared memory in chunks of FA_DEC_CHUNK keys, double buffered: chunk c+1 is copied
+    // asynchronously while warps 0..1 (one thread per output dim) replay the F16 accumulation over chunk c and one
+    // thread of warp 2 replays the running sum.  Keys are taken eight at a time with all operands in registers; only groups that
     // contain a new maximum take the path that rescales the accumulator.
     {
         const int n_chunks = (n_kv + FA_DEC_CHUNK - 1) / FA_DEC_CHUNK;
+        // asynchronous 16-byte copies (global -> shared, no register staging): every thread queues its share of the next
+        // chunk before it turns to its role, so the whole chunk is in flight while the current one is consumed
         auto fetch = [&](int c) {
             const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
-            uint4 * dstv = (uint4 *) (Vs + (size_t) (c & 1) * FA_DEC_CHUNK * 64);
-            for (int t = tid - 96; t < kn * 8; t += FA_DEC_THREADS - 96)
-                dstv[t] = *(const uint4 *) (vh + (int64_t) (k0 + (t >> 3)) * nbv1 + (t & 7) * 16);
+            const unsigned base = (unsigned) __cvta_generic_to_shared(Vs + (size_t) (c & 1) * FA_DEC_CHUNK * 64);
+            for (int t = tid; t < kn * 8; t += FA_DEC_THREADS) {
+                const char * src = vh + (int64_t) (k0 + (t >> 3)) * nbv1 + (t & 7) * 16;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(base + t * 16), "l"(src) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
         };
-        if (tid >= 96) fetch(0);
+        fetch(0);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
         float a = 0.0f, S = 0.0f;
         for (int c = 0; c < n_chunks; ++c) {
             const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
-            if (tid >= 96) {
-                if (c + 1 < n_chunks) fetch(c + 1);
-            } else if (tid < 64) {
+            if (c + 1 < n_chunks) fetch(c + 1);
+            if (tid < 64) {
                 const __half * vb = Vs + (size_t) (c & 1) * FA_DEC_CHUNK * 64 + tid;
                 int i = 0;
                 for (; i + 8 <= kn; i += 8) {
@@ -426,6 +433,7 @@ k_flash_attn_decode(FaRows rows, int max_kv) {
                 }
                 for (; i < kn; ++i) S = S_FMA ? __fmaf_rn(S, msv[k0 + i], sc[k0 + i]) : __fadd_rn(__fmul_rn(S, msv[k0 + i]), sc[k0 + i]);
             }
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
             __syncthreads();
         }
         if (tid < 64) Qs[tid] = a;         // Qs is free now
@@ -453,7 +461,7 @@ static int launch_fa_decode(const FaRows & rows, int n_rows, int64_t n_head, cud
         cudaFuncSetAttribute(k_flash_attn_decode<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) fa_dec_smem(FA_DEC_MAX_KV));
         attr_done[dev] = true;
     }
-    dim3 grid((unsigned) n_rows, (unsigned) n_head);
+    dim3 grid((unsigned) n_head, (unsigned) n_rows);
     if (g_fa_s_fma) k_flash_attn_decode<true><<<grid, FA_DEC_THREADS, fa_dec_smem(max_kv), st>>>(rows, max_kv);
     else            k_flash_attn_decode<false><<<grid, FA_DEC_THREADS, fa_dec_smem(max_kv), st>>>(rows, max_kv);
     B200_RETURN_LAST();

@@ -799,9 +799,125 @@ static int launch_skinny(const QPlanes & w, int64_t M, int nbk, const int8_t * x
     B200_RETURN_LAST();
 }
 
+// Second form of the skinny product: a thread owns one weight row and a PAIR of columns with all eight lane sums of
+// both (eight packed f32x2 accumulators), so the block scale is formed once per output and every lane update is one
+// packed FMA.  R rows per CTA, blockDim = R * ceil(n_cols / 2).
+template <int TYPE, int R>
+__global__ void __launch_bounds__(256)
+k_gemv_skinny2(QPlanes w, int64_t M, int nbk, const int8_t * __restrict__ xq, const float * __restrict__ xd, int n_cols,
+               GemvCols32 cols, GemvEp ep) {
+    extern __shared__ __align__(16) unsigned char sk_smem[];
+    const int CP  = (n_cols + 1) >> 1;
+    const int WS  = nbk * 8;                                          // words per weight row
+    const int XS  = nbk * 8 + 4;                                      // words per column, == 4 mod 32: conflict-free LDS.128 across columns
+    int *   Wsm = (int *) sk_smem;                                    // [R][WS]
+    int *   Xsm = Wsm + R * WS;                                       // [n_cols][XS]
+    float * dW  = (float *) (Xsm + n_cols * XS);                      // [R][nbk]
+    float * dX  = dW + R * nbk;                                       // [n_cols][nbk]
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int64_t row0 = (int64_t) blockIdx.x * R;
+
+    for (int it = tid; it < R * nbk; it += nthr) {
+        const int r = it / nbk, ib = it - r * nbk;
+        const int64_t m = row0 + r;
+        int wv[8];
+        float dw = 0.0f;
+#pragma unroll
+        for (int t = 0; t < 8; ++t) wv[t] = 0;
+        if (m < M) {
+            const int64_t blk = m * nbk + ib;
+            if (TYPE == B200_TYPE_Q5_0) {
+                const uint4    q  = __ldg(((const uint4 *) w.qs) + blk);
+                const uint32_t qh = __ldg(w.qh + blk);
+                const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int t = 0; t < 8; ++t) wv[t] = q5_lane_word(qw[t & 3], qh, t);
+            } else {
+                const uint4 a = __ldg(((const uint4 *) w.qs) + blk * 2), b = __ldg(((const uint4 *) w.qs) + blk * 2 + 1);
+                wv[0] = a.x; wv[1] = a.y; wv[2] = a.z; wv[3] = a.w;
+                wv[4] = b.x; wv[5] = b.y; wv[6] = b.z; wv[7] = b.w;
+            }
+            dw = __half2float(w.d[blk]);
+        }
+        *(int4 *) &Wsm[r * WS + ib * 8]     = make_int4(wv[0], wv[1], wv[2], wv[3]);
+        *(int4 *) &Wsm[r * WS + ib * 8 + 4] = make_int4(wv[4], wv[5], wv[6], wv[7]);
+        dW[r * nbk + ib] = dw;
+    }
+    {
+        const uint4 * src = (const uint4 *) xq;
+        const int per_col = nbk * 2;                                  // 16-byte pieces per column
+        for (int it = tid; it < n_cols * per_col; it += nthr) {
+            const int c = it / per_col, pz = it - c * per_col;
+            *(uint4 *) &Xsm[c * XS + pz * 4] = src[it];
+        }
+        for (int it = tid; it < n_cols * nbk; it += nthr) dX[it] = xd[it];
+    }
+    __syncthreads();
+
+    const int r = tid / CP, cp = tid - r * CP;
+    const int cA = cp, cB = min(cp + CP, n_cols - 1);
+    f32x2 acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0ull;
+    const int *   wrow = Wsm + r * WS;
+    const int *   xa   = Xsm + cA * XS;
+    const int *   xb   = Xsm + cB * XS;
+    const float * dwr  = dW + r * nbk;
+    const float * dxa  = dX + cA * nbk;
+    const float * dxb  = dX + cB * nbk;
+    const f32x2 neg_magic = pack2(-MAGIC_F, -MAGIC_F);
+#pragma unroll 2
+    for (int ib = 0; ib < nbk; ++ib) {
+        int wv[8], x0[8], x1[8];
+        *(int4 *) &wv[0] = *(const int4 *) &wrow[ib * 8];
+        *(int4 *) &wv[4] = *(const int4 *) &wrow[ib * 8 + 4];
+        *(int4 *) &x0[0] = *(const int4 *) &xa[ib * 8];
+        *(int4 *) &x0[4] = *(const int4 *) &xa[ib * 8 + 4];
+        *(int4 *) &x1[0] = *(const int4 *) &xb[ib * 8];
+        *(int4 *) &x1[4] = *(const int4 *) &xb[ib * 8 + 4];
+        const float dw = dwr[ib];
+        const f32x2 d = mul2(pack2(dw, dw), pack2(dxa[ib], dxb[ib]));
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const f32x2 q = add2(pack2i(__dp4a(wv[j], x0[j], MAGIC_I), __dp4a(wv[j], x1[j], MAGIC_I)), neg_magic);
+            acc[j] = fma2(d, q, acc[j]);
+        }
+    }
+    const f32x2 r0 = add2(acc[4], acc[0]), r1 = add2(acc[5], acc[1]);
+    const f32x2 r2 = add2(acc[6], acc[2]), r3 = add2(acc[7], acc[3]);
+    const f32x2 sres = add2(add2(r0, r2), add2(r1, r3));
+    float lo, hi;
+    unpack2(sres, lo, hi);
+    const int64_t m = row0 + r;
+    if (m < M) {
+        ep_store32(ep, cols, cA, m, lo);
+        if (cp + CP < n_cols) ep_store32(ep, cols, cp + CP, m, hi);
+    }
+}
+
+template <int TYPE, int R>
+static int launch_skinny2(const QPlanes & w, int64_t M, int nbk, const int8_t * xq, const float * xd, int n_cols, const GemvCols32 & cols,
+                          const GemvEp & ep, cudaStream_t st) {
+    const int CP = (n_cols + 1) / 2;
+    const size_t smem = ((size_t) R * nbk * 8 + (size_t) n_cols * (nbk * 8 + 4) + (size_t) R * nbk + (size_t) n_cols * nbk) * 4;
+    if (smem > 220 * 1024 || R * CP > 256) return B200_ERR_ARG;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaFuncSetAttribute(k_gemv_skinny2<TYPE, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        attr_done[dev] = true;
+    }
+    k_gemv_skinny2<TYPE, R><<<(unsigned) ((M + R - 1) / R), R * CP, smem, st>>>(w, M, nbk, xq, xd, n_cols, cols, ep);
+    B200_RETURN_LAST();
+}
+
 template <int TYPE>
 static int launch_skinny_n(const QPlanes & w, int64_t M, int nbk, const int8_t * xq, const float * xd, int n_cols, const GemvCols32 & cols,
                            const GemvEp & ep, cudaStream_t st) {
+    // measured on B200: the column-pair form wins for many columns on short rows and for the tall logits matrix
+    if (n_cols >= 9 && M >= 16384) return launch_skinny2<TYPE, 16>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
+    if (n_cols >= 17 && nbk <= 80) return launch_skinny2<TYPE, 8>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
     if (M >= 16384 && n_cols > 4) {      // tall matrices (logits): more rows per CTA so that the columns are staged fewer times
         if (n_cols <= 8)  return launch_skinny<TYPE, 32, 8>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
         if (n_cols <= 16) return launch_skinny<TYPE, 32, 16>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
