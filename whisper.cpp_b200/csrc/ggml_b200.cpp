@@ -19,6 +19,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <condition_variable>
+#include <memory>
 #include <mutex>
 #include <string>
 #include <unordered_map>
@@ -890,6 +891,7 @@ struct batch_req {
     uint64_t             sig;
     int                  state;     // 0 waiting, 1 done (stream must wait on ev), 2 run it yourself, 3 failed
     cudaEvent_t          ev;
+    int                  fits;      // checked against the cached plan by the submitting thread: 1 yes, -1 no, 0 not checked
 };
 
 struct device_batcher {
@@ -899,7 +901,7 @@ struct device_batcher {
     bool                    leader_active = false;
     std::vector<cudaEvent_t> events;       // round-robin pool
     size_t                  next_event = 0;
-    std::unordered_map<uint64_t, exec_plan> plans;      // by signature, fused
+    std::unordered_map<uint64_t, std::shared_ptr<const exec_plan>> plans;      // by signature, fused
     int                     alive = 0;                  // backend instances on this device
     double                  step_ns_ema = 0;            // typical time from "step enqueued" to "next step arrives"
 
@@ -966,9 +968,18 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
 
     // ---- batched path -------------------------------------------------------------------------
     if (batching && fuse && B.alive > 1 && is_decode_graph(cgraph)) {
-        batch_req req = { ctx, cgraph, graph_signature(cgraph), 0, nullptr };
+        batch_req req = { ctx, cgraph, graph_signature(cgraph), 0, nullptr, 0 };
         const int64_t t_arrive = now_ns();
         ctx->last_decode_ns = t_arrive;
+        {   // every thread checks its own graph against the cached plan, in parallel with the others
+            std::shared_ptr<const exec_plan> known;
+            {
+                std::lock_guard<std::mutex> lk0(B.mu);
+                auto pit = B.plans.find(req.sig);
+                if (pit != B.plans.end()) known = pit->second;
+            }
+            if (known) req.fits = graph_fits_plan(*known, cgraph) ? 1 : -1;
+        }
         std::unique_lock<std::mutex> lk(B.mu);
         {
             const int64_t t_served = ctx->served_ns.exchange(0);
@@ -1018,26 +1029,32 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
             if (B.events.size() < 64) { cudaEvent_t e; cudaEventCreateWithFlags(&e, cudaEventDisableTiming); B.events.push_back(e); }
             ev = B.events[B.next_event++ % B.events.size()];
             // plan of the leader's structure (cached by signature)
-            exec_plan * plan = nullptr;
-            auto pit = B.plans.find(req.sig);
-            if (pit == B.plans.end()) {
-                if (B.plans.size() > 256) B.plans.clear();
-                plan = &B.plans[req.sig];
-                build_plan(cgraph, *plan, true);
-            } else {
-                plan = &pit->second;
+            std::shared_ptr<const exec_plan> plan_sp;
+            {
+                auto pit = B.plans.find(req.sig);
+                if (pit == B.plans.end()) {
+                    if (B.plans.size() > 256) B.plans.clear();
+                    auto fresh = std::make_shared<exec_plan>();
+                    build_plan(cgraph, *fresh, true);
+                    plan_sp = fresh;
+                    B.plans[req.sig] = plan_sp;
+                    req.fits = 0;                                   // not yet checked against this plan
+                } else {
+                    plan_sp = pit->second;
+                }
             }
-            const exec_plan plan_copy = *plan;                    // the map may change once the lock is dropped
+            const exec_plan & plan_copy = *plan_sp;
             lk.unlock();
 
             std::vector<struct ggml_cgraph *> gs;
             std::vector<batch_req *> served;
             int rc = 0;
-            if (graph_fits_plan(plan_copy, cgraph)) {
+            auto fits = [&](batch_req * r) { return r->fits != 0 ? r->fits > 0 : graph_fits_plan(plan_copy, r->g); };
+            if (fits(&req)) {
                 gs.push_back(cgraph);
                 for (batch_req * r : mine) {
                     if (r == &req) continue;
-                    if (r->sig == req.sig && graph_fits_plan(plan_copy, r->g)) { gs.push_back(r->g); served.push_back(r); }
+                    if (r->sig == req.sig && fits(r)) { gs.push_back(r->g); served.push_back(r); }
                 }
                 size_t n_ev = 0;
                 g_ns_lead_prep += now_ns() - t_p0;
@@ -1094,13 +1111,13 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
         {
             std::lock_guard<std::mutex> lk(B.mu);
             auto pit = B.plans.find(sig);
-            if (pit != B.plans.end()) { plan = pit->second; have = true; }
+            if (pit != B.plans.end()) { plan = *pit->second; have = true; }
         }
         if (!have) {
             build_plan(cgraph, plan, fuse);
             std::lock_guard<std::mutex> lk(B.mu);
             if (B.plans.size() > 256) B.plans.clear();
-            B.plans[sig] = plan;
+            B.plans[sig] = std::make_shared<exec_plan>(plan);
         }
     }
     if (fuse && !graph_fits_plan(plan, cgraph)) build_plan(cgraph, plan, false);     // aliasing hazard somewhere: node by node
