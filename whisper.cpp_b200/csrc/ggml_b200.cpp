@@ -259,6 +259,7 @@ struct b200_backend_ctx {
     int64_t      colq_K = 0;
     int64_t      colq_seq = -2;              // ... written (or reused) by the item with this sequence number
     std::atomic<int64_t> served_ns{0};       // when a leader last enqueued a step for this instance (0: not in a batch)
+    cudaEvent_t  sync_event = nullptr;       // blocking-sync event: waiting threads sleep instead of spinning on a core
     int64_t      item_seq = 0;
 };
 #define COLQ_MAX_K 8192
@@ -277,6 +278,7 @@ static void b200_backend_free(ggml_backend_t backend) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->colq) cudaFree(ctx->colq);
+    if (ctx->sync_event) cudaEventDestroy(ctx->sync_event);
     for (cudaEvent_t e : ctx->events) cudaEventDestroy(e);
     cudaStreamDestroy(ctx->stream);
     delete ctx;
@@ -287,7 +289,10 @@ static void b200_backend_synchronize(ggml_backend_t backend) {
     b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
     cudaSetDevice(ctx->device);
     const int64_t t0 = now_ns();
-    cuda_ok(cudaStreamSynchronize(ctx->stream), "synchronize");
+    // With many whisper_states per GPU there are more host threads than cores; a spinning wait would take the cores
+    // away from the threads that are launching work.
+    if (ctx->sync_event && cudaEventRecord(ctx->sync_event, ctx->stream) == cudaSuccess) cuda_ok(cudaEventSynchronize(ctx->sync_event), "synchronize");
+    else cuda_ok(cudaStreamSynchronize(ctx->stream), "synchronize");
     g_host_ns_sync += now_ns() - t0;
 }
 
@@ -1197,6 +1202,7 @@ static ggml_backend_t b200_dev_init_backend(ggml_backend_dev_t dev, const char *
     if (!cuda_ok(cudaMalloc(&ctx->colq, (size_t) 32 * COLQ_MAX_K + (size_t) 32 * (COLQ_MAX_K / 32) * 4), "cudaMalloc(colq)")) {
         cudaStreamDestroy(ctx->stream); delete ctx; return nullptr;
     }
+    if (cudaEventCreateWithFlags(&ctx->sync_event, cudaEventBlockingSync | cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); ctx->sync_event = nullptr; }
     batcher_join(ctx);
     return new ggml_backend{ b200_guid(), b200_backend_iface, dev, ctx };
 }
