@@ -160,10 +160,21 @@ def main():
         run_reference(args, pkg)
         return
 
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    gpu_index = local
+    if world > 1:
+        # One process per GPU, and each process sees only its own GPU: whisper.cpp (src/whisper.cpp:1384-1405) always puts
+        # the first GPU-type device first in its weight buffer list, so weights would land on device 0 whatever gpu_device
+        # says; with a single visible device per process "device 0" is the right one.
+        visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+        ids = visible.split(",") if visible else [str(i) for i in range(64)]
+        os.environ["CUDA_VISIBLE_DEVICES"] = ids[local]
+        gpu_index = int(ids[local]) if ids[local].isdigit() else local
+        local = 0
+
     import torch
     import torch.distributed as dist
 
-    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py: no CUDA device; the B200 path has no CPU fallback")
     torch.cuda.set_device(local)
@@ -208,7 +219,7 @@ def main():
 
     def run_steps(kind):
         """W warm-up + K timed steps; returns (seconds of the timed steps (max over ranks), launches, h2d, d2h)."""
-        sampler = ClockSampler(local)
+        sampler = ClockSampler(gpu_index)
         times = []
         for s in range(args.warmup + args.steps):
             if s == args.warmup:
