@@ -110,6 +110,20 @@ int b200_mul_mat_cols_q(int wtype, const void * w_planes, int64_t nb_total, int6
                         const int8_t * xq, const float * xd, const b200_gemv_col * cols, int n_cols,
                         const b200_gemv_ep * ep, void * stream);
 
+/* The same product (ggml_compute_forward_mul_mat with ggml_vec_dot_q5_0_q8_0 / ggml_vec_dot_q8_0_q8_0, same bits)
+ * for many columns on the tensor pipe.  The integer lane sums of the AVX2 dot product are exact in an f16 MMA with
+ * f32 accumulation, the per-block float chain is replayed as in b200_mul_mat_q.  Operands are repacked once:
+ *   b200_mma_pack_weights: planes -> h[nb_total][16] u32 (the block's 32 integers as f16 pairs, pair 4r+t stored at
+ *                          position 4t+r) and d[nb_total] f32; 68 bytes per block, both 16-byte aligned.  No
+ *                          counterpart in the reference (layout helper, done once per weight tensor).
+ *   b200_mma_quantize:     quantize_row_q8_0 (ggml-cpu-quants.c:808-866) writing the same integers in that format.
+ *   b200_mul_mat_mma_ep:   dst[n*dst_stride + m] with the epilogue steps of b200_mul_mat_q_ep; K % 128 == 0. */
+int b200_mma_pack_weights(int wtype, const void * w_planes, int64_t nb_total, void * h, float * d, void * stream);
+int b200_mma_quantize(const float * x, int64_t n_rows, int64_t k, int64_t row_stride_bytes, void * h, float * d, void * stream);
+int b200_mul_mat_mma_ep(const void * wh, const float * wd, int64_t M, int64_t K,
+                        const void * xh, const float * xd, int64_t N,
+                        void * dst, int64_t dst_stride, const b200_epilogue * ep, void * stream);
+
 /* NORM -> MUL(gamma) -> ADD(beta) in one pass (ops.cpp:3109-3158 followed by binary-ops.cpp:50-137), each of the
  * three roundings kept: y = ((x - mean) * rstd) * gamma + beta. */
 int b200_layer_norm(const float * x, const float * gamma, const float * beta, float * y, int64_t ne00, int64_t nrows,

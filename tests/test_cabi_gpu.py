@@ -91,6 +91,45 @@ def test_mul_mat_q_both_paths(K, pkg, wtype, Kd, M, N):
     assert bits_equal(dst.cpu().numpy(), ref), "GEMM path"
 
 
+class EpStep(C.Structure):
+    _fields_ = [("kind", C.c_int), ("ptr", vp), ("stride_n", i64), ("scalar", C.c_float)]
+
+
+class Epilogue(C.Structure):
+    _fields_ = [("n_steps", C.c_int), ("step", EpStep * 4), ("store_f16", C.c_int)]
+
+
+@pytest.mark.parametrize("wtype", [6, 8])
+@pytest.mark.parametrize("Kd,M,N", [(384, 96, 40), (1280, 130, 73), (512, 64, 72), (2048, 70, 9), (128, 200, 150)])
+def test_mul_mat_mma_tensor_pipe_path(K, pkg, wtype, Kd, M, N):
+    """f16-MMA product (packed operands) against the restatement, bit for bit, ragged M / N tiles included."""
+    w, x = rnd(13, M, Kd, scale=0.02), rnd(14, N, Kd) * np.linspace(1e-3, 30, N, dtype=np.float32)[:, None]
+    x[N // 2] = 0
+    blocks, planes, nb = planes_of(K, pkg, wtype, w)
+    ref = O.mul_mat_q(wtype, blocks, M, Kd, x)
+    d_planes, dx, dst = dev(planes), dev(x), torch.zeros((N, M), device="cuda")
+    wh, wd = torch.empty((nb, 16), dtype=torch.int32, device="cuda"), torch.empty(nb, device="cuda")
+    xh, xd = torch.empty((N * Kd // 32, 16), dtype=torch.int32, device="cuda"), torch.empty(N * Kd // 32, device="cuda")
+    sync_ok(K.b200_mma_pack_weights(wtype, ptr(d_planes), i64(nb), ptr(wh), ptr(wd), None))
+    sync_ok(K.b200_mma_quantize(ptr(dx), i64(N), i64(Kd), i64(Kd * 4), ptr(xh), ptr(xd), None))
+    sync_ok(K.b200_mul_mat_mma_ep(ptr(wh), ptr(wd), i64(M), i64(Kd), ptr(xh), ptr(xd), i64(N), ptr(dst), i64(M), None, None))
+    assert bits_equal(dst.cpu().numpy(), ref)
+    # epilogue: + bias (broadcast over columns), GELU table, + residual, stored as f32; same steps on the dp4a path
+    bias, res = dev(rnd(15, M)), dev(rnd(16, N, M))
+    ep = Epilogue()
+    ep.n_steps = 3
+    ep.step[0].kind, ep.step[0].ptr, ep.step[0].stride_n = 1, bias.data_ptr(), 0
+    ep.step[1].kind = 3
+    ep.step[2].kind, ep.step[2].ptr, ep.step[2].stride_n = 1, res.data_ptr(), M
+    a, b = torch.zeros((N, M), device="cuda"), torch.zeros((N, M), device="cuda")
+    sync_ok(K.b200_mul_mat_mma_ep(ptr(wh), ptr(wd), i64(M), i64(Kd), ptr(xh), ptr(xd), i64(N), ptr(a), i64(M), C.byref(ep), None))
+    qs, d = torch.empty((N, Kd), dtype=torch.int8, device="cuda"), torch.empty((N, Kd // 32), device="cuda")
+    sync_ok(K.b200_quantize_q8_0(ptr(dx), i64(N), i64(Kd), i64(Kd * 4), ptr(qs), ptr(d), None))
+    sync_ok(K.b200_mul_mat_q_ep(wtype, ptr(d_planes), i64(nb), i64(M), i64(Kd), ptr(qs), ptr(d), i64(N), ptr(b), i64(M), C.byref(ep), None))
+    assert bits_equal(a.cpu().numpy(), b.cpu().numpy())
+    assert K.b200_mul_mat_mma_ep(ptr(wh), ptr(wd), i64(M), i64(96), ptr(xh), ptr(xd), i64(N), ptr(a), i64(M), None, None) != 0   # K % 128
+
+
 def test_mul_mat_q_rejects_bad_arguments(K):
     assert K.b200_mul_mat_vec_q(6, None, i64(0), i64(4), i64(48), None, i64(0), i64(1), None, i64(4), None) != 0   # K % 32
     assert K.b200_mul_mat_vec_q(6, None, i64(0), i64(4), i64(64), None, i64(0), i64(9), None, i64(4), None) != 0   # N > 8

@@ -87,9 +87,29 @@ struct b200_buffer_ctx {
     void * base;
 };
 
+// Tensor-pipe operands of quantised weight tensors (b200_mma_pack_weights), made on first use by a many-column
+// product and kept until the weight's buffer is written again or freed.  Key: device address of the tensor data.
+struct mma_weights { void * h; float * d; };
+static std::mutex g_mma_mu;
+static std::unordered_map<const void *, mma_weights> g_mma_cache;
+
+static void mma_cache_drop_range(const void * base, size_t size) {
+    std::lock_guard<std::mutex> lk(g_mma_mu);
+    for (auto it = g_mma_cache.begin(); it != g_mma_cache.end();) {
+        const char * p = (const char *) it->first;
+        if (p >= (const char *) base && p < (const char *) base + size) {
+            cudaFree(it->second.h);
+            it = g_mma_cache.erase(it);
+        } else {
+            ++it;
+        }
+    }
+}
+
 static void b200_buffer_free(ggml_backend_buffer_t buffer) {
     b200_buffer_ctx * ctx = (b200_buffer_ctx *) buffer->context;
     cudaSetDevice(ctx->device);
+    mma_cache_drop_range(ctx->base, buffer->size);
     cudaFree(ctx->base);
     delete ctx;
 }
@@ -101,6 +121,7 @@ static void * b200_buffer_get_base(ggml_backend_buffer_t buffer) {
 static void b200_buffer_memset_tensor(ggml_backend_buffer_t buffer, struct ggml_tensor * tensor, uint8_t value, size_t offset, size_t size) {
     b200_buffer_ctx * ctx = (b200_buffer_ctx *) buffer->context;
     cudaSetDevice(ctx->device);
+    if (is_quant(tensor->type)) mma_cache_drop_range(tensor->data, 1);
     cuda_ok(cudaMemsetAsync((char *) tensor->data + offset, value, size, cudaStreamPerThread), "memset_tensor");
     cuda_ok(cudaStreamSynchronize(cudaStreamPerThread), "memset_tensor sync");
 }
@@ -111,6 +132,7 @@ static void b200_buffer_set_tensor(ggml_backend_buffer_t buffer, struct ggml_ten
     cudaSetDevice(ctx->device);
     g_h2d_bytes += (int64_t) size;
     if (is_quant(tensor->type)) {
+        mma_cache_drop_range(tensor->data, 1);
         const size_t  bs = ggml_type_size(tensor->type);
         const int64_t nb_total = (int64_t) (ggml_nbytes(tensor) / bs);
         GGML_ASSERT(tensor->view_src == nullptr && "ggml-b200: views of block-quantised tensors are not supported");
@@ -192,6 +214,7 @@ static void b200_buffer_get_tensor(ggml_backend_buffer_t buffer, const struct gg
 static void b200_buffer_clear(ggml_backend_buffer_t buffer, uint8_t value) {
     b200_buffer_ctx * ctx = (b200_buffer_ctx *) buffer->context;
     cudaSetDevice(ctx->device);
+    mma_cache_drop_range(ctx->base, buffer->size);
     cuda_ok(cudaMemsetAsync(ctx->base, value, buffer->size, cudaStreamPerThread), "clear");
     cuda_ok(cudaStreamSynchronize(cudaStreamPerThread), "clear sync");
 }
@@ -310,6 +333,55 @@ static bool ensure_scratch(b200_backend_ctx * ctx, size_t size) {
     return true;
 }
 
+// Packed tensor-pipe copy of a quantised weight tensor; made once (pack kernel on this backend's stream, then a
+// stream synchronise under the lock, so that every other stream may use it afterwards).  Null when device memory
+// is short: the caller then keeps to the dp4a product.
+static bool mma_weights_of(b200_backend_ctx * ctx, const struct ggml_tensor * w, int64_t nb_total, mma_weights * out) {
+    std::lock_guard<std::mutex> lk(g_mma_mu);
+    auto it = g_mma_cache.find(w->data);
+    if (it != g_mma_cache.end()) { *out = it->second; return true; }
+    const size_t h_bytes = (size_t) nb_total * 64, d_bytes = (size_t) nb_total * 4;
+    void * p = nullptr;
+    if (cudaMalloc(&p, h_bytes + d_bytes) != cudaSuccess) { cudaGetLastError(); return false; }
+    mma_weights mw = { p, (float *) ((char *) p + h_bytes) };
+    if (b200_mma_pack_weights((int) w->type, w->data, nb_total, mw.h, mw.d, (void *) ctx->stream) != 0 ||
+        cudaStreamSynchronize(ctx->stream) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(p);
+        return false;
+    }
+    g_mma_cache[w->data] = mw;
+    *out = mw;
+    return true;
+}
+
+// Quantised weights x f32 activations for more than 8 columns: activations are quantised into this backend's
+// scratch, then the tensor-pipe product (K a multiple of 128, 32 columns or more) or the dp4a product runs.
+static int gemm_quant(b200_backend_ctx * ctx, const struct ggml_tensor * w, const float * x, int64_t x_stride_bytes, int64_t N,
+                      void * dst, int64_t ldd, const b200_epilogue * ep) {
+    static const bool use_mma = getenv("GGML_B200_NO_MMA") == nullptr;
+    void * st = (void *) ctx->stream;
+    const int64_t K = w->ne[0], M = w->ne[1];
+    const int64_t nb_total = (int64_t) (ggml_nbytes(w) / ggml_type_size(w->type));
+    mma_weights mw;
+    if (use_mma && N >= 32 && K % 128 == 0 && mma_weights_of(ctx, w, nb_total, &mw)) {
+        const size_t h_bytes = (size_t) N * (K / 32) * 64, d_bytes = (size_t) N * (K / 32) * 4;
+        if (!ensure_scratch(ctx, h_bytes + d_bytes)) return (int) cudaErrorMemoryAllocation;
+        float * xd = (float *) ((char *) ctx->scratch + h_bytes);
+        int e = b200_mma_quantize(x, N, K, x_stride_bytes, ctx->scratch, xd, st);
+        if (e) return e;
+        return b200_mul_mat_mma_ep(mw.h, mw.d, M, K, ctx->scratch, xd, N, dst, ldd, ep, st);
+    }
+    const size_t q_bytes = (size_t) N * K, d_bytes = (size_t) N * (K / 32) * 4;
+    const size_t q_pad = (q_bytes + 255) & ~(size_t) 255;
+    if (!ensure_scratch(ctx, q_pad + d_bytes)) return (int) cudaErrorMemoryAllocation;
+    int8_t * xq = (int8_t *) ctx->scratch;
+    float *  xd = (float *) ((char *) ctx->scratch + q_pad);
+    int e = b200_quantize_q8_0(x, N, K, x_stride_bytes, xq, xd, st);
+    if (e) return e;
+    return b200_mul_mat_q_ep((int) w->type, w->data, nb_total, M, K, xq, xd, N, dst, ldd, ep, st);
+}
+
 static bool is_view_op(enum ggml_op op) {
     return op == GGML_OP_NONE || op == GGML_OP_RESHAPE || op == GGML_OP_VIEW || op == GGML_OP_PERMUTE || op == GGML_OP_TRANSPOSE;
 }
@@ -336,14 +408,7 @@ static int compute_node(b200_backend_ctx * ctx, struct ggml_tensor * node) {
                     return b200_mul_mat_vec_q((int) s0->type, s0->data, nb_total, M, K, (const float *) s1->data, nb1[1], N,
                                               (float *) node->data, nbd[1] / 4, st);
                 }
-                const size_t q_bytes = (size_t) N * K, d_bytes = (size_t) N * (K / 32) * 4;
-                const size_t q_pad = (q_bytes + 255) & ~(size_t) 255;
-                if (!ensure_scratch(ctx, q_pad + d_bytes)) return (int) cudaErrorMemoryAllocation;
-                int8_t * xq = (int8_t *) ctx->scratch;
-                float *  xd = (float *) ((char *) ctx->scratch + q_pad);
-                int e = b200_quantize_q8_0((const float *) s1->data, N, K, nb1[1], xq, xd, st);
-                if (e) return e;
-                return b200_mul_mat_q((int) s0->type, s0->data, nb_total, M, K, xq, xd, N, (float *) node->data, nbd[1] / 4, st);
+                return gemm_quant(ctx, s0, (const float *) s1->data, nb1[1], N, node->data, nbd[1] / 4, nullptr);
             }
             return b200_mul_mat_f16(s0->data, ne0, nb0, s1->data, (int) s1->type, ne1, nb1, (float *) node->data, nbd, st);
         }
@@ -789,15 +854,8 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
                     ep.step[s].stride_n = o->ne[1] == 1 ? 0 : (int64_t) o->nb[1] / 4;
                 }
             }
-            const size_t q_bytes = (size_t) N * K, d_bytes = (size_t) N * (K / 32) * 4;
-            const size_t q_pad = (q_bytes + 255) & ~(size_t) 255;
-            if (!ensure_scratch(ctx, q_pad + d_bytes)) return (int) cudaErrorMemoryAllocation;
-            int8_t * xq = (int8_t *) ctx->scratch;
-            float *  xd = (float *) ((char *) ctx->scratch + q_pad);
-            int e = b200_quantize_q8_0((const float *) x->data, N, K, (int64_t) x->nb[1], xq, xd, st);
-            if (e) return e;
             const int64_t ldd = it.store_f16 ? M : (int64_t) out->nb[1] / 4;
-            e = b200_mul_mat_q_ep((int) w->type, w->data, nb_total, M, K, xq, xd, N, out->data, ldd, &ep, st);
+            int e = gemm_quant(ctx, w, (const float *) x->data, (int64_t) x->nb[1], N, out->data, ldd, &ep);
             if (e) return e;
         }
         return 0;

@@ -239,7 +239,8 @@ k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
 // replays the running sum.  Every query row carries its own K/V/mask/output pointers and key count.
 #define FA_DEC_THREADS 128
 #define FA_DEC_MAX_KV  8192
-#define FA_DEC_CHUNK   128
+#define FA_DEC_CHUNK   64
+#define FA_DEC_STAGES  3
 #define FA_DEC_MAX_ROWS 32
 struct FaRow {
     const char * q;        // 64 f32 per head, head stride nbq2
@@ -267,7 +268,7 @@ k_flash_attn_decode(FaRows rows, int max_kv) {
     float * sc  = Qs + 64;                 // [n_kv] scores, later vs (-0.0f marks a skipped key)
     float * msv = sc + max_kv;             // [n_kv] ms (1 unless a new maximum)
     unsigned char * evt = (unsigned char *) (msv + max_kv);                 // [n_kv/8] group contains a new maximum
-    __half * Vs = (__half *) (fa_smem + ((64 + 2 * max_kv + (max_kv + 31) / 32 + 3) & ~3));   // [2][FA_DEC_CHUNK][64], 16-byte aligned
+    __half * Vs = (__half *) (fa_smem + ((64 + 2 * max_kv + (max_kv + 31) / 32 + 3) & ~3));   // [FA_DEC_STAGES][FA_DEC_CHUNK][64], 16-byte aligned
     __shared__ float seg_max[FA_DEC_THREADS];
     __shared__ float s_S;
     const int tid = threadIdx.x;
@@ -368,9 +369,10 @@ k_flash_attn_decode(FaRows rows, int max_kv) {
     }
     __syncthreads();
 
-    // V is streamed through shared memory in chunks of FA_DEC_CHUNK keys, double buffered: chunk c+1 is copied
-    // asynchronously while warps 0..1 (one thread per output dim) replay the F16 accumulation over chunk c and one
-    // thread of warp 2 replays the running sum.  Keys are taken eight at a time with all operands in registers; only groups that
+    // V is streamed through shared memory in chunks of FA_DEC_CHUNK keys, FA_DEC_STAGES buffers: chunks c+1 and c+2 are
+    // being copied asynchronously while warps 0..1 (one thread per output dim) replay the F16 accumulation over chunk c
+    // and one thread of warp 2 replays the running sum.  The buffers are kept small so that every (row, head) CTA of 32
+    // rows x 20 heads is resident at once (no second wave).  Keys are taken eight at a time with all operands in registers; only groups that
     // contain a new maximum take the path that rescales the accumulator.
     {
         const int n_chunks = (n_kv + FA_DEC_CHUNK - 1) / FA_DEC_CHUNK;
@@ -378,7 +380,7 @@ k_flash_attn_decode(FaRows rows, int max_kv) {
         // chunk before it turns to its role, so the whole chunk is in flight while the current one is consumed
         auto fetch = [&](int c) {
             const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
-            const unsigned base = (unsigned) __cvta_generic_to_shared(Vs + (size_t) (c & 1) * FA_DEC_CHUNK * 64);
+            const unsigned base = (unsigned) __cvta_generic_to_shared(Vs + (size_t) (c % FA_DEC_STAGES) * FA_DEC_CHUNK * 64);
             for (int t = tid; t < kn * 8; t += FA_DEC_THREADS) {
                 const char * src = vh + (int64_t) (k0 + (t >> 3)) * nbv1 + (t & 7) * 16;
                 asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(base + t * 16), "l"(src) : "memory");
@@ -386,14 +388,18 @@ k_flash_attn_decode(FaRows rows, int max_kv) {
             asm volatile("cp.async.commit_group;" ::: "memory");
         };
         fetch(0);
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        __syncthreads();
+        if (n_chunks > 1) fetch(1);
         float a = 0.0f, S = 0.0f;
         for (int c = 0; c < n_chunks; ++c) {
             const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
-            if (c + 1 < n_chunks) fetch(c + 1);
+            // chunk c has landed (at most the group of chunk c+1 may still be in flight); the barrier also says that
+            // everybody is done with chunk c-1, whose buffer chunk c+2 reuses
+            if (c + 1 < n_chunks) asm volatile("cp.async.wait_group 1;" ::: "memory");
+            else                  asm volatile("cp.async.wait_group 0;" ::: "memory");
+            __syncthreads();
+            if (c + 2 < n_chunks) fetch(c + 2);
             if (tid < 64) {
-                const __half * vb = Vs + (size_t) (c & 1) * FA_DEC_CHUNK * 64 + tid;
+                const __half * vb = Vs + (size_t) (c % FA_DEC_STAGES) * FA_DEC_CHUNK * 64 + tid;
                 int i = 0;
                 for (; i + 8 <= kn; i += 8) {
                     float vs[8], vv[8];
@@ -433,8 +439,6 @@ k_flash_attn_decode(FaRows rows, int max_kv) {
                 }
                 for (; i < kn; ++i) S = S_FMA ? __fmaf_rn(S, msv[k0 + i], sc[k0 + i]) : __fadd_rn(__fmul_rn(S, msv[k0 + i]), sc[k0 + i]);
             }
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
-            __syncthreads();
         }
         if (tid < 64) Qs[tid] = a;         // Qs is free now
         if (tid == 64) s_S = S;
@@ -444,7 +448,7 @@ k_flash_attn_decode(FaRows rows, int max_kv) {
 }
 
 static size_t fa_dec_smem(int max_kv) {
-    return (size_t) ((64 + 2 * max_kv + (max_kv + 31) / 32 + 3) & ~3) * sizeof(float) + 2 * FA_DEC_CHUNK * 64 * sizeof(__half);
+    return (size_t) ((64 + 2 * max_kv + (max_kv + 31) / 32 + 3) & ~3) * sizeof(float) + FA_DEC_STAGES * FA_DEC_CHUNK * 64 * sizeof(__half);
 }
 
 static bool g_fa_s_fma = true;

@@ -5,6 +5,7 @@
 // (ggml/src/ggml-cpu/ggml-cpu-quants.c:49-55, 3076-3100, 3869-3886).
 #include "b200_common.cuh"
 #include <string.h>
+#include <stdlib.h>
 #include <stdio.h>
 
 std::atomic<int64_t> g_b200_launches{0};
@@ -350,6 +351,209 @@ k_mul_mat_q(QPlanes w, int64_t M, int64_t nbk, const int8_t * __restrict__ xq, c
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// GEMM on the tensor pipe, still bit-exact.  The eight lane sums of a (weight row, column, 32-block) are exact
+// integers, so ANY summation order gives them; only the float chain acc_j = fma(d, q_j, acc_j) is order-bound.
+// An int8 MMA (m16n8k32) is made to deliver separate lane sums by zero-expanding the weight operand: MMA r of four
+// carries, for the eight weight rows of a group, lane 2r in A-rows 0..7 and lane 2r+1 in A-rows 8..15, each
+// non-zero only in the four K-slots that hold that lane's activations.  K-slots are permuted (low half slot s =
+// lane 2s, high half slot s = lane 2s+1), which makes the plain activation fragment one 8-byte shared load and the
+// weight fragment of thread (g, t) the quad {word 2t, 0, 0, word 2t+1} of row g in MMA r == t and zero otherwise.
+// The quads are laid out ready-made in shared memory (with one zero quad per row record), so a fragment is one
+// 16-byte load from an address chosen once per thread.  After the four MMAs thread (g, t) holds all eight lane sums
+// of outputs (row g, columns 2t and 2t+1) as register pairs: the block scale d_w*d_x is formed once per output pair
+// and the chain runs on packed f32x2 operations.  The accumulator input of the MMA is the magic integer, so its
+// result is already the bit pattern of 12582912 + q.
+// Warp tile: 8G rows x 8T columns; CTA: 4 x 2 warps.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma_lane_sums(f32x2 & q01, f32x2 & q23, const uint4 & a, const uint2 & b, const int4 & c) {
+    asm("{\n\t.reg .b32 d0, d1, d2, d3;\n\t"
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {d0, d1, d2, d3}, {%2, %3, %4, %5}, {%6, %7}, {%8, %9, %10, %11};\n\t"
+        "mov.b64 %0, {d0, d1};\n\t"
+        "mov.b64 %1, {d2, d3};\n\t}"
+        : "=l"(q01), "=l"(q23) : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b.x), "r"(b.y), "r"(c.x), "r"(c.y), "r"(c.z), "r"(c.w));
+}
+
+template <int TYPE, int G, int T>
+__global__ void __launch_bounds__(256, (G * T <= 4) ? 2 : 1)
+k_mul_mat_q_mma(QPlanes w, int64_t M, int64_t nbk, const int8_t * __restrict__ xq, const float * __restrict__ xd,
+                int64_t N, void * __restrict__ dst, int64_t ldd, GemmEp ep) {
+    constexpr int WM = 4, WN = 2, KC = 4;
+    constexpr int BM = WM * 8 * G, BN = WN * 8 * T;
+    constexpr int WREC = 80;                                        // bytes per (row, block): four fragment quads + a zero quad
+    static_assert(BM * KC <= 256 && BN * KC <= 256, "one staged item per thread");
+    constexpr int OFF_X = KC * BM * WREC, OFF_DW = OFF_X + KC * BN * 32, OFF_DX = OFF_DW + KC * BM * 8, OFF_MAGIC = OFF_DX + KC * BN * 4;
+    constexpr int STAGE_BYTES = OFF_MAGIC + 16;
+    constexpr int CS_BYTES = BN * (BM + 1) * 4;
+    __shared__ __align__(16) unsigned char smem_raw[STAGE_BYTES > CS_BYTES ? STAGE_BYTES : CS_BYTES];
+    unsigned char * Wq = smem_raw;                                  // [KC][BM][WREC]
+    int    (*Xs)[BN][8] = (int (*)[BN][8]) (smem_raw + OFF_X);
+    float2 (*dWs)[BM]   = (float2 (*)[BM]) (smem_raw + OFF_DW);     // (d, d)
+    float  (*dXs)[BN]   = (float (*)[BN]) (smem_raw + OFF_DX);
+    float  (*Cs)[BM + 1] = (float (*)[BM + 1]) smem_raw;           // after the main loop
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int wm = warp & 3, wn = warp >> 2;
+    const int64_t m0 = (int64_t) blockIdx.x * BM;
+    const int64_t n0 = (int64_t) blockIdx.y * BN;
+
+    f32x2 acc[G][T][8];                // [row group][column tile][lane] = (column 2t, column 2t + 1) of row g
+#pragma unroll
+    for (int gi = 0; gi < G; ++gi)
+#pragma unroll
+        for (int ti = 0; ti < T; ++ti)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[gi][ti][j] = 0ull;
+
+    // staging: thread i fetches (row i % BM, block i / BM) of W and (column i % BN, block i / BN) of X
+    const int wrow = tid % BM, wkb = tid / BM;
+    const int xcol = tid % BN, xkb = tid / BN;
+    const bool has_w = tid < BM * KC, has_x = tid < BN * KC;
+    if (has_w) *(uint4 *) (Wq + (wkb * BM + wrow) * WREC + 64) = make_uint4(0, 0, 0, 0);       // the record's zero quad, written once
+    if (tid == 0) *(int4 *) (smem_raw + OFF_MAGIC) = make_int4(MAGIC_I, MAGIC_I, MAGIC_I, MAGIC_I);
+    uint4 wa = make_uint4(0, 0, 0, 0), wb = wa, xa = wa, xb = wa;
+    uint32_t wqh = 0;
+    float wd = 0.0f, xdv = 0.0f;
+    auto fetch = [&](int64_t kb0) {
+        wa = make_uint4(0, 0, 0, 0); wb = wa; xa = wa; xb = wa; wqh = 0; wd = 0.0f; xdv = 0.0f;
+        if (has_w) {
+            const int64_t m = m0 + wrow, ib = kb0 + wkb;
+            if (m < M && ib < nbk) {
+                const int64_t blk = m * nbk + ib;
+                if (TYPE == B200_TYPE_Q5_0) { wa = ((const uint4 *) w.qs)[blk]; wqh = w.qh[blk]; }
+                else { wa = ((const uint4 *) w.qs)[blk * 2]; wb = ((const uint4 *) w.qs)[blk * 2 + 1]; }
+                wd = __half2float(w.d[blk]);
+            }
+        }
+        if (has_x) {
+            const int64_t n = n0 + xcol, ib = kb0 + xkb;
+            if (n < N && ib < nbk) {
+                const uint4 * p = (const uint4 *) (xq + (n * nbk + ib) * 32);
+                xa = p[0]; xb = p[1];
+                xdv = xd[n * nbk + ib];
+            }
+        }
+    };
+    fetch(0);
+
+    // per-thread byte offsets inside a row record: the thread's own quad for MMA r == t, the zero quad otherwise
+    int aoff[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) aoff[r] = (t == r) ? t * 16 : 64;
+    const unsigned char * wq_thr = Wq + (wm * (8 * G) + g) * WREC;
+    const f32x2 neg_magic = pack2(-MAGIC_F, -MAGIC_F);
+    int4 magic = make_int4(0, 0, 0, 0);
+
+    for (int64_t kb0 = 0; kb0 < nbk; kb0 += KC) {
+        if (has_w) {
+            int wv[8];
+            if (TYPE == B200_TYPE_Q5_0) {
+                const uint32_t qw[4] = {wa.x, wa.y, wa.z, wa.w};
+#pragma unroll
+                for (int u = 0; u < 8; ++u) wv[u] = q5_lane_word(qw[u & 3], wqh, u);
+            } else {
+                wv[0] = wa.x; wv[1] = wa.y; wv[2] = wa.z; wv[3] = wa.w;
+                wv[4] = wb.x; wv[5] = wb.y; wv[6] = wb.z; wv[7] = wb.w;
+            }
+            unsigned char * rec = Wq + (wkb * BM + wrow) * WREC;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) *(int4 *) (rec + u * 16) = make_int4(wv[2 * u], 0, 0, wv[2 * u + 1]);
+            dWs[wkb][wrow] = make_float2(wd, wd);
+        }
+        if (has_x) {
+            *(uint4 *) &Xs[xkb][xcol][0] = xa;
+            *(uint4 *) &Xs[xkb][xcol][4] = xb;
+            dXs[xkb][xcol] = xdv;
+        }
+        __syncthreads();
+        if (kb0 == 0)       // the four accumulator inputs come from memory so that they stay in four registers
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(magic.x), "=r"(magic.y), "=r"(magic.z), "=r"(magic.w)
+                         : "r"((unsigned) __cvta_generic_to_shared(smem_raw + OFF_MAGIC)));
+        if (kb0 + KC < nbk) fetch(kb0 + KC);
+
+#pragma unroll 1
+        for (int kb = 0; kb < KC; ++kb) {
+#pragma unroll
+            for (int gi = 0; gi < G; ++gi) {
+                const int row = wm * (8 * G) + gi * 8 + g;
+                const unsigned char * rec = wq_thr + (kb * BM + gi * 8) * WREC;
+                uint4 a[4];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) a[r] = *(const uint4 *) (rec + aoff[r]);
+                const f32x2 dwp = *(const f32x2 *) &dWs[kb][row];
+#pragma unroll
+                for (int ti = 0; ti < T; ++ti) {
+                    const int col = wn * (8 * T) + ti * 8;
+                    const uint2 xv = *(const uint2 *) &Xs[kb][col + g][2 * t];
+                    const f32x2 dxp = *(const f32x2 *) &dXs[kb][col + 2 * t];
+                    const f32x2 d = mul2(dwp, dxp);
+                    f32x2 q[8];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) mma_lane_sums(q[2 * r], q[2 * r + 1], a[r], xv, magic);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[gi][ti][j] = fma2(d, add2(q[j], neg_magic), acc[gi][ti][j]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+
+    // hsum_float_8: (l0+l4, l1+l5, l2+l6, l3+l7) -> (+2) -> (+1), both columns at once
+#pragma unroll
+    for (int gi = 0; gi < G; ++gi)
+#pragma unroll
+        for (int ti = 0; ti < T; ++ti) {
+            const f32x2 * a = acc[gi][ti];
+            const f32x2 r0 = add2(a[4], a[0]), r1 = add2(a[5], a[1]);
+            const f32x2 r2 = add2(a[6], a[2]), r3 = add2(a[7], a[3]);
+            const f32x2 s  = add2(add2(r0, r2), add2(r1, r3));
+            float lo, hi;
+            unpack2(s, lo, hi);
+            const int row = wm * (8 * G) + gi * 8 + g, col = wn * (8 * T) + ti * 8 + 2 * t;
+            Cs[col][row]     = lo;
+            Cs[col + 1][row] = hi;
+        }
+    __syncthreads();
+    {   // epilogue with full-row global accesses
+        const int ml = tid % BM;
+        const int64_t m = m0 + ml;
+        if (m < M) {
+#pragma unroll 4
+            for (int nl = tid / BM; nl < BN; nl += 256 / BM) {
+                const int64_t n = n0 + nl;
+                if (n < N) {
+                    const float v = gemm_ep_apply(ep, n, m, Cs[nl][ml]);
+                    if (ep.store_f16) ((__half *) dst)[n * ldd + m] = __float2half_rn(v);
+                    else              ((float *) dst)[n * ldd + m] = v;
+                }
+            }
+        }
+    }
+}
+
+// 0: dp4a kernel, 1: MMA 64 x 64 tile, 2: MMA 32 x 64 tile (B200_GEMM_VARIANT, read once)
+static int gemm_variant() {
+    static const int v = getenv("B200_GEMM_VARIANT") ? atoi(getenv("B200_GEMM_VARIANT")) : 1;
+    return v;
+}
+
+template <int TYPE>
+static void launch_gemm(const QPlanes & w, int64_t M, int64_t nbk, const int8_t * xq, const float * xd, int64_t N,
+                        void * dst, int64_t ldd, const GemmEp & e, cudaStream_t st) {
+    const int v = gemm_variant();
+    if (v == 1) {
+        dim3 grid((unsigned) ((M + 63) / 64), (unsigned) ((N + 63) / 64));
+        k_mul_mat_q_mma<TYPE, 2, 4><<<grid, 256, 0, st>>>(w, M, nbk, xq, xd, N, dst, ldd, e);
+    } else if (v == 2) {
+        dim3 grid((unsigned) ((M + 31) / 32), (unsigned) ((N + 63) / 64));
+        k_mul_mat_q_mma<TYPE, 1, 4><<<grid, 256, 0, st>>>(w, M, nbk, xq, xd, N, dst, ldd, e);
+    } else {
+        dim3 grid((unsigned) ((M + 31) / 32), (unsigned) ((N + 31) / 32));
+        k_mul_mat_q<TYPE><<<grid, 256, 0, st>>>(w, M, nbk, xq, xd, N, dst, ldd, e);
+    }
+}
+
 const uint16_t * b200_gelu_table_device(int * err);
 
 extern "C" int b200_mul_mat_q_ep(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
@@ -373,14 +577,10 @@ extern "C" int b200_mul_mat_q_ep(int wtype, const void * w_planes, int64_t nb_to
             } else if (e.kind[s] != B200_EP_SCALE) return B200_ERR_ARG;
         }
     }
-    dim3 grid((unsigned) ((M + 31) / 32), (unsigned) ((N + 31) / 32));
     const QPlanes w = q_planes(wtype, w_planes, nb_total);
-    if (wtype == B200_TYPE_Q5_0)
-        k_mul_mat_q<B200_TYPE_Q5_0><<<grid, 256, 0, as_stream(stream)>>>(w, M, nbk, xq, xd, N, dst, dst_stride, e);
-    else if (wtype == B200_TYPE_Q8_0)
-        k_mul_mat_q<B200_TYPE_Q8_0><<<grid, 256, 0, as_stream(stream)>>>(w, M, nbk, xq, xd, N, dst, dst_stride, e);
-    else
-        return B200_ERR_ARG;
+    if (wtype == B200_TYPE_Q5_0)      launch_gemm<B200_TYPE_Q5_0>(w, M, nbk, xq, xd, N, dst, dst_stride, e, as_stream(stream));
+    else if (wtype == B200_TYPE_Q8_0) launch_gemm<B200_TYPE_Q8_0>(w, M, nbk, xq, xd, N, dst, dst_stride, e, as_stream(stream));
+    else return B200_ERR_ARG;
     B200_RETURN_LAST();
 }
 

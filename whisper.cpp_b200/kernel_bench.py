@@ -122,6 +122,15 @@ def main():
         assert K.b200_quantize_q8_0(ptr(x), i64(N), i64(Kd), i64(Kd * 4), ptr(xq), ptr(xd), None) == 0
         t = timeit(lambda: K.b200_mul_mat_q(6, ptr(p), i64(nb), i64(M), i64(Kd), ptr(xq), ptr(xd), i64(N), ptr(out), i64(M), None), 10)
         print(f"  mul_mat_q {name:6s}: {t:8.1f} us   {2 * M * N * Kd / t / 1e6:7.2f} TFLOP/s")
+        wh, wd = torch.empty((nb, 16), dtype=torch.int32, device="cuda"), torch.empty(nb, device="cuda")
+        xh, xdh = torch.empty((N * Kd // 32, 16), dtype=torch.int32, device="cuda"), torch.empty(N * Kd // 32, device="cuda")
+        xf = torch.randn((N, Kd), device="cuda")
+        assert K.b200_mma_pack_weights(6, ptr(p), i64(nb), ptr(wh), ptr(wd), None) == 0
+        assert K.b200_mma_quantize(ptr(xf), i64(N), i64(Kd), i64(Kd * 4), ptr(xh), ptr(xdh), None) == 0
+        t = timeit(lambda: K.b200_mul_mat_mma_ep(ptr(wh), ptr(wd), i64(M), i64(Kd), ptr(xh), ptr(xdh), i64(N), ptr(out), i64(M), None, None), 10)
+        print(f"  mul_mat_mma {name:6s}: {t:6.1f} us   {2 * M * N * Kd / t / 1e6:7.2f} TFLOP/s")
+        t = timeit(lambda: K.b200_mma_quantize(ptr(xf), i64(N), i64(Kd), i64(Kd * 4), ptr(xh), ptr(xdh), None), 10)
+        print(f"  mma_quantize {name:6s}: {t:5.1f} us")
         print(f"  quantize_q8_0 [{N} x {Kd}]: {timeit(lambda: K.b200_quantize_q8_0(ptr(x), i64(N), i64(Kd), i64(Kd * 4), ptr(xq), ptr(xd), None), 10):.1f} us")
     n_q, n_kv = 1500, 1536
     q = torch.randn((n_q, H * 64), device="cuda")
