@@ -37,6 +37,15 @@ N_NEW = 224
 CLIP_SECONDS = 30.0
 TOTAL_CLIPS = 64
 
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one representative launch of each kernel class, from the
+# ncu captures summarised under profiles/ (small cases of the same kernels; traffic grows with the bytes streamed).
+TRAFFIC_NCU = {
+    "mul_mat_vec_q":     {"bytes": 1.19e6,  "launch": "1280 x 1280 Q5_0 weights x 32 columns (algorithmic 1.34e6: columns and output stay in L2)"},
+    "flash_attn_decode": {"bytes": 251.9e6, "launch": "32 rows x 20 heads x 1536 keys (algorithmic 251.7e6)"},
+    "flash_attn_ext":    {"bytes": 15.6e6,  "launch": "1500 x 1536 keys x 20 heads (Q + K/V once; K/V re-reads hit L2)"},
+    "mul_mat_q":         {"bytes": 3.3e6,   "launch": "1280 x 1280 Q5_0 x 1500 columns, dp4a kernel (weights + int8 activations once)"},
+}
+
 
 def peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
@@ -187,7 +196,9 @@ def main():
         torch.cuda.synchronize()
 
     cores = len(os.sched_getaffinity(0))
-    n_states = args.states or min(32, max(1, args.clips // world))      # decode steps of concurrent states are merged in the plugin
+    # one whisper_state per clip, at most 64: their decode steps are merged by the plugin in groups of up to 16 states, and
+    # several groups in flight keep the device busy while the host threads of the others build their next step
+    n_states = args.states or min(64, max(1, args.clips // world))
     path = model_file(pkg, args.arch, args.wtype, rank, barrier)
     clips_rank = args.clips // world
     pcm = make_pcm(pkg, clips_rank, 1000 + rank * clips_rank)
@@ -256,33 +267,50 @@ def main():
     h2d_step = h2d / args.steps + clips_rank * mel_h2d
     d2h_step = d2h / args.steps + clips_rank * mel_d2h
 
-    # roofline of the dominant kernel: one extra pass of a few clips with per-operator CUDA events
+    # Roofline of the dominant kernel: per-operator CUDA events on the backend's own streams (b200_timing_*), two extra
+    # passes inside this run.  Encoder-side classes are timed with ONE state on two clips (concurrent states would run
+    # their kernels side by side and inflate each other's event times); decode-side classes are timed with all states
+    # stepping together, as in the timed region.  Times are reported per clip.
     roof = None
-    tt = {}
+    per_clip = {}
     if rank == 0:
         en = C.CFUNCTYPE(None, C.c_int)(lib.drv_backend_proc(b"B200", b"b200_timing_enable"))
         rs = C.CFUNCTYPE(None)(lib.drv_backend_proc(b"B200", b"b200_timing_reset"))
-        one = pkg.Whisper.__new__(pkg.Whisper)  # reuse the context with a single state for a serial pass
+        one = pkg.Whisper.__new__(pkg.Whisper)  # the same context with a single state
         one.__dict__.update(w.__dict__)
         one.states = w.states[:1]
-        rs()
-        en(1)
-        one.greedy_batch(N_NEW, mels=mels[:2])
+        n_serial = min(2, clips_rank)
+        rs(); en(1)
+        one.greedy_batch(min(N_NEW, 4), mels=mels[:n_serial])
         en(0)
-        tt = timing_table(lib)
+        t_serial = timing_table(lib)
+        n_batched = min(n_states, clips_rank)
+        rs(); en(1)
+        w.greedy_batch(N_NEW, mels=mels[:n_batched])
+        en(0)
+        t_batched = timing_table(lib)
+        decode_side = ("mul_mat_vec_q", "flash_attn_decode", "norm", "get_rows")
+        for k, v in t_batched.items():
+            if k in decode_side:
+                per_clip[k] = {"launch_groups": v["launch_groups"] / n_batched, "ms": v["ms"] / n_batched, "work": v["work"] / n_batched,
+                               "timed": f"{n_batched} states stepping together"}
+        for k, v in t_serial.items():
+            if k not in decode_side:
+                per_clip[k] = {"launch_groups": v["launch_groups"] / n_serial, "ms": v["ms"] / n_serial, "work": v["work"] / n_serial,
+                               "timed": "one state"}
         hbm, tf, which = peaks()
-        top = max(tt.items(), key=lambda kv: kv[1]["ms"])[0] if tt else None
+        top = max(per_clip.items(), key=lambda kv: kv[1]["ms"])[0] if per_clip else None
         if top:
-            r = tt[top]
+            r = per_clip[top]
             per_launch_work = r["work"] / r["launch_groups"]
             per_launch_s = r["ms"] / 1000.0 / r["launch_groups"]
             if top in ("mul_mat_q", "mul_mat_f16", "flash_attn_ext"):
                 ach, peak, unit, bound = per_launch_work / per_launch_s / 1e12, tf, "TFLOP/s", "tensor"
             else:
                 ach, peak, unit, bound = per_launch_work / per_launch_s / 1e9, hbm, "GB/s", "hbm"
-            roof = {"kernel": top, "bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak, "traffic": None,
-                    "peak_source": which, "launches": r["launch_groups"], "avg_us": per_launch_s * 1e6,
-                    "share_of_gpu_time": r["ms"] / sum(v["ms"] for v in tt.values())}
+            roof = {"kernel": top, "bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
+                    "traffic": TRAFFIC_NCU.get(top), "peak_source": which, "avg_us": per_launch_s * 1e6,
+                    "share_of_gpu_time": r["ms"] / sum(v["ms"] for v in per_clip.values()), "timed": r["timed"]}
 
     cpu_base = None
     if rank == 0 and not args.no_cpu_baseline:
@@ -307,7 +335,8 @@ def main():
             "e2e": {"value": e2e, "unit": "audio-s/s", "h2d_bytes_per_step": int(h2d_step), "d2h_bytes_per_step": int(d2h_step),
                     "ms_per_step": 1000.0 * sec_e / args.steps},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu_base,
-            "kernel_classes": {k: {"launch_groups": v["launch_groups"], "ms": round(v["ms"], 3)} for k, v in tt.items()},
+            "kernel_classes_per_clip": {k: {"launch_groups": round(v["launch_groups"], 1), "ms": round(v["ms"], 3), "timed": v["timed"]}
+                                        for k, v in sorted(per_clip.items(), key=lambda kv: -kv[1]["ms"])},
         }))
     if world > 1:
         dist.destroy_process_group()

@@ -173,6 +173,10 @@ int b200_flash_attn_ext(const float * q, int64_t nbq1, int64_t nbq2,
 typedef struct { const float * q; const void * k; const void * v; const void * mask; float * dst; int64_t n_kv; } b200_fa_row;
 int b200_flash_attn_decode_rows(const b200_fa_row * rows, int n_rows, int64_t n_head, int64_t nbq2, int64_t nbk1, int64_t nbk2,
                                 int64_t nbv1, int64_t nbv2, float scale, void * stream);
+/* The same, and additionally every output row quantised as b200_quantize_cols would do it afterwards (row i ->
+ * xq[i][n_head*64], xd[i][n_head*2]): saves the separate quantisation launch before the output projection. */
+int b200_flash_attn_decode_rows_q(const b200_fa_row * rows, int n_rows, int64_t n_head, int64_t nbq2, int64_t nbk1, int64_t nbk2,
+                                  int64_t nbv1, int64_t nbv2, float scale, int8_t * xq, float * xd, void * stream);
 
 /* ggml_compute_forward_norm_f32 (ops.cpp:3109-3158): rows of ne00 f32, row strides in bytes. */
 int b200_norm(const float * x, float * y, int64_t ne00, int64_t ne01, int64_t ne02, int64_t ne03,
@@ -181,6 +185,11 @@ int b200_norm(const float * x, float * y, int64_t ne00, int64_t ne01, int64_t ne
 /* b200_layer_norm for rows that live at unrelated addresses (at most 64; rows of several decoder states). */
 typedef struct { const float * x; float * y; } b200_ln_row;
 int b200_layer_norm_rows(const b200_ln_row * rows, int n_rows, const float * gamma, const float * beta, int64_t ne00, float eps, void * stream);
+/* The same, and additionally every output row quantised as b200_quantize_cols would do it afterwards (row i ->
+ * xq[i][ne00], xd[i][ne00/32]; ne00 a multiple of 32): saves the separate quantisation launch before the products that
+ * consume the rows.  No counterpart in the reference beyond quantize_row_q8_0 itself. */
+int b200_layer_norm_rows_q(const b200_ln_row * rows, int n_rows, const float * gamma, const float * beta, int64_t ne00, float eps,
+                           int8_t * xq, float * xd, void * stream);
 
 /* ADD (op 0) / MUL (op 1) with ggml broadcasting of src1 (ggml/src/ggml-cpu/binary-ops.cpp:50-137). */
 int b200_binary(int op, const float * a, const int64_t * nea, const int64_t * nba,

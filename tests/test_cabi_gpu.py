@@ -321,6 +321,16 @@ def test_decode_rows_attention_and_layer_norm_rows(K):
     sync_ok(K.b200_flash_attn_decode_rows(rows, 3, i64(H), i64(64 * 4), i64(d * 2), i64(128), i64(d * 2), i64(128), C.c_float(0.125), None))
     for i in range(3):
         assert bits_equal(keep[5 * i + 3].cpu().numpy(), want[i]), f"row {i}"
+    # the variant that also leaves the rows quantised (layout of b200_quantize_cols) for the projection that follows
+    xq, xd = torch.zeros((3, H * 64), dtype=torch.int8, device="cuda"), torch.zeros((3, H * 2), device="cuda")
+    for i in range(3):
+        keep[5 * i + 3].zero_()
+    sync_ok(K.b200_flash_attn_decode_rows_q(rows, 3, i64(H), i64(64 * 4), i64(d * 2), i64(128), i64(d * 2), i64(128), C.c_float(0.125),
+                                            ptr(xq), ptr(xd), None))
+    for i in range(3):
+        assert bits_equal(keep[5 * i + 3].cpu().numpy(), want[i]), f"row {i} (quantising variant)"
+    rq, rd = O.quantize_row_q8_0(np.stack([w_.reshape(-1) for w_ in want]))
+    assert np.array_equal(xq.cpu().numpy().reshape(-1), rq) and bits_equal(xd.cpu().numpy().reshape(-1), rd)
 
     class LnRow(C.Structure):
         _fields_ = [("x", vp), ("y", vp)]
@@ -333,3 +343,13 @@ def test_decode_rows_attention_and_layer_norm_rows(K):
         lr[i].x, lr[i].y = dx[i].data_ptr(), dy[4 - i].data_ptr()
     sync_ok(K.b200_layer_norm_rows(lr, 5, ptr(dg), ptr(db), i64(1280), C.c_float(1e-5), None))
     assert bits_equal(dy.cpu().numpy()[::-1], O.norm(x) * gamma + beta)
+    # the variant that also leaves the rows quantised (layout of b200_quantize_cols) for the product that follows
+    dy2 = torch.zeros((5, 1280), device="cuda")
+    for i in range(5):
+        lr[i].y = dy2[4 - i].data_ptr()
+    xq, xd = torch.zeros((5, 1280), dtype=torch.int8, device="cuda"), torch.zeros((5, 40), device="cuda")
+    sync_ok(K.b200_layer_norm_rows_q(lr, 5, ptr(dg), ptr(db), i64(1280), C.c_float(1e-5), ptr(xq), ptr(xd), None))
+    assert bits_equal(dy2.cpu().numpy(), dy.cpu().numpy())
+    rq, rd = O.quantize_row_q8_0(dy.cpu().numpy()[::-1].copy())       # row i of the launch wrote dy[4 - i]
+    assert np.array_equal(xq.cpu().numpy().reshape(-1), rq) and bits_equal(xd.cpu().numpy().reshape(-1), rd)
+    assert K.b200_layer_norm_rows_q(lr, 5, ptr(dg), ptr(db), i64(1290), C.c_float(1e-5), ptr(xq), ptr(xd), None) != 0

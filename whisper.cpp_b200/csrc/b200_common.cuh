@@ -4,6 +4,7 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 #include <atomic>
+#include <utility>
 #include "b200_whisper.h"
 
 extern std::atomic<int64_t> g_b200_launches;
@@ -12,6 +13,26 @@ extern std::atomic<int64_t> g_b200_launches;
 #define B200_RETURN_LAST() do { B200_LAUNCHED(); return (int) cudaGetLastError(); } while (0)
 
 static inline cudaStream_t as_stream(void * s) { return (cudaStream_t) s; }
+
+// Programmatic dependent launch for the chain of small kernels of a decode step.  A kernel launched through
+// launch_chained may start (block scheduling, its own prologue, loads of weights) while its predecessor in the
+// stream is still running; it calls chain_wait() before it touches anything the predecessor writes or reads, and
+// every such kernel calls chain_release() first thing so that its own successor may be scheduled early.  Both are
+// no-ops for a kernel launched the ordinary way.  B200_NO_PDL=1 turns the launch attribute off.
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void chain_wait()    { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+bool b200_chained_launches(void);
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = b200_chained_launches() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 // f32 -> f16 round-to-nearest-even -> f32, the F16C round trip of GGML_FP32_TO_FP16 / GGML_FP16_TO_FP32.
 // The packed conversion (cvt.rn.f16x2.f32) is used on purpose: the scalar f32->f16 conversion issues to the

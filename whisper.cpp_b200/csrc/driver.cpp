@@ -21,6 +21,8 @@
 #include <cstdio>
 #include <cstring>
 #include <thread>
+#include <condition_variable>
+#include <mutex>
 #include <vector>
 
 extern "C" {
@@ -126,10 +128,24 @@ static int argmax_f32(const float * x, int n) {
 // If force != NULL the fed-back token at step i is force[i] (teacher forcing) while out[i] still
 // reports this run's argmax.  margins (optional) receives top1-top2 of every step; logits_out
 // (optional) receives the raw logits of every step, n_vocab floats each.
+// Admission gate for encoders: at most `limit` states run whisper_encode at a time (0 = no limit), so that the rest of
+// the states keep decoding together while a few encoders fill the GPU, instead of all states encoding, then all decoding.
+struct enc_gate {
+    std::mutex mu;
+    std::condition_variable cv;
+    int limit = 0, busy = 0;
+    void enter() { if (limit <= 0) return; std::unique_lock<std::mutex> lk(mu); cv.wait(lk, [&] { return busy < limit; }); ++busy; }
+    void leave() { if (limit <= 0) return; { std::lock_guard<std::mutex> lk(mu); --busy; } cv.notify_one(); }
+};
+static enc_gate g_enc_gate;
+
 int drv_greedy(void * vctx, void * vst, int n_new, int threads, const int * force, int * out, float * margins, float * logits_out) {
     struct whisper_context * ctx = (struct whisper_context *) vctx;
     struct whisper_state *   st  = (struct whisper_state *) vst;
-    if (whisper_encode_with_state(ctx, st, 0, threads) != 0) return -1;
+    g_enc_gate.enter();
+    const int enc = whisper_encode_with_state(ctx, st, 0, threads);
+    g_enc_gate.leave();
+    if (enc != 0) return -1;
     int prefix[4];
     drv_prefix(ctx, prefix);
     const int n_vocab = whisper_n_vocab(ctx);
@@ -222,6 +238,7 @@ int drv_greedy_batch(void * vctx, void ** states, int n_states, void ** mel_plan
                      const float * mels, int n_len, int n_mel, int n_clips, int n_new, int threads, int * tokens_out, double * seconds) {
     struct whisper_context * ctx = (struct whisper_context *) vctx;
     std::atomic<int> next{0}, err{0};
+    g_enc_gate.limit = getenv("DRV_MAX_ENC") ? atoi(getenv("DRV_MAX_ENC")) : 0;
     const auto t0 = std::chrono::steady_clock::now();
     auto work = [&](int w) {
         struct whisper_state * st = (struct whisper_state *) states[w];

@@ -726,6 +726,7 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
     if (it.kind == PK_LAYER_NORM) {
         b200_ln_row rows[64];
         int n_rows = 0;
+        bool launched_rows = false;
         struct ggml_tensor * n0 = ggml_graph_node(gs[0], it.node);
         const float * gamma = (const float *) ggml_graph_node(gs[0], it.node + 1)->src[1]->data;
         const float * beta  = (const float *) ggml_graph_node(gs[0], it.last)->src[1]->data;
@@ -747,13 +748,28 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
                     const int e = b200_layer_norm_rows(rows, n_rows, gamma, beta, ne00, eps, st);
                     if (e) return e;
                     n_rows = 0;
+                    launched_rows = true;
                 }
                 rows[n_rows].x = (const float *) ((const char *) x->data + r * x->nb[1]);
                 rows[n_rows].y = (float *) ((char *) out->data + r * out->nb[1]);
                 ++n_rows;
             }
         }
-        return n_rows ? b200_layer_norm_rows(rows, n_rows, gamma, beta, ne00, eps, st) : 0;
+        if (!n_rows) return 0;
+        // Rows of several states go to a product next (5..32 columns: the quantised-column path): the same kernel also
+        // leaves them quantised in the column buffer, marked as written by this item so that the product reuses them.
+        static const bool fuse_q = getenv("GGML_B200_NO_FUSION") == nullptr;
+        if (fuse_q && !launched_rows && n_rows > 4 && n_rows <= 32 && ne00 % 32 == 0 && ne00 <= COLQ_MAX_K) {
+            int8_t * xq = (int8_t *) ctx->colq;
+            float *  xd = (float *) ((char *) ctx->colq + (size_t) 32 * COLQ_MAX_K);
+            const int e = b200_layer_norm_rows_q(rows, n_rows, gamma, beta, ne00, eps, xq, xd, st);
+            ctx->colq_ptrs.resize(n_rows);
+            for (int i = 0; i < n_rows; ++i) ctx->colq_ptrs[i] = rows[i].y;
+            ctx->colq_K = ne00;
+            ctx->colq_seq = ctx->item_seq;
+            return e;
+        }
+        return b200_layer_norm_rows(rows, n_rows, gamma, beta, ne00, eps, st);
     }
     if (it.kind == PK_GEMV) {
         struct ggml_tensor * n0 = ggml_graph_node(gs[0], it.node);
@@ -868,10 +884,29 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
         memcpy(&scale, (const float *) n0->op_params + 0, sizeof(float));
         b200_fa_row rows[32];
         int n_rows = 0;
+        static const bool fuse_q = getenv("GGML_B200_NO_FUSION") == nullptr;
+        int n_launches = 0;
+        bool last = false;
         auto flush = [&]() -> int {
             if (!n_rows) return 0;
-            const int e = b200_flash_attn_decode_rows(rows, n_rows, q0->ne[2], (int64_t) q0->nb[2], (int64_t) k0->nb[1], (int64_t) k0->nb[2],
-                                                      (int64_t) v0->nb[1], (int64_t) v0->nb[2], scale, st);
+            int e;
+            // A single launch that covers all rows, followed by the output projection (5..32 columns: the quantised-column
+            // path): the kernel also leaves the rows quantised in the column buffer, marked as written by this item.
+            const int64_t kk = q0->ne[2] * 64;
+            if (fuse_q && last && n_launches == 0 && n_rows > 4 && kk <= COLQ_MAX_K && q0->ne[0] == 64) {
+                int8_t * xq = (int8_t *) ctx->colq;
+                float *  xd = (float *) ((char *) ctx->colq + (size_t) 32 * COLQ_MAX_K);
+                e = b200_flash_attn_decode_rows_q(rows, n_rows, q0->ne[2], (int64_t) q0->nb[2], (int64_t) k0->nb[1], (int64_t) k0->nb[2],
+                                                  (int64_t) v0->nb[1], (int64_t) v0->nb[2], scale, xq, xd, st);
+                ctx->colq_ptrs.resize(n_rows);
+                for (int i = 0; i < n_rows; ++i) ctx->colq_ptrs[i] = rows[i].dst;
+                ctx->colq_K = kk;
+                ctx->colq_seq = ctx->item_seq;
+            } else {
+                e = b200_flash_attn_decode_rows(rows, n_rows, q0->ne[2], (int64_t) q0->nb[2], (int64_t) k0->nb[1], (int64_t) k0->nb[2],
+                                                (int64_t) v0->nb[1], (int64_t) v0->nb[2], scale, st);
+            }
+            ++n_launches;
             n_rows = 0;
             return e;
         };
@@ -889,6 +924,7 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
                 if (e) return e;
                 e = compute_node(ctx, fa);
                 if (e) return e;
+                ++n_launches;
                 continue;
             }
             for (int64_t r = 0; r < q->ne[1]; ++r) {
@@ -902,8 +938,13 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
                 ++n_rows;
             }
         }
+        last = true;
         return flush();
     }
+}
+
+static bool is_noop(enum ggml_op op) {
+    return op == GGML_OP_NONE || op == GGML_OP_RESHAPE || op == GGML_OP_VIEW || op == GGML_OP_PERMUTE || op == GGML_OP_TRANSPOSE;
 }
 
 static int run_plan(b200_backend_ctx * ctx, const exec_plan & plan, struct ggml_cgraph * const * gs, int n_g, bool timing,
@@ -914,7 +955,8 @@ static int run_plan(b200_backend_ctx * ctx, const exec_plan & plan, struct ggml_
     };
     ctx->colq_seq = -2;                      // activations of an earlier graph never carry over
     for (const plan_item & it : plan.items) {
-        ctx->item_seq++;
+        // views do nothing and do not separate a producer of quantised columns from the product that reuses them
+        if (!(it.kind == PK_NODE && is_noop(ggml_graph_node(gs[0], it.node)->op))) ctx->item_seq++;
         if (timing) {
             double work = 0;
             struct ggml_tensor * node = ggml_graph_node(gs[0], it.node);
@@ -1014,6 +1056,7 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
     static const bool fuse     = getenv("GGML_B200_NO_FUSION") == nullptr;
     static const bool batching = getenv("GGML_B200_NO_BATCHING") == nullptr;
     static const int  window_us = getenv("GGML_B200_BATCH_WINDOW_US") ? atoi(getenv("GGML_B200_BATCH_WINDOW_US")) : 300;
+    static const int  max_group = getenv("GGML_B200_MAX_GROUP") && atoi(getenv("GGML_B200_MAX_GROUP")) > 0 ? atoi(getenv("GGML_B200_MAX_GROUP")) : 16;
     const bool timing = g_timing_on.load() != 0;
     device_batcher & B = g_batchers[ctx->device];
 
@@ -1071,6 +1114,7 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
             int expected = 0;
             const int64_t now = now_ns();
             for (b200_backend_ctx * c : B.members) if (now - c->last_decode_ns < 20 * 1000 * 1000) ++expected;
+            if (expected > max_group) expected = max_group;     // larger populations run as several groups whose steps overlap on the device
             // States that were served by an earlier batch come back one turn later.  Waiting for them merges the groups:
             // while they are away the device is busy with their step anyway, so the wait costs nothing when the device
             // is the bottleneck, and one merged group needs one pass over the weights instead of one per group.
@@ -1086,7 +1130,7 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
             g_ns_lead_wait += now_ns() - t_w0;
             const int64_t t_p0 = now_ns();
             std::vector<batch_req *> mine;
-            mine.swap(B.pending);
+            mine.swap(B.pending);                                 // everything that is waiting now (may exceed max_group by a few)
             B.leader_active = false;                              // later arrivals elect their own leader
             cudaEvent_t ev = nullptr;
             if (B.events.size() < 64) { cudaEvent_t e; cudaEventCreateWithFlags(&e, cudaEventDisableTiming); B.events.push_back(e); }

@@ -258,7 +258,7 @@ struct FaRows {
 
 template <bool S_FMA>
 __global__ void __launch_bounds__(FA_DEC_THREADS)
-k_flash_attn_decode(FaRows rows, int max_kv) {
+k_flash_attn_decode(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * __restrict__ xd) {
     extern __shared__ __align__(16) float fa_smem[];
     // heads of one query row are neighbours in launch order: they walk the same K/V rows (d_model wide, 128 bytes per
     // head) at about the same time, which keeps the DRAM pages they share open
@@ -275,6 +275,7 @@ k_flash_attn_decode(FaRows rows, int max_kv) {
     const int64_t h = blockIdx.x;
     const int64_t nbk1 = rows.nbk1, nbv1 = rows.nbv1;
     const float scale = rows.scale;
+    chain_wait();                          // Q, and for self-attention the newest K/V rows, come from the kernels before this one
 
     if (tid < 64) Qs[tid] = round_f16(*(const float *) (R.q + h * rows.nbq2 + tid * 4));
     for (int g = tid; g < (n_kv + 7) / 8; g += FA_DEC_THREADS) evt[g] = 0;
@@ -444,7 +445,21 @@ k_flash_attn_decode(FaRows rows, int max_kv) {
         if (tid == 64) s_S = S;
     }
     __syncthreads();
-    if (tid < 64) R.dst[h * 64 + tid] = __fmul_rn(Qs[tid], __fdiv_rn(1.0f, s_S));
+    if (tid < 64) {
+        const float o = __fmul_rn(Qs[tid], __fdiv_rn(1.0f, s_S));
+        R.dst[h * 64 + tid] = o;
+        // optional second output: this head's two 32-blocks of the row quantised as quantize_row_q8_0 does it, in the
+        // layout of b200_quantize_cols (row = blockIdx.y), for the projection that consumes the row next
+        if (xq != nullptr) {
+            float amax = fabsf(o);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+            const float id = (amax != 0.0f) ? __fdiv_rn(127.f, amax) : 0.0f;
+            const size_t kk = (size_t) gridDim.x * 64;
+            xq[blockIdx.y * kk + h * 64 + tid] = (int8_t) __float2int_rn(__fmul_rn(o, id));
+            if ((tid & 31) == 0) xd[blockIdx.y * (kk >> 5) + h * 2 + (tid >> 5)] = round_f16(__fdiv_rn(amax, 127.f));
+        }
+    }
 }
 
 static size_t fa_dec_smem(int max_kv) {
@@ -453,7 +468,7 @@ static size_t fa_dec_smem(int max_kv) {
 
 static bool g_fa_s_fma = true;
 
-static int launch_fa_decode(const FaRows & rows, int n_rows, int64_t n_head, cudaStream_t st) {
+static int launch_fa_decode(const FaRows & rows, int n_rows, int64_t n_head, int8_t * xq, float * xd, cudaStream_t st) {
     int max_kv = 1;
     for (int i = 0; i < n_rows; ++i) max_kv = max(max_kv, rows.r[i].n_kv);
     max_kv = (max_kv + 7) & ~7;
@@ -466,13 +481,13 @@ static int launch_fa_decode(const FaRows & rows, int n_rows, int64_t n_head, cud
         attr_done[dev] = true;
     }
     dim3 grid((unsigned) n_head, (unsigned) n_rows);
-    if (g_fa_s_fma) k_flash_attn_decode<true><<<grid, FA_DEC_THREADS, fa_dec_smem(max_kv), st>>>(rows, max_kv);
-    else            k_flash_attn_decode<false><<<grid, FA_DEC_THREADS, fa_dec_smem(max_kv), st>>>(rows, max_kv);
+    if (g_fa_s_fma) launch_chained(k_flash_attn_decode<true>, grid, dim3(FA_DEC_THREADS), fa_dec_smem(max_kv), st, rows, max_kv, xq, xd);
+    else            launch_chained(k_flash_attn_decode<false>, grid, dim3(FA_DEC_THREADS), fa_dec_smem(max_kv), st, rows, max_kv, xq, xd);
     B200_RETURN_LAST();
 }
 
-extern "C" int b200_flash_attn_decode_rows(const b200_fa_row * rows, int n_rows, int64_t n_head, int64_t nbq2, int64_t nbk1, int64_t nbk2,
-                                           int64_t nbv1, int64_t nbv2, float scale, void * stream) {
+extern "C" int b200_flash_attn_decode_rows_q(const b200_fa_row * rows, int n_rows, int64_t n_head, int64_t nbq2, int64_t nbk1, int64_t nbk2,
+                                             int64_t nbv1, int64_t nbv2, float scale, int8_t * xq, float * xd, void * stream) {
     if (n_rows <= 0) return 0;
     if (n_rows > FA_DEC_MAX_ROWS || n_head <= 0 || n_head > 65535) return B200_ERR_ARG;
     if ((nbk1 & 15) || (nbk2 & 15) || (nbv1 & 15) || (nbv2 & 15) || (nbq2 & 3)) return B200_ERR_ARG;
@@ -486,7 +501,12 @@ extern "C" int b200_flash_attn_decode_rows(const b200_fa_row * rows, int n_rows,
         r.r[i].q = (const char *) rows[i].q; r.r[i].k = (const char *) rows[i].k; r.r[i].v = (const char *) rows[i].v;
         r.r[i].mask = (const char *) rows[i].mask; r.r[i].dst = rows[i].dst; r.r[i].n_kv = (int) rows[i].n_kv;
     }
-    return launch_fa_decode(r, n_rows, n_head, as_stream(stream));
+    return launch_fa_decode(r, n_rows, n_head, xq, xd, as_stream(stream));
+}
+
+extern "C" int b200_flash_attn_decode_rows(const b200_fa_row * rows, int n_rows, int64_t n_head, int64_t nbq2, int64_t nbk1, int64_t nbk2,
+                                           int64_t nbv1, int64_t nbv2, float scale, void * stream) {
+    return b200_flash_attn_decode_rows_q(rows, n_rows, n_head, nbq2, nbk1, nbk2, nbv1, nbv2, scale, nullptr, nullptr, stream);
 }
 
 // The host compiler of the reference contracts "S*ms + vs" into one FMA (GNU mode, -mfma).
@@ -511,7 +531,7 @@ extern "C" int b200_flash_attn_ext(const float * q, int64_t nbq1, int64_t nbq2,
             r.r[i].mask = mask ? (const char *) mask + i * nbm1 : nullptr;
             r.r[i].dst = dst + (int64_t) i * n_head * 64; r.r[i].n_kv = (int) n_kv;
         }
-        return launch_fa_decode(r, (int) n_q, n_head, as_stream(stream));
+        return launch_fa_decode(r, (int) n_q, n_head, nullptr, nullptr, as_stream(stream));
     }
     dim3 grid((unsigned) ((n_q + 4 * FA_R - 1) / (4 * FA_R)), (unsigned) n_head);
     const bool has_skip = mask != nullptr || (n_kv % 32) != 0;

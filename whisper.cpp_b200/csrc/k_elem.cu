@@ -74,10 +74,13 @@ k_layer_norm(const char * __restrict__ x, const float * __restrict__ gamma, cons
 // few rows (decode): one CTA of 256 threads per row, row held in registers
 struct LnRows { const float * x[64]; float * y[64]; };
 __global__ void __launch_bounds__(256)
-k_layer_norm_row(LnRows rows, const float * __restrict__ gamma, const float * __restrict__ beta, int ne00, float eps) {
+k_layer_norm_row(LnRows rows, const float * __restrict__ gamma, const float * __restrict__ beta, int ne00, float eps,
+                 int8_t * __restrict__ xq, float * __restrict__ xd) {
     __shared__ double red[8];
     __shared__ float s_mean, s_scale;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    chain_release();
+    chain_wait();
     const float * xp = rows.x[blockIdx.x];
     float *       yp = rows.y[blockIdx.x];
     float v[8];
@@ -121,7 +124,18 @@ k_layer_norm_row(LnRows rows, const float * __restrict__ gamma, const float * __
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
         const int i = tid + u * 256;
-        if (i < ne00) yp[i] = __fadd_rn(__fmul_rn(__fmul_rn(v[u], scale), gamma[i]), beta[i]);
+        float y = 0.0f;
+        if (i < ne00) { y = __fadd_rn(__fmul_rn(__fmul_rn(v[u], scale), gamma[i]), beta[i]); yp[i] = y; }
+        // optional second output: the row quantised as quantize_row_q8_0 does it (ne00 a multiple of 32: a warp holds one
+        // 32-block per pass), in the layout of b200_quantize_cols, for the product that consumes this row next
+        if (xq != nullptr && u * 256 + warp * 32 < ne00) {
+            float amax = fabsf(y);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            const float id = (amax != 0.0f) ? __fdiv_rn(127.f, amax) : 0.0f;
+            xq[(size_t) blockIdx.x * ne00 + i] = (int8_t) __float2int_rn(__fmul_rn(y, id));
+            if (lane == 0) xd[(size_t) blockIdx.x * (ne00 >> 5) + (i >> 5)] = round_f16(__fdiv_rn(amax, 127.f));
+        }
     }
 }
 
@@ -134,7 +148,7 @@ extern "C" int b200_layer_norm(const float * x, const float * gamma, const float
             r.x[i] = (const float *) ((const char *) x + i * x_row_stride_bytes);
             r.y[i] = (float *) ((char *) y + i * y_row_stride_bytes);
         }
-        k_layer_norm_row<<<(unsigned) nrows, 256, 0, as_stream(stream)>>>(r, gamma, beta, (int) ne00, eps);
+        k_layer_norm_row<<<(unsigned) nrows, 256, 0, as_stream(stream)>>>(r, gamma, beta, (int) ne00, eps, nullptr, nullptr);
         B200_RETURN_LAST();
     }
     k_layer_norm<<<(unsigned) ((nrows + 3) / 4), 128, 0, as_stream(stream)>>>((const char *) x, gamma, beta, (char *) y, ne00, nrows,
@@ -147,7 +161,17 @@ extern "C" int b200_layer_norm_rows(const b200_ln_row * rows, int n_rows, const 
     if (n_rows > 64 || ne00 <= 0 || ne00 > 2048) return B200_ERR_ARG;
     LnRows r;
     for (int i = 0; i < n_rows; ++i) { r.x[i] = rows[i].x; r.y[i] = rows[i].y; }
-    k_layer_norm_row<<<(unsigned) n_rows, 256, 0, as_stream(stream)>>>(r, gamma, beta, (int) ne00, eps);
+    launch_chained(k_layer_norm_row, dim3((unsigned) n_rows), dim3(256), 0, as_stream(stream), r, gamma, beta, (int) ne00, eps, (int8_t *) nullptr, (float *) nullptr);
+    B200_RETURN_LAST();
+}
+
+extern "C" int b200_layer_norm_rows_q(const b200_ln_row * rows, int n_rows, const float * gamma, const float * beta, int64_t ne00, float eps,
+                                      int8_t * xq, float * xd, void * stream) {
+    if (n_rows <= 0) return 0;
+    if (n_rows > 64 || ne00 <= 0 || ne00 > 2048 || ne00 % 32 != 0 || !xq || !xd) return B200_ERR_ARG;
+    LnRows r;
+    for (int i = 0; i < n_rows; ++i) { r.x[i] = rows[i].x; r.y[i] = rows[i].y; }
+    launch_chained(k_layer_norm_row, dim3((unsigned) n_rows), dim3(256), 0, as_stream(stream), r, gamma, beta, (int) ne00, eps, xq, xd);
     B200_RETURN_LAST();
 }
 

@@ -137,26 +137,24 @@ __device__ __forceinline__ float mma_ep_apply(const MmaEp & ep, int64_t n, int64
     return v;
 }
 
-// CTA: 4 x 3 warps, warp tile 16 rows x 24 columns -> 64 x 72 outputs; 1500 columns of a 1280-row weight give
-// 20 x 21 = 420 CTAs, a little under three full waves of one CTA per SM.  Operands arrive by cp.async (16 bytes,
-// zero fill beyond M / N), three stages of four 32-blocks.
-#define MMA_WM 4
-#define MMA_WN 3
-#define MMA_G 2
-#define MMA_T 3
+// CTA: WM x WN warps, warp tile 8G rows x 8T columns.  Default 4 x 3 warps of 16 x 24: 64 x 72 outputs, so that the
+// 1500 columns of a 1280-row weight give 20 x 21 = 420 CTAs, a little under three full waves of one CTA per SM.
+// Operands arrive by cp.async (16 bytes, zero fill beyond M / N), three stages of four 32-blocks.
 #define MMA_KC 4
 #define MMA_STAGES 3
-#define MMA_BM (MMA_WM * 8 * MMA_G)
-#define MMA_BN (MMA_WN * 8 * MMA_T)
-#define MMA_THREADS (MMA_WM * MMA_WN * 32)
-#define MMA_STAGE_BYTES (MMA_KC * MMA_BM * 64 + MMA_KC * MMA_BN * 64 + MMA_BM * MMA_KC * 4 + MMA_KC * MMA_BN * 4)
-#define MMA_SMEM_BYTES (MMA_STAGES * MMA_STAGE_BYTES)
+template <int WM, int WN, int G, int T> struct MmaCfg {
+    static constexpr int BM = WM * 8 * G, BN = WN * 8 * T, THREADS = WM * WN * 32;
+    static constexpr int STAGE_BYTES = MMA_KC * BM * 64 + MMA_KC * BN * 64 + BM * MMA_KC * 4 + MMA_KC * BN * 4;
+    static constexpr int SMEM_BYTES = MMA_STAGES * STAGE_BYTES;
+};
 
-__global__ void __launch_bounds__(MMA_THREADS, 1)
+template <int WM, int WN, int G, int T>
+__global__ void __launch_bounds__(WM * WN * 32, 1)
 k_mul_mat_mma(const uint32_t * __restrict__ wh, const float * __restrict__ wd, int64_t M, int nbk,
               const uint32_t * __restrict__ xh, const float * __restrict__ xd, int64_t N,
               void * __restrict__ dst, int64_t ldd, MmaEp ep) {
-    constexpr int BM = MMA_BM, BN = MMA_BN, KC = MMA_KC, G = MMA_G, T = MMA_T;
+    typedef MmaCfg<WM, WN, G, T> Cfg;
+    constexpr int BM = Cfg::BM, BN = Cfg::BN, KC = MMA_KC, MMA_THREADS = Cfg::THREADS, MMA_STAGE_BYTES = Cfg::STAGE_BYTES;
     constexpr int OFF_X = KC * BM * 64, OFF_DW = OFF_X + KC * BN * 64, OFF_DX = OFF_DW + BM * KC * 4;
     static_assert(BN * (BM + 1) * 4 <= MMA_STAGE_BYTES, "epilogue tile fits one stage");
     static_assert(BN * KC <= MMA_THREADS && BM <= MMA_THREADS, "one scale piece per thread");
@@ -164,7 +162,7 @@ k_mul_mat_mma(const uint32_t * __restrict__ wh, const float * __restrict__ wd, i
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    const int wm = warp % MMA_WM, wn = warp / MMA_WM;
+    const int wm = warp % WM, wn = warp / WM;
     const int64_t m0 = (int64_t) blockIdx.x * BM;
     const int64_t n0 = (int64_t) blockIdx.y * BN;
     const unsigned smem_u = (unsigned) __cvta_generic_to_shared(mma_smem);
@@ -250,35 +248,22 @@ k_mul_mat_mma(const uint32_t * __restrict__ wh, const float * __restrict__ wd, i
                 const float dw = dWs[row * KC + kb];
                 dwp[gi] = pk2(dw, dw);
             }
-            uint32_t xr[T][4];
-            f32x2 dxp[T];
 #pragma unroll
             for (int ti = 0; ti < T; ++ti) {
                 const int col = wn * (8 * T) + ti * 8;
                 const uint4 xv = *(const uint4 *) &Xs[(kb * BN + col + g) * 16 + t * 4];
-                xr[ti][0] = xv.x; xr[ti][1] = xv.y; xr[ti][2] = xv.z; xr[ti][3] = xv.w;
-                dxp[ti] = *(const f32x2 *) &dXs[kb * BN + col + 2 * t];
-            }
-            // The G*T quads (four MMAs each) of this block are software-pipelined: the MMAs of quad i+1 are issued
-            // between the packed FMAs that consume quad i, so that the tensor pipe and the FMA pipe work side by side.
-            f32x2 q[2][8];
+                const uint32_t xr[4] = {xv.x, xv.y, xv.z, xv.w};
+                const f32x2 dxp = *(const f32x2 *) &dXs[kb * BN + col + 2 * t];
 #pragma unroll
-            for (int r = 0; r < 4; ++r) hmma_lane_sums(q[0][2 * r], q[0][2 * r + 1], a0[0][r], a1[0][r], xr[0][r]);
-#pragma unroll
-            for (int i = 0; i < G * T; ++i) {
-                const int ti = i / G, gi = i % G, cur = i & 1;
-                const f32x2 d = mul2(dwp[gi], dxp[ti]);
-                if (i + 1 < G * T) {
-                    const int ti2 = (i + 1) / G, gi2 = (i + 1) % G;
+                for (int gi = 0; gi < G; ++gi) {
+                    const f32x2 d = mul2(dwp[gi], dxp);
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
-                        hmma_lane_sums(q[cur ^ 1][2 * r], q[cur ^ 1][2 * r + 1], a0[gi2][r], a1[gi2][r], xr[ti2][r]);
-                        acc[gi][ti][2 * r]     = fma2(d, q[cur][2 * r],     acc[gi][ti][2 * r]);
-                        acc[gi][ti][2 * r + 1] = fma2(d, q[cur][2 * r + 1], acc[gi][ti][2 * r + 1]);
+                        f32x2 q01, q23;
+                        hmma_lane_sums(q01, q23, a0[gi][r], a1[gi][r], xr[r]);
+                        acc[gi][ti][2 * r]     = fma2(d, q01, acc[gi][ti][2 * r]);
+                        acc[gi][ti][2 * r + 1] = fma2(d, q23, acc[gi][ti][2 * r + 1]);
                     }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) acc[gi][ti][j] = fma2(d, q[cur][j], acc[gi][ti][j]);
                 }
             }
         }
@@ -321,6 +306,24 @@ k_mul_mat_mma(const uint32_t * __restrict__ wh, const float * __restrict__ wd, i
 
 const uint16_t * b200_gelu_table_device(int * err);
 
+template <int WM, int WN, int G, int T>
+static int launch_mma(const void * wh, const float * wd, int64_t M, int64_t K, const void * xh, const float * xd, int64_t N,
+                      void * dst, int64_t ldd, const MmaEp & e, cudaStream_t st) {
+    typedef MmaCfg<WM, WN, G, T> Cfg;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaError_t ce = cudaFuncSetAttribute(k_mul_mat_mma<WM, WN, G, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+        if (ce != cudaSuccess) return (int) ce;
+        attr_done[dev] = true;
+    }
+    dim3 grid((unsigned) ((M + Cfg::BM - 1) / Cfg::BM), (unsigned) ((N + Cfg::BN - 1) / Cfg::BN));
+    k_mul_mat_mma<WM, WN, G, T><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, st>>>((const uint32_t *) wh, wd, M, (int) (K / 32),
+                                                                              (const uint32_t *) xh, xd, N, dst, ldd, e);
+    return 0;
+}
+
 extern "C" int b200_mul_mat_mma_ep(const void * wh, const float * wd, int64_t M, int64_t K,
                                    const void * xh, const float * xd, int64_t N,
                                    void * dst, int64_t dst_stride, const b200_epilogue * ep, void * stream) {
@@ -341,16 +344,11 @@ extern "C" int b200_mul_mat_mma_ep(const void * wh, const float * wd, int64_t M,
             } else if (e.kind[s] != B200_EP_SCALE) return B200_ERR_ARG;
         }
     }
-    static bool attr_done[64] = {false};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        cudaError_t ce = cudaFuncSetAttribute(k_mul_mat_mma, cudaFuncAttributeMaxDynamicSharedMemorySize, MMA_SMEM_BYTES);
-        if (ce != cudaSuccess) return (int) ce;
-        attr_done[dev] = true;
-    }
-    dim3 grid((unsigned) ((M + MMA_BM - 1) / MMA_BM), (unsigned) ((N + MMA_BN - 1) / MMA_BN));
-    k_mul_mat_mma<<<grid, MMA_THREADS, MMA_SMEM_BYTES, as_stream(stream)>>>((const uint32_t *) wh, wd, M, (int) (K / 32),
-                                                                           (const uint32_t *) xh, xd, N, dst, dst_stride, e);
+    static const int cfg = getenv("B200_MMA_CFG") ? atoi(getenv("B200_MMA_CFG")) : 0;
+    int rc;
+    if (cfg == 1)      rc = launch_mma<4, 4, 2, 2>(wh, wd, M, K, xh, xd, N, dst, dst_stride, e, as_stream(stream));
+    else if (cfg == 2) rc = launch_mma<2, 7, 2, 2>(wh, wd, M, K, xh, xd, N, dst, dst_stride, e, as_stream(stream));
+    else               rc = launch_mma<4, 3, 2, 3>(wh, wd, M, K, xh, xd, N, dst, dst_stride, e, as_stream(stream));
+    if (rc) return rc;
     B200_RETURN_LAST();
 }

@@ -11,6 +11,10 @@
 std::atomic<int64_t> g_b200_launches{0};
 
 extern "C" int64_t b200_launch_count(void) { return g_b200_launches.load(); }
+bool b200_chained_launches(void) {
+    static const bool on = getenv("B200_NO_PDL") == nullptr;
+    return on;
+}
 extern "C" const char * b200_version(void) { return "b200-whisper 0.1 (sm_100a)"; }
 
 // ------------------------------------------------------------------------------------------------
@@ -659,7 +663,9 @@ k_mul_mat_vec_q(QPlanes w, int64_t M, int64_t nbk, GemvCols cols, int rows_per_w
             pdw = __half2float(w.d[blk]);
         }
     };
+    chain_release();
     if (rows_here > 0) prefetch(row0, 0);
+    chain_wait();                                    // the activations come from the kernel before this one
 
     // quantise the activation columns (whole CTA): every thread fetches float4 pieces up front (four loads in
     // flight per column), eight consecutive lanes hold one 32-block and share its maximum by shuffles.
@@ -775,7 +781,7 @@ static int launch_vec(const QPlanes & w, int64_t M, int64_t nbk, const GemvCols 
     int rpw = 1;
     while (rpw < 8 && (M + 4 * (rpw * 2) - 1) / (4 * (rpw * 2)) >= 148 * 4) rpw *= 2;
     const int64_t rows_per_cta = 4 * rpw;
-    k_mul_mat_vec_q<TYPE, N><<<(unsigned) ((M + rows_per_cta - 1) / rows_per_cta), 128, smem, st>>>(w, M, nbk, cols, rpw, ep);
+    launch_chained(k_mul_mat_vec_q<TYPE, N>, dim3((unsigned) ((M + rows_per_cta - 1) / rows_per_cta)), dim3(128), smem, st, w, M, nbk, cols, rpw, ep);
     B200_RETURN_LAST();
 }
 
@@ -911,6 +917,7 @@ k_gemv_skinny(QPlanes w, int64_t M, int nbk, const int8_t * __restrict__ xq, con
     float * dX  = dW + R * nbk;                                       // [n_cols][nbk]
     const int tid = threadIdx.x;
     const int64_t row0 = (int64_t) blockIdx.x * R;
+    chain_release();
 
     for (int it = tid; it < R * nbk; it += 256) {                     // weight rows: one (row, block) per thread and pass
         const int r = it / nbk, ib = it - r * nbk;
@@ -938,6 +945,7 @@ k_gemv_skinny(QPlanes w, int64_t M, int nbk, const int8_t * __restrict__ xq, con
         *(int4 *) &Wsm[r * RS + ib * 8 + 4] = make_int4(wv[4], wv[5], wv[6], wv[7]);
         dW[r * nbk + ib] = dw;
     }
+    chain_wait();                                                     // the columns come from the kernel before this one
     {
         const uint4 * src = (const uint4 *) xq;
         uint4 * dstv = (uint4 *) Xsm;
@@ -995,7 +1003,7 @@ static int launch_skinny(const QPlanes & w, int64_t M, int nbk, const int8_t * x
         cudaFuncSetAttribute(k_gemv_skinny<TYPE, R, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         attr_done[dev] = true;
     }
-    k_gemv_skinny<TYPE, R, CT><<<(unsigned) ((M + R - 1) / R), 256, smem, st>>>(w, M, nbk, xq, xd, n_cols, cols, ep);
+    launch_chained(k_gemv_skinny<TYPE, R, CT>, dim3((unsigned) ((M + R - 1) / R)), dim3(256), smem, st, w, M, nbk, xq, xd, n_cols, cols, ep);
     B200_RETURN_LAST();
 }
 
@@ -1016,6 +1024,7 @@ k_gemv_skinny2(QPlanes w, int64_t M, int nbk, const int8_t * __restrict__ xq, co
     float * dX  = dW + R * nbk;                                       // [n_cols][nbk]
     const int tid = threadIdx.x, nthr = blockDim.x;
     const int64_t row0 = (int64_t) blockIdx.x * R;
+    chain_release();
 
     for (int it = tid; it < R * nbk; it += nthr) {
         const int r = it / nbk, ib = it - r * nbk;
@@ -1043,6 +1052,7 @@ k_gemv_skinny2(QPlanes w, int64_t M, int nbk, const int8_t * __restrict__ xq, co
         *(int4 *) &Wsm[r * WS + ib * 8 + 4] = make_int4(wv[4], wv[5], wv[6], wv[7]);
         dW[r * nbk + ib] = dw;
     }
+    chain_wait();                                                     // the columns come from the kernel before this one
     {
         const uint4 * src = (const uint4 *) xq;
         const int per_col = nbk * 2;                                  // 16-byte pieces per column
@@ -1108,7 +1118,7 @@ static int launch_skinny2(const QPlanes & w, int64_t M, int nbk, const int8_t * 
         cudaFuncSetAttribute(k_gemv_skinny2<TYPE, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
         attr_done[dev] = true;
     }
-    k_gemv_skinny2<TYPE, R><<<(unsigned) ((M + R - 1) / R), R * CP, smem, st>>>(w, M, nbk, xq, xd, n_cols, cols, ep);
+    launch_chained(k_gemv_skinny2<TYPE, R>, dim3((unsigned) ((M + R - 1) / R)), dim3(R * CP), smem, st, w, M, nbk, xq, xd, n_cols, cols, ep);
     B200_RETURN_LAST();
 }
 
@@ -1135,6 +1145,8 @@ struct ColPtrs32 { const float * x[32]; };
 __global__ void k_quantize_cols(ColPtrs32 cols, int n_cols, int nbk, int8_t * __restrict__ qs, float * __restrict__ d) {
     const int lane = threadIdx.x & 31;
     const int blk  = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    chain_release();
+    chain_wait();
     if (blk >= n_cols * nbk) return;
     const int c = blk / nbk, ib = blk - c * nbk;
     const float v = cols.x[c][ib * 32 + lane];
@@ -1151,7 +1163,7 @@ extern "C" int b200_quantize_cols(const float * const * x_cols, int n_cols, int6
     for (int i = 0; i < n_cols; ++i) { if (!x_cols[i]) return B200_ERR_ARG; c.x[i] = x_cols[i]; }
     const int nbk = (int) (K / 32);
     const int nblk = n_cols * nbk;
-    k_quantize_cols<<<(unsigned) ((nblk + 7) / 8), 256, 0, as_stream(stream)>>>(c, n_cols, nbk, xq, xd);
+    launch_chained(k_quantize_cols, dim3((unsigned) ((nblk + 7) / 8)), dim3(256), 0, as_stream(stream), c, n_cols, nbk, xq, xd);
     B200_RETURN_LAST();
 }
 
