@@ -139,6 +139,23 @@ struct enc_gate {
 };
 static enc_gate g_enc_gate;
 
+// Measurement aid: when a hook is set, the states of a batch meet after their prompt step and the last one to arrive
+// calls hook(1) before anybody takes the first single-token step (per-operator timing of the decode loop alone).
+static void (*g_phase_hook)(int) = nullptr;
+static int g_phase_parties = 0, g_phase_arrived = 0;
+static std::mutex g_phase_mu;
+static std::condition_variable g_phase_cv;
+void drv_set_decode_phase_hook(void (*hook)(int), int parties) {
+    std::lock_guard<std::mutex> lk(g_phase_mu);
+    g_phase_hook = hook; g_phase_parties = parties; g_phase_arrived = 0;
+}
+static void decode_phase_meet() {
+    std::unique_lock<std::mutex> lk(g_phase_mu);
+    if (!g_phase_hook || g_phase_parties <= 0) return;
+    if (++g_phase_arrived >= g_phase_parties) { g_phase_hook(1); g_phase_cv.notify_all(); }
+    else g_phase_cv.wait(lk, [&] { return g_phase_arrived >= g_phase_parties || !g_phase_hook; });
+}
+
 int drv_greedy(void * vctx, void * vst, int n_new, int threads, const int * force, int * out, float * margins, float * logits_out) {
     struct whisper_context * ctx = (struct whisper_context *) vctx;
     struct whisper_state *   st  = (struct whisper_state *) vst;
@@ -150,6 +167,7 @@ int drv_greedy(void * vctx, void * vst, int n_new, int threads, const int * forc
     drv_prefix(ctx, prefix);
     const int n_vocab = whisper_n_vocab(ctx);
     if (whisper_decode_with_state(ctx, st, prefix, 4, 0, threads) != 0) return -2;
+    decode_phase_meet();
     int n_past = 4;
     for (int i = 0; i < n_new; ++i) {
         // logits of the last fed token: row n_tokens-1 of the state's logits buffer

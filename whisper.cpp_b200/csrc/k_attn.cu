@@ -68,7 +68,7 @@ __device__ __forceinline__ float expf_glibc(float x) {
 // is not a multiple of 32; without it the per-key "skipped" handling is compiled out.
 #define FA_R 4
 template <bool S_FMA, bool HAS_SKIP>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, 5)
 k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
                  const char * __restrict__ k, int64_t nbk1, int64_t nbk2,
                  const char * __restrict__ v, int64_t nbv1, int64_t nbv2,
@@ -240,7 +240,6 @@ k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
 #define FA_DEC_THREADS 128
 #define FA_DEC_MAX_KV  8192
 #define FA_DEC_CHUNK   64
-#define FA_DEC_STAGES  3
 #define FA_DEC_MAX_ROWS 32
 struct FaRow {
     const char * q;        // 64 f32 per head, head stride nbq2
@@ -256,7 +255,9 @@ struct FaRows {
     float scale;
 };
 
-template <bool S_FMA>
+// STAGES buffers of FA_DEC_CHUNK keys: STAGES - 1 chunks are in flight ahead of the one in use (3: small enough for all
+// CTAs of 32 rows x 20 heads to be resident at once; 6 was measured and changes nothing, the CTA is bound by its chains)
+template <bool S_FMA, int STAGES>
 __global__ void __launch_bounds__(FA_DEC_THREADS)
 k_flash_attn_decode(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * __restrict__ xd) {
     extern __shared__ __align__(16) float fa_smem[];
@@ -268,7 +269,7 @@ k_flash_attn_decode(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * _
     float * sc  = Qs + 64;                 // [n_kv] scores, later vs (-0.0f marks a skipped key)
     float * msv = sc + max_kv;             // [n_kv] ms (1 unless a new maximum)
     unsigned char * evt = (unsigned char *) (msv + max_kv);                 // [n_kv/8] group contains a new maximum
-    __half * Vs = (__half *) (fa_smem + ((64 + 2 * max_kv + (max_kv + 31) / 32 + 3) & ~3));   // [FA_DEC_STAGES][FA_DEC_CHUNK][64], 16-byte aligned
+    __half * Vs = (__half *) (fa_smem + ((64 + 2 * max_kv + (max_kv + 31) / 32 + 3) & ~3));   // [STAGES][FA_DEC_CHUNK][64], 16-byte aligned
     __shared__ float seg_max[FA_DEC_THREADS];
     __shared__ float s_S;
     const int tid = threadIdx.x;
@@ -285,55 +286,96 @@ k_flash_attn_decode(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * _
     const char * vh = R.v + h * rows.nbv2;
     const __half * mp = (const __half *) R.mask;
 
-    // scores
-#pragma unroll 2
-    for (int ic = tid; ic < n_kv; ic += FA_DEC_THREADS) {
-        float mv = 0.0f;
-        if (mp) mv = __half2float(mp[ic]);
-        float s = -INFINITY;
-        const bool skip = (mv == -INFINITY);
-        if (!skip) {
-            float acc[32];
-            const uint4 * kp = (const uint4 *) (kh + (int64_t) ic * nbk1);
-#pragma unroll
-            for (int step = 0; step < 2; ++step) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const uint4 kv = kp[step * 4 + c];
-                    const float4 qa = *(const float4 *) &Qs[step * 32 + c * 8];
-                    const float4 qb = *(const float4 *) &Qs[step * 32 + c * 8 + 4];
-                    const float2 k0 = __half22float2(*(const __half2 *) &kv.x);
-                    const float2 k1 = __half22float2(*(const __half2 *) &kv.y);
-                    const float2 k2 = __half22float2(*(const __half2 *) &kv.z);
-                    const float2 k3 = __half22float2(*(const __half2 *) &kv.w);
-                    float * a = &acc[c * 8];
-                    if (step == 0) {
-                        a[0] = __fmaf_rn(k0.x, qa.x, 0.0f); a[1] = __fmaf_rn(k0.y, qa.y, 0.0f);
-                        a[2] = __fmaf_rn(k1.x, qa.z, 0.0f); a[3] = __fmaf_rn(k1.y, qa.w, 0.0f);
-                        a[4] = __fmaf_rn(k2.x, qb.x, 0.0f); a[5] = __fmaf_rn(k2.y, qb.y, 0.0f);
-                        a[6] = __fmaf_rn(k3.x, qb.z, 0.0f); a[7] = __fmaf_rn(k3.y, qb.w, 0.0f);
-                    } else {
-                        a[0] = __fmaf_rn(k0.x, qa.x, a[0]); a[1] = __fmaf_rn(k0.y, qa.y, a[1]);
-                        a[2] = __fmaf_rn(k1.x, qa.z, a[2]); a[3] = __fmaf_rn(k1.y, qa.w, a[3]);
-                        a[4] = __fmaf_rn(k2.x, qb.x, a[4]); a[5] = __fmaf_rn(k2.y, qb.y, a[5]);
-                        a[6] = __fmaf_rn(k3.x, qb.z, a[6]); a[7] = __fmaf_rn(k3.y, qb.w, a[7]);
-                    }
-                }
+    // scores: K is streamed through shared memory in chunks of FA_DEC_CHUNK keys (the buffers V uses later), copied
+    // asynchronously in 16-byte pieces that are contiguous in global memory; the eight pieces of a key row are stored
+    // XOR-swizzled by the key index so that the threads of a warp, one key each, read them without bank conflicts.
+    // Warps 0..1 score chunk c while chunks c+1 and c+2 are in flight.
+    {
+        const int n_chunks = (n_kv + FA_DEC_CHUNK - 1) / FA_DEC_CHUNK;
+        auto fetch_k = [&](int c) {
+            const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);      // kn <= 0 beyond the last chunk: empty group
+            const unsigned base = (unsigned) __cvta_generic_to_shared(Vs + (size_t) (c % STAGES) * FA_DEC_CHUNK * 64);
+            for (int t = tid; t < kn * 8; t += FA_DEC_THREADS) {
+                const int key = t >> 3, pc = t & 7;
+                const char * src = kh + (int64_t) (k0 + key) * nbk1 + pc * 16;
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(base + key * 128 + ((pc ^ (key & 7)) << 4)), "l"(src) : "memory");
             }
-            float y[8];
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        // one group is committed per prologue slot and per iteration (empty beyond the last chunk), so chunk c is always
+        // followed by exactly STAGES - 2 younger groups when it is waited for
 #pragma unroll
-            for (int p = 0; p < 8; ++p)
-                y[p] = __fadd_rn(__fadd_rn(acc[p], acc[16 + p]), __fadd_rn(acc[8 + p], acc[24 + p]));
-            const float t0 = __fadd_rn(y[0], y[4]), t1 = __fadd_rn(y[1], y[5]);
-            const float t2 = __fadd_rn(y[2], y[6]), t3 = __fadd_rn(y[3], y[7]);
-            s = __fadd_rn(__fadd_rn(t0, t1), __fadd_rn(t2, t3));
-            s = __fmul_rn(s, scale);
-            s = __fadd_rn(s, mv);
+        for (int c = 0; c < STAGES - 1; ++c) fetch_k(c);
+        for (int c = 0; c < n_chunks; ++c) {
+            const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
+            asm volatile("cp.async.wait_group %0;" :: "n"(STAGES - 2) : "memory");
+            __syncthreads();
+            fetch_k(c + STAGES - 1);
+            if (tid < kn) {
+                const int ic = k0 + tid;
+                float mv = 0.0f;
+                if (mp) mv = __half2float(mp[ic]);
+                float s = -INFINITY;
+                const bool skip = (mv == -INFINITY);
+                if (!skip) {
+                    float acc[32];
+                    const char * krow = (const char *) (Vs + (size_t) (c % STAGES) * FA_DEC_CHUNK * 64) + tid * 128;
+#pragma unroll
+                    for (int step = 0; step < 2; ++step) {
+#pragma unroll
+                        for (int cc = 0; cc < 4; ++cc) {
+                            const uint4 kv = *(const uint4 *) (krow + (((step * 4 + cc) ^ (tid & 7)) << 4));
+                            const float4 qa = *(const float4 *) &Qs[step * 32 + cc * 8];
+                            const float4 qb = *(const float4 *) &Qs[step * 32 + cc * 8 + 4];
+                            const float2 k0v = __half22float2(*(const __half2 *) &kv.x);
+                            const float2 k1v = __half22float2(*(const __half2 *) &kv.y);
+                            const float2 k2v = __half22float2(*(const __half2 *) &kv.z);
+                            const float2 k3v = __half22float2(*(const __half2 *) &kv.w);
+                            float * a = &acc[cc * 8];
+                            if (step == 0) {
+                                a[0] = __fmaf_rn(k0v.x, qa.x, 0.0f); a[1] = __fmaf_rn(k0v.y, qa.y, 0.0f);
+                                a[2] = __fmaf_rn(k1v.x, qa.z, 0.0f); a[3] = __fmaf_rn(k1v.y, qa.w, 0.0f);
+                                a[4] = __fmaf_rn(k2v.x, qb.x, 0.0f); a[5] = __fmaf_rn(k2v.y, qb.y, 0.0f);
+                                a[6] = __fmaf_rn(k3v.x, qb.z, 0.0f); a[7] = __fmaf_rn(k3v.y, qb.w, 0.0f);
+                            } else {
+                                a[0] = __fmaf_rn(k0v.x, qa.x, a[0]); a[1] = __fmaf_rn(k0v.y, qa.y, a[1]);
+                                a[2] = __fmaf_rn(k1v.x, qa.z, a[2]); a[3] = __fmaf_rn(k1v.y, qa.w, a[3]);
+                                a[4] = __fmaf_rn(k2v.x, qb.x, a[4]); a[5] = __fmaf_rn(k2v.y, qb.y, a[5]);
+                                a[6] = __fmaf_rn(k3v.x, qb.z, a[6]); a[7] = __fmaf_rn(k3v.y, qb.w, a[7]);
+                            }
+                        }
+                    }
+                    float y[8];
+#pragma unroll
+                    for (int pp = 0; pp < 8; ++pp)
+                        y[pp] = __fadd_rn(__fadd_rn(acc[pp], acc[16 + pp]), __fadd_rn(acc[8 + pp], acc[24 + pp]));
+                    const float t0 = __fadd_rn(y[0], y[4]), t1 = __fadd_rn(y[1], y[5]);
+                    const float t2 = __fadd_rn(y[2], y[6]), t3 = __fadd_rn(y[3], y[7]);
+                    s = __fadd_rn(__fadd_rn(t0, t1), __fadd_rn(t2, t3));
+                    s = __fmul_rn(s, scale);
+                    s = __fadd_rn(s, mv);
+                }
+                sc[ic]  = s;                       // -inf for skipped keys: never a new maximum
+                msv[ic] = skip ? -1.0f : 1.0f;     // temporary skip mark
+            }
         }
-        sc[ic]  = s;                       // -inf for skipped keys: never a new maximum
-        msv[ic] = skip ? -1.0f : 1.0f;     // temporary skip mark
     }
     __syncthreads();
+
+    // V takes over the buffers: its first two chunks are requested now and arrive while the maxima and exponentials
+    // below are computed
+    const int n_chunks = (n_kv + FA_DEC_CHUNK - 1) / FA_DEC_CHUNK;
+    auto fetch = [&](int c) {
+        const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
+        const unsigned base = (unsigned) __cvta_generic_to_shared(Vs + (size_t) (c % STAGES) * FA_DEC_CHUNK * 64);
+        for (int t = tid; t < kn * 8; t += FA_DEC_THREADS) {
+            const char * src = vh + (int64_t) (k0 + (t >> 3)) * nbv1 + (t & 7) * 16;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(base + t * 16), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+#pragma unroll
+    for (int c = 0; c < STAGES - 1; ++c) fetch(c);
 
     // contiguous segment per thread: segment maxima, exclusive block scan, then the per-key pass
     const int seg = (n_kv + FA_DEC_THREADS - 1) / FA_DEC_THREADS;
@@ -370,37 +412,22 @@ k_flash_attn_decode(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * _
     }
     __syncthreads();
 
-    // V is streamed through shared memory in chunks of FA_DEC_CHUNK keys, FA_DEC_STAGES buffers: chunks c+1 and c+2 are
+    // V is streamed through shared memory in chunks of FA_DEC_CHUNK keys, STAGES buffers: chunks c+1 and c+2 are
     // being copied asynchronously while warps 0..1 (one thread per output dim) replay the F16 accumulation over chunk c
     // and one thread of warp 2 replays the running sum.  The buffers are kept small so that every (row, head) CTA of 32
     // rows x 20 heads is resident at once (no second wave).  Keys are taken eight at a time with all operands in registers; only groups that
     // contain a new maximum take the path that rescales the accumulator.
     {
-        const int n_chunks = (n_kv + FA_DEC_CHUNK - 1) / FA_DEC_CHUNK;
-        // asynchronous 16-byte copies (global -> shared, no register staging): every thread queues its share of the next
-        // chunk before it turns to its role, so the whole chunk is in flight while the current one is consumed
-        auto fetch = [&](int c) {
-            const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
-            const unsigned base = (unsigned) __cvta_generic_to_shared(Vs + (size_t) (c % FA_DEC_STAGES) * FA_DEC_CHUNK * 64);
-            for (int t = tid; t < kn * 8; t += FA_DEC_THREADS) {
-                const char * src = vh + (int64_t) (k0 + (t >> 3)) * nbv1 + (t & 7) * 16;
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(base + t * 16), "l"(src) : "memory");
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        };
-        fetch(0);
-        if (n_chunks > 1) fetch(1);
         float a = 0.0f, S = 0.0f;
         for (int c = 0; c < n_chunks; ++c) {
             const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
             // chunk c has landed (at most the group of chunk c+1 may still be in flight); the barrier also says that
             // everybody is done with chunk c-1, whose buffer chunk c+2 reuses
-            if (c + 1 < n_chunks) asm volatile("cp.async.wait_group 1;" ::: "memory");
-            else                  asm volatile("cp.async.wait_group 0;" ::: "memory");
+            asm volatile("cp.async.wait_group %0;" :: "n"(STAGES - 2) : "memory");
             __syncthreads();
-            if (c + 2 < n_chunks) fetch(c + 2);
+            fetch(c + STAGES - 1);
             if (tid < 64) {
-                const __half * vb = Vs + (size_t) (c % FA_DEC_STAGES) * FA_DEC_CHUNK * 64 + tid;
+                const __half * vb = Vs + (size_t) (c % STAGES) * FA_DEC_CHUNK * 64 + tid;
                 int i = 0;
                 for (; i + 8 <= kn; i += 8) {
                     float vs[8], vv[8];
@@ -462,8 +489,8 @@ k_flash_attn_decode(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * _
     }
 }
 
-static size_t fa_dec_smem(int max_kv) {
-    return (size_t) ((64 + 2 * max_kv + (max_kv + 31) / 32 + 3) & ~3) * sizeof(float) + FA_DEC_STAGES * FA_DEC_CHUNK * 64 * sizeof(__half);
+static size_t fa_dec_smem(int max_kv, int stages) {
+    return (size_t) ((64 + 2 * max_kv + (max_kv + 31) / 32 + 3) & ~3) * sizeof(float) + (size_t) stages * FA_DEC_CHUNK * 64 * sizeof(__half);
 }
 
 static bool g_fa_s_fma = true;
@@ -476,13 +503,13 @@ static int launch_fa_decode(const FaRows & rows, int n_rows, int64_t n_head, int
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        cudaFuncSetAttribute(k_flash_attn_decode<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) fa_dec_smem(FA_DEC_MAX_KV));
-        cudaFuncSetAttribute(k_flash_attn_decode<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) fa_dec_smem(FA_DEC_MAX_KV));
+        cudaFuncSetAttribute(k_flash_attn_decode<true, 3>,  cudaFuncAttributeMaxDynamicSharedMemorySize, (int) fa_dec_smem(FA_DEC_MAX_KV, 3));
+        cudaFuncSetAttribute(k_flash_attn_decode<false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) fa_dec_smem(FA_DEC_MAX_KV, 3));
         attr_done[dev] = true;
     }
     dim3 grid((unsigned) n_head, (unsigned) n_rows);
-    if (g_fa_s_fma) launch_chained(k_flash_attn_decode<true>, grid, dim3(FA_DEC_THREADS), fa_dec_smem(max_kv), st, rows, max_kv, xq, xd);
-    else            launch_chained(k_flash_attn_decode<false>, grid, dim3(FA_DEC_THREADS), fa_dec_smem(max_kv), st, rows, max_kv, xq, xd);
+    if (g_fa_s_fma) launch_chained(k_flash_attn_decode<true, 3>,  grid, dim3(FA_DEC_THREADS), fa_dec_smem(max_kv, 3), st, rows, max_kv, xq, xd);
+    else            launch_chained(k_flash_attn_decode<false, 3>, grid, dim3(FA_DEC_THREADS), fa_dec_smem(max_kv, 3), st, rows, max_kv, xq, xd);
     B200_RETURN_LAST();
 }
 
