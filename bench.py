@@ -39,11 +39,19 @@ TOTAL_CLIPS = 64
 
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one representative launch of each kernel class, from the
 # ncu captures summarised under profiles/ (small cases of the same kernels; traffic grows with the bytes streamed).
+# what actually limits each class (ncu counters, profiles/): the reference's summation orders are replayed exactly, which keeps
+# the attention kernels and the float chain of the products off the MMA accumulators
+LIMITER = {
+    "flash_attn_ext":    "F16 accumulation chain and 32-way score sums replayed exactly: instruction issue 49 %, tensor pipe unused by design",
+    "mul_mat_q":         "integer lane sums on the tensor pipe (f16 MMA, 44 % busy), float chain on the FMA pipe; 7/8 of each MMA are zero padding",
+    "mul_mat_vec_q":     "launch and load latency of small dependent launches, not bandwidth",
+    "flash_attn_decode": "sequential F16 chain over the keys of each (row, head); 46 % of HBM peak at 32 rows",
+}
 TRAFFIC_NCU = {
-    "mul_mat_vec_q":     {"bytes": 1.19e6,  "launch": "1280 x 1280 Q5_0 weights x 32 columns (algorithmic 1.34e6: columns and output stay in L2)"},
+    "mul_mat_vec_q":     {"bytes": 1.175e6, "launch": "1280 x 1280 Q5_0 weights x 16 columns (algorithmic 1.23e6: columns and output stay in L2)"},
     "flash_attn_decode": {"bytes": 251.9e6, "launch": "32 rows x 20 heads x 1536 keys (algorithmic 251.7e6)"},
     "flash_attn_ext":    {"bytes": 15.6e6,  "launch": "1500 x 1536 keys x 20 heads (Q + K/V once; K/V re-reads hit L2)"},
-    "mul_mat_q":         {"bytes": 3.3e6,   "launch": "1280 x 1280 Q5_0 x 1500 columns, dp4a kernel (weights + int8 activations once)"},
+    "mul_mat_q":         {"bytes": 7.6e6,   "launch": "1280 x 1280 x 1500 columns on the tensor pipe (packed weights 3.5e6 + packed activations 4.1e6, each once)"},
 }
 
 
@@ -320,7 +328,8 @@ def main():
                 ach, peak, unit, bound = per_launch_work / per_launch_s / 1e9, hbm, "GB/s", "hbm"
             roof = {"kernel": top, "bound": bound, "achieved": ach, "peak": peak, "unit": unit, "frac": ach / peak,
                     "traffic": TRAFFIC_NCU.get(top), "peak_source": which, "avg_us": per_launch_s * 1e6,
-                    "share_of_gpu_time": r["ms"] / sum(v["ms"] for v in per_clip.values()), "timed": r["timed"]}
+                    "share_of_gpu_time": r["ms"] / sum(v["ms"] for v in per_clip.values()), "timed": r["timed"],
+                    "note": LIMITER.get(top)}
 
     cpu_base = None
     if rank == 0 and not args.no_cpu_baseline:
