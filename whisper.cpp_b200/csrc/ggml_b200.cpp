@@ -968,7 +968,7 @@ static int run_plan(b200_backend_ctx * ctx, const exec_plan & plan, struct ggml_
             } else {
                 t_work->push_back(work * n_g);
             }
-            cudaEventRecord(next_event(), ctx->stream);
+            if (*n_ev == 0) cudaEventRecord(next_event(), ctx->stream);      // one event per item boundary: item k runs between events k and k+1
         }
         const int e = run_item(ctx, it, gs, n_g);
         if (timing) cudaEventRecord(next_event(), ctx->stream);
@@ -1174,7 +1174,7 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
                     std::lock_guard<std::mutex> tl(g_timing_mu);
                     for (size_t k = 0; k < bt_class.size(); ++k) {
                         float ms = 0;
-                        cudaEventElapsedTime(&ms, ctx->events[2 * k], ctx->events[2 * k + 1]);
+                        cudaEventElapsedTime(&ms, ctx->events[k], ctx->events[k + 1]);
                         g_tc_ms[bt_class[k]] += ms;
                         g_tc_work[bt_class[k]] += bt_work[k];
                         g_tc_count[bt_class[k]] += 1;
@@ -1242,7 +1242,7 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
         std::lock_guard<std::mutex> lk(g_timing_mu);
         for (size_t k = 0; k < t_class.size(); ++k) {
             float ms = 0;
-            cudaEventElapsedTime(&ms, ctx->events[2 * k], ctx->events[2 * k + 1]);
+            cudaEventElapsedTime(&ms, ctx->events[k], ctx->events[k + 1]);
             g_tc_ms[t_class[k]] += ms;
             g_tc_work[t_class[k]] += t_work[k];
             g_tc_count[t_class[k]] += 1;

@@ -29,7 +29,9 @@ static void ensure_exp_table() {
     done[dev] = true;
 }
 
-__device__ __forceinline__ float expf_glibc(float x) {
+// tab: the 32-entry 2^(i/32) table in SHARED memory (every lane indexes it differently; the same lookup in constant
+// memory is serialised per distinct address)
+__device__ __forceinline__ float expf_glibc(float x, const uint64_t * tab) {
     const uint32_t ux = __float_as_uint(x);
     const uint32_t abstop = (ux >> 20) & 0x7ffu;
     if (abstop >= 0x42bu) {                       // |x| >= 88
@@ -49,7 +51,7 @@ __device__ __forceinline__ float expf_glibc(float x) {
     const uint64_t ki = (uint64_t) __double_as_longlong(kd);
     kd = __dadd_rn(kd, -Shift);
     const double r = __dadd_rn(z, -kd);
-    uint64_t t = c_exp2f_tab[ki & 31];
+    uint64_t t = tab[ki & 31];
     t += ki << 47;
     const double s = __longlong_as_double((long long) t);
     z = __fma_rn(C0, r, C1);
@@ -77,10 +79,12 @@ k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
     __shared__ __align__(16) float Qs[4][FA_R][64];
     __shared__ __align__(16) float MS[4][FA_R][32];
     __shared__ __align__(16) float VS[4][FA_R][32];
+    __shared__ uint64_t s_exp_tab[32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t row0 = ((int64_t) blockIdx.x * 4 + warp) * FA_R;
     const int64_t h    = blockIdx.y;
     if (row0 >= n_q) return;
+    s_exp_tab[lane] = c_exp2f_tab[lane];      // every warp writes the same 32 values; visible to this warp after its __syncwarp
     const int n_rows = (int) min((int64_t) FA_R, n_q - row0);
 
 #pragma unroll
@@ -171,7 +175,7 @@ k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
             const float Mprev  = fmaxf(M[r], ex);
             const bool  newmax = !skip && (s > Mprev);
             float e = 1.0f;
-            if (!skip) e = expf_glibc(newmax ? __fadd_rn(Mprev, -s) : __fadd_rn(s, -Mprev));
+            if (!skip) e = expf_glibc(newmax ? __fadd_rn(Mprev, -s) : __fadd_rn(s, -Mprev), s_exp_tab);
             MS[warp][r][lane] = newmax ? e : 1.0f;
             VS[warp][r][lane] = skip ? -0.0f : (newmax ? 1.0f : e);
             if (__ballot_sync(0xffffffffu, newmax)) evt_any |= 1u << r;
@@ -257,6 +261,13 @@ struct FaRows {
 
 // STAGES buffers of FA_DEC_CHUNK keys: STAGES - 1 chunks are in flight ahead of the one in use (3: small enough for all
 // CTAs of 32 rows x 20 heads to be resident at once; 6 was measured and changes nothing, the CTA is bound by its chains)
+#ifdef FA_DEC_PROFILE
+__device__ long long g_fa_prof[8];
+#define FA_PROF(i) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) g_fa_prof[i] = clock64(); } while (0)
+extern "C" int b200_fa_prof_read(long long * out) { return (int) cudaMemcpyFromSymbol(out, g_fa_prof, sizeof(g_fa_prof)); }
+#else
+#define FA_PROF(i) do { } while (0)
+#endif
 template <bool S_FMA, int STAGES>
 __global__ void __launch_bounds__(FA_DEC_THREADS)
 k_flash_attn_decode(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * __restrict__ xd) {
@@ -272,13 +283,16 @@ k_flash_attn_decode(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * _
     __half * Vs = (__half *) (fa_smem + ((64 + 2 * max_kv + (max_kv + 31) / 32 + 3) & ~3));   // [STAGES][FA_DEC_CHUNK][64], 16-byte aligned
     __shared__ float seg_max[FA_DEC_THREADS];
     __shared__ float s_S;
+    __shared__ uint64_t s_exp_tab[32];
     const int tid = threadIdx.x;
     const int64_t h = blockIdx.x;
     const int64_t nbk1 = rows.nbk1, nbv1 = rows.nbv1;
     const float scale = rows.scale;
     chain_wait();                          // Q, and for self-attention the newest K/V rows, come from the kernels before this one
+    FA_PROF(0);
 
     if (tid < 64) Qs[tid] = round_f16(*(const float *) (R.q + h * rows.nbq2 + tid * 4));
+    if (tid >= 96) s_exp_tab[tid - 96] = c_exp2f_tab[tid - 96];
     for (int g = tid; g < (n_kv + 7) / 8; g += FA_DEC_THREADS) evt[g] = 0;
     __syncthreads();
 
@@ -362,6 +376,7 @@ k_flash_attn_decode(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * _
     }
     __syncthreads();
 
+    FA_PROF(1);
     // V takes over the buffers: its first two chunks are requested now and arrive while the maxima and exponentials
     // below are computed
     const int n_chunks = (n_kv + FA_DEC_CHUNK - 1) / FA_DEC_CHUNK;
@@ -402,16 +417,41 @@ k_flash_attn_decode(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * _
     }
     __syncthreads();
     {
+        // the running maximum is a cheap sequential chain; the exponentials (double precision inside) do not depend on
+        // each other, so four keys are taken at a time with the branches turned into selects
         float M = seg_max[tid];
-        for (int i = i0; i < i1; ++i) {
-            if (msv[i] < 0.0f) { msv[i] = 1.0f; sc[i] = -0.0f; continue; }      // skipped: ms = 1, vs = -0
+        int i = i0;
+        for (; i + 4 <= i1; i += 4) {
+            float arg[4], e[4];
+            bool skipk[4], newmax[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float s = sc[i + u];
+                skipk[u]  = msv[i + u] < 0.0f;
+                newmax[u] = !skipk[u] && s > M;
+                arg[u] = newmax[u] ? __fadd_rn(M, -s) : __fadd_rn(s, -M);
+                if (skipk[u]) arg[u] = 0.0f;
+                if (newmax[u]) M = s;
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) e[u] = expf_glibc(arg[u], s_exp_tab);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (skipk[u])       { msv[i + u] = 1.0f; sc[i + u] = -0.0f; }               // skipped: ms = 1, vs = -0
+                else if (newmax[u]) { msv[i + u] = e[u]; sc[i + u] = 1.0f; evt[(i + u) >> 3] = 1; }
+                else                { sc[i + u] = e[u]; }
+            }
+        }
+        for (; i < i1; ++i) {
+            if (msv[i] < 0.0f) { msv[i] = 1.0f; sc[i] = -0.0f; continue; }
             const float s = sc[i];
-            if (s > M) { msv[i] = expf_glibc(__fadd_rn(M, -s)); sc[i] = 1.0f; M = s; evt[i >> 3] = 1; }
-            else       { sc[i] = expf_glibc(__fadd_rn(s, -M)); }
+            if (s > M) { msv[i] = expf_glibc(__fadd_rn(M, -s), s_exp_tab); sc[i] = 1.0f; M = s; evt[i >> 3] = 1; }
+            else       { sc[i] = expf_glibc(__fadd_rn(s, -M), s_exp_tab); }
         }
     }
     __syncthreads();
 
+    FA_PROF(2);
     // V is streamed through shared memory in chunks of FA_DEC_CHUNK keys, STAGES buffers: chunks c+1 and c+2 are
     // being copied asynchronously while warps 0..1 (one thread per output dim) replay the F16 accumulation over chunk c
     // and one thread of warp 2 replays the running sum.  The buffers are kept small so that every (row, head) CTA of 32
@@ -429,13 +469,26 @@ k_flash_attn_decode(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * _
             if (tid < 64) {
                 const __half * vb = Vs + (size_t) (c % STAGES) * FA_DEC_CHUNK * 64 + tid;
                 int i = 0;
+                // Common case, a full chunk without a new maximum: one straight-line block of 64 dependent steps, so that the
+                // compiler can place the shared-memory loads and conversions of later keys into the latency gaps of the chain
+                // (a warp issues in order; with loops or branches in between it would wait for the loads instead).
+                if (kn == FA_DEC_CHUNK && *(const unsigned long long *) &evt[k0 >> 3] == 0ull) {
+#pragma unroll
+                    for (int u = 0; u < FA_DEC_CHUNK; ++u) {
+                        const float vsu = sc[k0 + u];
+                        float vvu = __half2float(vb[u * 64]);
+                        if (__float_as_uint(vsu) == 0x80000000u) vvu = 0.0f;         // skipped key: exact no-op whatever V holds
+                        a = round_f16(__fmaf_rn(vvu, vsu, a));
+                    }
+                    i = FA_DEC_CHUNK;
+                }
                 for (; i + 8 <= kn; i += 8) {
                     float vs[8], vv[8];
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
                         vs[u] = sc[k0 + i + u];
                         vv[u] = __half2float(vb[(i + u) * 64]);
-                        if (__float_as_uint(vs[u]) == 0x80000000u) vv[u] = 0.0f;     // skipped key: exact no-op whatever V holds
+                        if (__float_as_uint(vs[u]) == 0x80000000u) vv[u] = 0.0f;
                     }
                     if (!evt[(k0 + i) >> 3]) {
 #pragma unroll
@@ -468,6 +521,7 @@ k_flash_attn_decode(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * _
                 for (; i < kn; ++i) S = S_FMA ? __fmaf_rn(S, msv[k0 + i], sc[k0 + i]) : __fadd_rn(__fmul_rn(S, msv[k0 + i]), sc[k0 + i]);
             }
         }
+        FA_PROF(3);
         if (tid < 64) Qs[tid] = a;         // Qs is free now
         if (tid == 64) s_S = S;
     }
@@ -632,7 +686,7 @@ k_soft_max(const float * __restrict__ x, const char * __restrict__ mask, int mas
     }
     for (int64_t i = n8; i < ne00; ++i) {       // scalar tail uses libm expf
         float val = 0.0f;
-        if (lane == 0) { val = expf_glibc(__fadd_rn(dp[i], -mx)); dp[i] = val; }
+        if (lane == 0) { val = expf_glibc(__fadd_rn(dp[i], -mx), c_exp2f_tab); dp[i] = val; }
         val = __shfl_sync(0xffffffffu, val, 0);
         sum += (double) val;
     }
