@@ -5,6 +5,7 @@
 //    expf (table of 2^(i/32) + degree-3 polynomial in double);
 //  * soft_max (ops.cpp:4641-4737) with the vectorised exp of vec.h:603-640 and its 8-wide sums.
 #include "b200_common.cuh"
+#include <stdlib.h>
 #include <math.h>
 #include <mutex>
 
@@ -543,6 +544,188 @@ k_flash_attn_decode(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * _
     }
 }
 
+// Streaming form of the kernel above for launches whose CTAs are all resident with the larger buffers: warps 2..3
+// score chunk c+1 (one key per thread, running maximum carried from chunk to chunk, exponentials) while warps 0..1
+// replay the F16 accumulation and the running sum over chunk c, so that the sequential chain is the only thing on
+// the critical path.  K and V arrive through separate three-stage rings of FA_DEC_CHUNK keys.
+template <bool S_FMA>
+__global__ void __launch_bounds__(FA_DEC_THREADS)
+k_flash_attn_decode_stream(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * __restrict__ xd) {
+    extern __shared__ __align__(16) float fa_smem[];
+    const FaRow & R = rows.r[blockIdx.y];
+    const int n_kv = R.n_kv;
+    float * Qs  = fa_smem;                 // [64]
+    float * sc  = Qs + 64;                 // [n_kv] vs (-0.0f marks a skipped key)
+    float * msv = sc + max_kv;             // [n_kv] ms (1 unless a new maximum)
+    unsigned char * evt = (unsigned char *) (msv + max_kv);                 // [n_kv/8] group contains a new maximum
+    __half * Vs = (__half *) (fa_smem + ((64 + 2 * max_kv + (max_kv + 31) / 32 + 3) & ~3));   // [3][FA_DEC_CHUNK][64], 16-byte aligned
+    __half * Ks = Vs + 3 * FA_DEC_CHUNK * 64;                                                 // [3][FA_DEC_CHUNK][64], swizzled pieces
+    __shared__ float s_tot[2];             // maxima of the two scorer warps over the chunk in hand
+    __shared__ uint64_t s_exp_tab[32];
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int64_t h = blockIdx.x;
+    const int64_t nbk1 = rows.nbk1, nbv1 = rows.nbv1;
+    const float scale = rows.scale;
+    chain_wait();                          // Q, and for self-attention the newest K/V rows, come from the kernels before this one
+
+    if (tid < 64) Qs[tid] = round_f16(*(const float *) (R.q + h * rows.nbq2 + tid * 4));
+    if (tid >= 96) s_exp_tab[tid - 96] = c_exp2f_tab[tid - 96];
+    for (int g = tid; g < (max_kv + 7) / 8; g += FA_DEC_THREADS) evt[g] = 0;
+
+    const char * kh = R.k + h * rows.nbk2;
+    const char * vh = R.v + h * rows.nbv2;
+    const __half * mp = (const __half *) R.mask;
+    const int n_chunks = (n_kv + FA_DEC_CHUNK - 1) / FA_DEC_CHUNK;
+
+    auto fetch_k = [&](int c) {            // chunk c of K, pieces XOR-swizzled by the key index; nothing beyond the last chunk
+        const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
+        const unsigned base = (unsigned) __cvta_generic_to_shared(Ks + (size_t) (c % 3) * FA_DEC_CHUNK * 64);
+        for (int t = tid; t < kn * 8; t += FA_DEC_THREADS) {
+            const int key = t >> 3, pc = t & 7;
+            const char * src = kh + (int64_t) (k0 + key) * nbk1 + pc * 16;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(base + key * 128 + ((pc ^ (key & 7)) << 4)), "l"(src) : "memory");
+        }
+    };
+    auto fetch_v = [&](int c) {
+        const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
+        const unsigned base = (unsigned) __cvta_generic_to_shared(Vs + (size_t) (c % 3) * FA_DEC_CHUNK * 64);
+        for (int t = tid; t < kn * 8; t += FA_DEC_THREADS) {
+            const char * src = vh + (int64_t) (k0 + (t >> 3)) * nbv1 + (t & 7) * 16;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(base + t * 16), "l"(src) : "memory");
+        }
+    };
+
+    float m_carry = -INFINITY;             // scorer threads: maximum over all earlier chunks
+    auto score_chunk = [&](int c) {        // the 64 threads of warps 2..3; thread j scores key k0 + j
+        const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
+        const int j = tid - 64, ic = k0 + j;
+        float s = -INFINITY;
+        bool skip = true;
+        if (j < kn) {
+            float mv = 0.0f;
+            if (mp) mv = __half2float(mp[ic]);
+            skip = (mv == -INFINITY);
+            if (!skip) {
+                float acc[32];
+                const char * krow = (const char *) (Ks + (size_t) (c % 3) * FA_DEC_CHUNK * 64) + j * 128;
+#pragma unroll
+                for (int step = 0; step < 2; ++step) {
+#pragma unroll
+                    for (int cc = 0; cc < 4; ++cc) {
+                        const uint4 kv = *(const uint4 *) (krow + (((step * 4 + cc) ^ (j & 7)) << 4));
+                        const float4 qa = *(const float4 *) &Qs[step * 32 + cc * 8];
+                        const float4 qb = *(const float4 *) &Qs[step * 32 + cc * 8 + 4];
+                        const float2 k0v = __half22float2(*(const __half2 *) &kv.x);
+                        const float2 k1v = __half22float2(*(const __half2 *) &kv.y);
+                        const float2 k2v = __half22float2(*(const __half2 *) &kv.z);
+                        const float2 k3v = __half22float2(*(const __half2 *) &kv.w);
+                        float * a = &acc[cc * 8];
+                        if (step == 0) {
+                            a[0] = __fmaf_rn(k0v.x, qa.x, 0.0f); a[1] = __fmaf_rn(k0v.y, qa.y, 0.0f);
+                            a[2] = __fmaf_rn(k1v.x, qa.z, 0.0f); a[3] = __fmaf_rn(k1v.y, qa.w, 0.0f);
+                            a[4] = __fmaf_rn(k2v.x, qb.x, 0.0f); a[5] = __fmaf_rn(k2v.y, qb.y, 0.0f);
+                            a[6] = __fmaf_rn(k3v.x, qb.z, 0.0f); a[7] = __fmaf_rn(k3v.y, qb.w, 0.0f);
+                        } else {
+                            a[0] = __fmaf_rn(k0v.x, qa.x, a[0]); a[1] = __fmaf_rn(k0v.y, qa.y, a[1]);
+                            a[2] = __fmaf_rn(k1v.x, qa.z, a[2]); a[3] = __fmaf_rn(k1v.y, qa.w, a[3]);
+                            a[4] = __fmaf_rn(k2v.x, qb.x, a[4]); a[5] = __fmaf_rn(k2v.y, qb.y, a[5]);
+                            a[6] = __fmaf_rn(k3v.x, qb.z, a[6]); a[7] = __fmaf_rn(k3v.y, qb.w, a[7]);
+                        }
+                    }
+                }
+                float y[8];
+#pragma unroll
+                for (int pp = 0; pp < 8; ++pp)
+                    y[pp] = __fadd_rn(__fadd_rn(acc[pp], acc[16 + pp]), __fadd_rn(acc[8 + pp], acc[24 + pp]));
+                const float t0 = __fadd_rn(y[0], y[4]), t1 = __fadd_rn(y[1], y[5]);
+                const float t2 = __fadd_rn(y[2], y[6]), t3 = __fadd_rn(y[3], y[7]);
+                s = __fadd_rn(__fadd_rn(t0, t1), __fadd_rn(t2, t3));
+                s = __fmul_rn(s, scale);
+                s = __fadd_rn(s, mv);
+            }
+        }
+        // running maximum met by each key: earlier chunks (m_carry), warp 2's keys for warp 3, earlier lanes of the own warp
+        float pm = s;                      // -inf for skipped keys and beyond the end
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float tt = __shfl_up_sync(0xffffffffu, pm, o);
+            if (lane >= o) pm = fmaxf(pm, tt);
+        }
+        float ex = __shfl_up_sync(0xffffffffu, pm, 1);
+        if (lane == 0) ex = -INFINITY;
+        if (lane == 31) s_tot[(tid >> 5) - 2] = pm;
+        asm volatile("bar.sync 1, 64;" ::: "memory");               // the two scorer warps only
+        const float tot2 = s_tot[0], tot3 = s_tot[1];
+        float m_before = fmaxf(m_carry, ex);
+        if (tid >= 96) m_before = fmaxf(m_before, tot2);
+        if (j < kn) {
+            if (skip)              { msv[ic] = 1.0f; sc[ic] = -0.0f; }                  // skipped: ms = 1, vs = -0
+            else if (s > m_before) { msv[ic] = expf_glibc(__fadd_rn(m_before, -s), s_exp_tab); sc[ic] = 1.0f; evt[ic >> 3] = 1; }
+            else                   { msv[ic] = 1.0f; sc[ic] = expf_glibc(__fadd_rn(s, -m_before), s_exp_tab); }
+        }
+        m_carry = fmaxf(m_carry, fmaxf(tot2, tot3));
+    };
+
+    // copy groups: P0 = {K0, V0}, P1 = {K1, V1, K2}, then group c = {V(c+2), K(c+3)} committed in iteration c
+    fetch_k(0); fetch_v(0);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    fetch_k(1); fetch_v(1); fetch_k(2);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    __syncthreads();                       // K0 has landed; Qs, the table and the cleared flags are visible
+    if (tid >= 64) score_chunk(0);
+
+    float a = 0.0f, S = 0.0f;
+    for (int c = 0; c < n_chunks; ++c) {
+        const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
+        // V(c) and K(c+1) have landed when at most the newest group is pending (everything for c == 0)
+        if (c == 0) asm volatile("cp.async.wait_group 0;" ::: "memory");
+        else        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();                   // scores of chunk c are written; chunk c-1 is consumed (its V stage and K(c)'s stage are free)
+        fetch_v(c + 2); fetch_k(c + 3);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (tid >= 64) {
+            if (c + 1 < n_chunks) score_chunk(c + 1);
+        } else {
+            const __half * vb = Vs + (size_t) (c % 3) * FA_DEC_CHUNK * 64 + tid;
+            int i = 0;
+            // a full chunk without a new maximum: one straight-line block of 64 dependent steps (see the kernel above)
+            if (kn == FA_DEC_CHUNK && *(const unsigned long long *) &evt[k0 >> 3] == 0ull) {
+#pragma unroll
+                for (int u = 0; u < FA_DEC_CHUNK; ++u) {
+                    const float vsu = sc[k0 + u];
+                    float vvu = __half2float(vb[u * 64]);
+                    if (__float_as_uint(vsu) == 0x80000000u) vvu = 0.0f;             // skipped key: exact no-op whatever V holds
+                    a = round_f16(__fmaf_rn(vvu, vsu, a));
+                    S = __fadd_rn(S, vsu);                                          // ms == 1: fma(S, 1, vs) and S*1 + vs are both S + vs
+                }
+                i = FA_DEC_CHUNK;
+            }
+            for (; i < kn; ++i) {
+                const float ms = msv[k0 + i], vs1 = sc[k0 + i];
+                float vv1 = __half2float(vb[i * 64]);
+                if (__float_as_uint(vs1) == 0x80000000u) vv1 = 0.0f;
+                if (ms != 1.0f) a = round_f16(__fmul_rn(a, ms));
+                a = round_f16(__fmaf_rn(vv1, vs1, a));
+                S = S_FMA ? __fmaf_rn(S, ms, vs1) : __fadd_rn(__fmul_rn(S, ms), vs1);
+            }
+        }
+    }
+    if (tid < 64) {
+        const float o = __fmul_rn(a, __fdiv_rn(1.0f, S));
+        R.dst[h * 64 + tid] = o;
+        if (xq != nullptr) {               // second output, as in the kernel above
+            float amax = fabsf(o);
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+            const float id = (amax != 0.0f) ? __fdiv_rn(127.f, amax) : 0.0f;
+            const size_t kk = (size_t) gridDim.x * 64;
+            xq[blockIdx.y * kk + h * 64 + tid] = (int8_t) __float2int_rn(__fmul_rn(o, id));
+            if ((tid & 31) == 0) xd[blockIdx.y * (kk >> 5) + h * 2 + (tid >> 5)] = round_f16(__fdiv_rn(amax, 127.f));
+        }
+    }
+}
+
 static size_t fa_dec_smem(int max_kv, int stages) {
     return (size_t) ((64 + 2 * max_kv + (max_kv + 31) / 32 + 3) & ~3) * sizeof(float) + (size_t) stages * FA_DEC_CHUNK * 64 * sizeof(__half);
 }
@@ -559,9 +742,18 @@ static int launch_fa_decode(const FaRows & rows, int n_rows, int64_t n_head, int
     if (dev >= 0 && dev < 64 && !attr_done[dev]) {
         cudaFuncSetAttribute(k_flash_attn_decode<true, 3>,  cudaFuncAttributeMaxDynamicSharedMemorySize, (int) fa_dec_smem(FA_DEC_MAX_KV, 3));
         cudaFuncSetAttribute(k_flash_attn_decode<false, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) fa_dec_smem(FA_DEC_MAX_KV, 3));
+        cudaFuncSetAttribute(k_flash_attn_decode_stream<true>,  cudaFuncAttributeMaxDynamicSharedMemorySize, (int) fa_dec_smem(FA_DEC_MAX_KV, 6));
+        cudaFuncSetAttribute(k_flash_attn_decode_stream<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) fa_dec_smem(FA_DEC_MAX_KV, 6));
         attr_done[dev] = true;
     }
     dim3 grid((unsigned) n_head, (unsigned) n_rows);
+    // the streaming kernel needs two rings (six chunk buffers): three CTAs per SM; larger launches keep to the small one
+    static const bool no_stream = getenv("B200_FA_NO_STREAM") != nullptr;
+    if (!no_stream && (int64_t) n_head * n_rows <= 3 * 148) {
+        if (g_fa_s_fma) launch_chained(k_flash_attn_decode_stream<true>,  grid, dim3(FA_DEC_THREADS), fa_dec_smem(max_kv, 6), st, rows, max_kv, xq, xd);
+        else            launch_chained(k_flash_attn_decode_stream<false>, grid, dim3(FA_DEC_THREADS), fa_dec_smem(max_kv, 6), st, rows, max_kv, xq, xd);
+        B200_RETURN_LAST();
+    }
     if (g_fa_s_fma) launch_chained(k_flash_attn_decode<true, 3>,  grid, dim3(FA_DEC_THREADS), fa_dec_smem(max_kv, 3), st, rows, max_kv, xq, xd);
     else            launch_chained(k_flash_attn_decode<false, 3>, grid, dim3(FA_DEC_THREADS), fa_dec_smem(max_kv, 3), st, rows, max_kv, xq, xd);
     B200_RETURN_LAST();
