@@ -110,6 +110,13 @@ int b200_mul_mat_cols_q(int wtype, const void * w_planes, int64_t nb_total, int6
                         const int8_t * xq, const float * xd, const b200_gemv_col * cols, int n_cols,
                         const b200_gemv_ep * ep, void * stream);
 
+/* Up to three b200_mul_mat_cols_q products on the SAME quantised columns in one launch (the Q, K and V projections of
+ * a decoder layer): job i has its own weights (w_planes[i], nb_total[i], M[i] rows; all jobs share K and the type), its own
+ * outputs cols[i][0..n_cols) and its own epilogue ep[i] (ep or ep[i] may be NULL).  No counterpart in the reference. */
+int b200_mul_mat_cols_q_multi(int wtype, int n_jobs, const void * const * w_planes, const int64_t * nb_total, const int64_t * M,
+                              int64_t K, const int8_t * xq, const float * xd, const b200_gemv_col * const * cols, int n_cols,
+                              const b200_gemv_ep * const * ep, void * stream);
+
 /* The same product (ggml_compute_forward_mul_mat with ggml_vec_dot_q5_0_q8_0 / ggml_vec_dot_q8_0_q8_0, same bits)
  * for many columns on the tensor pipe.  The integer lane sums of the AVX2 dot product are exact in an f16 MMA with
  * f32 accumulation, the per-block float chain is replayed as in b200_mul_mat_q.  Operands are repacked once:

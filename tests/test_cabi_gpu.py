@@ -293,6 +293,48 @@ def test_mul_mat_cols_q_scattered_columns(K, pkg, wtype, Kd, M, N):
         assert bits_equal(outs[:, 1].cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("wtype", [6, 8])
+@pytest.mark.parametrize("Kd,Ms,N", [(1280, (200, 200, 200), 16), (384, (96, 130, 64), 7), (512, (70, 33), 32)])
+def test_mul_mat_cols_q_multi_shared_columns(K, pkg, wtype, Kd, Ms, N):
+    """Several weight matrices on the same quantised columns in one launch (Q, K, V of a decoder layer): every job has its
+    own outputs and epilogue (f32 + bias, f16 store, plain f32) and must equal the single-product entry point."""
+    x = rnd(41, N, Kd)
+    dx = dev(x)
+
+    class Col(C.Structure):
+        _fields_ = [("x", vp), ("dst", vp), ("add", vp * 4)]
+
+    class Ep(C.Structure):
+        _fields_ = [("n_steps", C.c_int), ("kind", C.c_int * 4), ("scalar", C.c_float * 4), ("store_f16", C.c_int)]
+
+    xs = (vp * N)(*[dx[n].data_ptr() for n in range(N)])
+    xq, xd = torch.empty((N, Kd), dtype=torch.int8, device="cuda"), torch.empty((N, Kd // 32), device="cuda")
+    sync_ok(K.b200_quantize_cols(xs, N, i64(Kd), ptr(xq), ptr(xd), None))
+    nj = len(Ms)
+    eps = [Ep(1, (C.c_int * 4)(1, 0, 0, 0), (C.c_float * 4)(0, 0, 0, 0), 0), Ep(0, (C.c_int * 4)(), (C.c_float * 4)(), 1),
+           Ep(1, (C.c_int * 4)(2, 0, 0, 0), (C.c_float * 4)(0.25, 0, 0, 0), 0)][:nj]
+    keep, cols_l, planes_l, nbs, single = [], [], [], [], []
+    for i, M in enumerate(Ms):
+        blocks, planes, nb = planes_of(K, pkg, wtype, rnd(50 + i, M, Kd, scale=0.02))
+        d_planes, bias = dev(planes), dev(rnd(60 + i, M))
+        out_multi = torch.zeros((N, M), dtype=torch.float16 if eps[i].store_f16 else torch.float32, device="cuda")
+        out_single = torch.zeros_like(out_multi)
+        cm, cs = (Col * N)(), (Col * N)()
+        for n in range(N):
+            cm[n].dst, cs[n].dst = out_multi[n].data_ptr(), out_single[n].data_ptr()
+            cm[n].add[0] = cs[n].add[0] = bias.data_ptr()
+        sync_ok(K.b200_mul_mat_cols_q(wtype, ptr(d_planes), i64(nb), i64(M), i64(Kd), ptr(xq), ptr(xd), cs, N, C.byref(eps[i]), None))
+        keep += [d_planes, bias, out_multi, out_single, cm, cs]
+        cols_l.append(cm); planes_l.append(d_planes); nbs.append(nb); single.append((out_multi, out_single))
+    wp = (vp * nj)(*[t.data_ptr() for t in planes_l])
+    colp = (C.POINTER(Col) * nj)(*[C.cast(c, C.POINTER(Col)) for c in cols_l])
+    epp = (C.POINTER(Ep) * nj)(*[C.pointer(e) for e in eps])
+    sync_ok(K.b200_mul_mat_cols_q_multi(wtype, nj, wp, (i64 * nj)(*nbs), (i64 * nj)(*Ms), i64(Kd), ptr(xq), ptr(xd), colp, N, epp, None))
+    for i, (a, b) in enumerate(single):
+        assert bits_equal(a.cpu().numpy(), b.cpu().numpy()), f"job {i}"
+        assert np.abs(b.float().cpu().numpy()).max() > 0
+
+
 def test_decode_rows_attention_and_layer_norm_rows(K):
     """Row-descriptor entry points: every row has its own buffers and key count."""
     H, d = 3, 192

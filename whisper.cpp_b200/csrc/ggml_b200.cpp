@@ -943,6 +943,73 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
     }
 }
 
+// Consecutive products on the same activation columns (the Q, K and V projections of a decoder layer, for 5..32 columns
+// of states that step together) as ONE launch.  Returns -1 when the items do not qualify; the caller then runs them one
+// by one.  Columns, outputs and epilogue operands are gathered exactly as run_item does for a single product.
+static int run_gemv_group(b200_backend_ctx * ctx, const plan_item * its, int n_items, struct ggml_cgraph * const * gs, int n_g) {
+    if (n_items < 2 || n_items > 3) return -1;
+    void * st = (void *) ctx->stream;
+    const struct ggml_tensor * w0 = ggml_graph_node(gs[0], its[0].node)->src[0];
+    const int64_t K = w0->ne[0];
+    if (K > COLQ_MAX_K) return -1;
+    b200_gemv_col cols[3][32];
+    b200_gemv_ep  eps[3];
+    const float * xs[32];
+    const void *  wp[3];
+    int64_t       nbt[3], Ms[3];
+    int n_cols = 0;
+    for (int i = 0; i < n_items; ++i) {
+        const plan_item & it = its[i];
+        struct ggml_tensor * n0 = ggml_graph_node(gs[0], it.node);
+        const struct ggml_tensor * w = n0->src[0];
+        if (it.kind != PK_GEMV || w->type != w0->type || w->ne[0] != K || w->ne[1] >= 16384) return -1;
+        wp[i] = w->data; Ms[i] = w->ne[1];
+        nbt[i] = (int64_t) (ggml_nbytes(w) / ggml_type_size(w->type));
+        memset(&eps[i], 0, sizeof(eps[i]));
+        eps[i].n_steps = it.n_steps; eps[i].store_f16 = it.store_f16;
+        for (int s = 0; s < it.n_steps; ++s) {
+            eps[i].kind[s] = it.step_kind[s];
+            if (it.step_kind[s] == B200_EP_SCALE) memcpy(&eps[i].scalar[s], ggml_graph_node(gs[0], it.step_node[s])->op_params, sizeof(float));
+        }
+        int nc = 0;
+        for (int g = 0; g < n_g; ++g) {
+            struct ggml_tensor * mm = ggml_graph_node(gs[g], it.node), * out = ggml_graph_node(gs[g], it.last);
+            if (mm->src[0]->data != w->data) return -1;                 // a state of another model: not here
+            const struct ggml_tensor * x = mm->src[1];
+            const int64_t out_stride = it.store_f16 ? mm->ne[0] * 2 : (int64_t) out->nb[1];
+            for (int64_t c = 0; c < x->ne[1]; ++c) {
+                if (nc == 32) return -1;
+                b200_gemv_col & col = cols[i][nc];
+                memset(&col, 0, sizeof(col));
+                col.x = (const float *) ((const char *) x->data + c * x->nb[1]);
+                if (i == 0) xs[nc] = col.x; else if (xs[nc] != col.x) return -1;      // all products read the same columns
+                col.dst = (char *) out->data + c * out_stride;
+                for (int s = 0; s < it.n_steps; ++s) {
+                    if (it.step_kind[s] != B200_EP_ADD) continue;
+                    const struct ggml_tensor * o = ggml_graph_node(gs[g], it.step_node[s])->src[it.step_src[s]];
+                    col.add[s] = (const float *) ((const char *) o->data + (o->ne[1] == 1 ? 0 : c * o->nb[1]));
+                }
+                ++nc;
+            }
+        }
+        if (i == 0) n_cols = nc; else if (nc != n_cols) return -1;
+    }
+    if (n_cols <= 4) return -1;
+    int8_t * xq = (int8_t *) ctx->colq;
+    float *  xd = (float *) ((char *) ctx->colq + (size_t) 32 * COLQ_MAX_K);
+    const bool reuse = ctx->colq_seq + 1 == ctx->item_seq && ctx->colq_K == K && (int) ctx->colq_ptrs.size() == n_cols &&
+                       memcmp(ctx->colq_ptrs.data(), xs, sizeof(xs[0]) * n_cols) == 0;
+    if (!reuse) {
+        const int e = b200_quantize_cols(xs, n_cols, K, xq, xd, st);
+        if (e) return e;
+        ctx->colq_ptrs.assign(xs, xs + n_cols);
+        ctx->colq_K = K;
+    }
+    const b200_gemv_col * colp[3] = { cols[0], cols[1], cols[2] };
+    const b200_gemv_ep *  epp[3]  = { &eps[0], &eps[1], &eps[2] };
+    return b200_mul_mat_cols_q_multi((int) w0->type, n_items, wp, nbt, Ms, K, xq, xd, colp, n_cols, epp, st);
+}
+
 static bool is_noop(enum ggml_op op) {
     return op == GGML_OP_NONE || op == GGML_OP_RESHAPE || op == GGML_OP_VIEW || op == GGML_OP_PERMUTE || op == GGML_OP_TRANSPOSE;
 }
@@ -954,9 +1021,28 @@ static int run_plan(b200_backend_ctx * ctx, const exec_plan & plan, struct ggml_
         return ctx->events[(*n_ev)++];
     };
     ctx->colq_seq = -2;                      // activations of an earlier graph never carry over
-    for (const plan_item & it : plan.items) {
+    static const bool group_gemv = getenv("GGML_B200_NO_FUSION") == nullptr && getenv("GGML_B200_NO_QKV_GROUP") == nullptr;
+    for (size_t ii = 0; ii < plan.items.size(); ++ii) {
+        const plan_item & it = plan.items[ii];
         // views do nothing and do not separate a producer of quantised columns from the product that reuses them
         if (!(it.kind == PK_NODE && is_noop(ggml_graph_node(gs[0], it.node)->op))) ctx->item_seq++;
+        if (group_gemv && !timing && it.kind == PK_GEMV && ii + 1 < plan.items.size() && plan.items[ii + 1].kind == PK_GEMV) {
+            // products that follow each other on the same activations (Q, K, V): one launch
+            const void * x0 = ggml_graph_node(gs[0], it.node)->src[1]->data;
+            int n_items = 1;
+            while (n_items < 3 && ii + n_items < plan.items.size() && plan.items[ii + n_items].kind == PK_GEMV &&
+                   ggml_graph_node(gs[0], plan.items[ii + n_items].node)->src[1]->data == x0) ++n_items;
+            if (n_items >= 2) {
+                const int e = run_gemv_group(ctx, &plan.items[ii], n_items, gs, n_g);
+                if (e > 0) return e;
+                if (e == 0) {
+                    ctx->item_seq += n_items - 1;
+                    ctx->colq_seq = ctx->item_seq;          // the columns stay valid for a product that follows immediately
+                    ii += n_items - 1;
+                    continue;
+                }
+            }
+        }
         if (timing) {
             double work = 0;
             struct ggml_tensor * node = ggml_graph_node(gs[0], it.node);

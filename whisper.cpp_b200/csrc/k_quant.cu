@@ -904,9 +904,8 @@ __device__ __forceinline__ void ep_store32(const GemvEp & ep, const GemvCols32 &
 }
 
 template <int TYPE, int R, int CT>
-__global__ void __launch_bounds__(256)
-k_gemv_skinny(QPlanes w, int64_t M, int nbk, const int8_t * __restrict__ xq, const float * __restrict__ xd, int n_cols,
-              GemvCols32 cols, GemvEp ep) {
+__device__ __forceinline__ void gemv_skinny_body(const QPlanes & w, int64_t M, int nbk, const int8_t * __restrict__ xq, const float * __restrict__ xd,
+                                                 int n_cols, const GemvCols32 & cols, const GemvEp & ep, int64_t row0) {
     extern __shared__ __align__(16) unsigned char sk_smem[];
     constexpr int CG = 32 / R;
     const int RS   = nbk * 8 + ((8 - (nbk * 8) % 32 + 32) % 32);      // row stride in words, == 8 mod 32
@@ -916,7 +915,6 @@ k_gemv_skinny(QPlanes w, int64_t M, int nbk, const int8_t * __restrict__ xq, con
     float * dW  = (float *) (Xsm + n_cols * XS);                      // [R][nbk]
     float * dX  = dW + R * nbk;                                       // [n_cols][nbk]
     const int tid = threadIdx.x;
-    const int64_t row0 = (int64_t) blockIdx.x * R;
     chain_release();
 
     for (int it = tid; it < R * nbk; it += 256) {                     // weight rows: one (row, block) per thread and pass
@@ -988,6 +986,44 @@ k_gemv_skinny(QPlanes w, int64_t M, int nbk, const int8_t * __restrict__ xq, con
 #pragma unroll
         for (int c = 0; c < CT; ++c) if (c0 + c < n_cols) ep_store32(ep, cols, c0 + c, m, acc[c]);
     }
+}
+
+template <int TYPE, int R, int CT>
+__global__ void __launch_bounds__(256)
+k_gemv_skinny(QPlanes w, int64_t M, int nbk, const int8_t * __restrict__ xq, const float * __restrict__ xd, int n_cols,
+              GemvCols32 cols, GemvEp ep) {
+    gemv_skinny_body<TYPE, R, CT>(w, M, nbk, xq, xd, n_cols, cols, ep, (int64_t) blockIdx.x * R);
+}
+
+// Up to three products that share their activation columns (the Q, K and V projections of a layer) in one launch:
+// blockIdx.y selects the weight matrix with its own outputs and epilogue.
+struct SkinnyJob { QPlanes w; int64_t M; GemvCols32 cols; GemvEp ep; };
+struct SkinnyJobs { SkinnyJob j[3]; };
+template <int TYPE, int R, int CT>
+__global__ void __launch_bounds__(256)
+k_gemv_skinny_multi(const __grid_constant__ SkinnyJobs jobs, int nbk, const int8_t * __restrict__ xq, const float * __restrict__ xd, int n_cols) {
+    const SkinnyJob & J = jobs.j[blockIdx.y];
+    const int64_t row0 = (int64_t) blockIdx.x * R;
+    if (row0 >= J.M) return;
+    gemv_skinny_body<TYPE, R, CT>(J.w, J.M, nbk, xq, xd, n_cols, J.cols, J.ep, row0);
+}
+
+template <int TYPE, int R, int CT>
+static int launch_skinny_multi(const SkinnyJobs & jobs, int n_jobs, int nbk, const int8_t * xq, const float * xd, int n_cols, cudaStream_t st) {
+    const int RS = nbk * 8 + ((8 - (nbk * 8) % 32 + 32) % 32);
+    const size_t smem = ((size_t) R * RS + (size_t) n_cols * nbk * 8 + (size_t) R * nbk + (size_t) n_cols * nbk) * 4;
+    if (smem > 220 * 1024) return B200_ERR_ARG;
+    static bool attr_done[64] = {false};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+        cudaFuncSetAttribute(k_gemv_skinny_multi<TYPE, R, CT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+        attr_done[dev] = true;
+    }
+    int64_t max_m = 0;
+    for (int i = 0; i < n_jobs; ++i) max_m = jobs.j[i].M > max_m ? jobs.j[i].M : max_m;
+    launch_chained(k_gemv_skinny_multi<TYPE, R, CT>, dim3((unsigned) ((max_m + R - 1) / R), (unsigned) n_jobs), dim3(256), smem, st, jobs, nbk, xq, xd, n_cols);
+    B200_RETURN_LAST();
 }
 
 template <int TYPE, int R, int CT>
@@ -1194,6 +1230,45 @@ extern "C" int b200_mul_mat_cols_q(int wtype, const void * w_planes, int64_t nb_
     if (wtype == B200_TYPE_Q8_0) return launch_skinny_n<B200_TYPE_Q8_0>(w, M, (int) nbk, xq, xd, n_cols, c, e, as_stream(stream));
     return B200_ERR_ARG;
 }
+
+extern "C" int b200_mul_mat_cols_q_multi(int wtype, int n_jobs, const void * const * w_planes, const int64_t * nb_total, const int64_t * M,
+                                         int64_t K, const int8_t * xq, const float * xd, const b200_gemv_col * const * cols, int n_cols,
+                                         const b200_gemv_ep * const * ep, void * stream) {
+    if (n_jobs < 1 || n_jobs > 3 || K % 32 != 0 || n_cols < 1 || n_cols > 32 || !cols || !w_planes || !nb_total || !M) return B200_ERR_ARG;
+    if (((uintptr_t) xq & 15) != 0) return B200_ERR_ARG;
+    const int64_t nbk = K / 32;
+    static const int   no_kind[4]   = {0, 0, 0, 0};
+    static const float no_scalar[4] = {0, 0, 0, 0};
+    SkinnyJobs jobs;
+    memset(&jobs, 0, sizeof(jobs));
+    for (int i = 0; i < n_jobs; ++i) {
+        if (!w_planes[i] || ((uintptr_t) w_planes[i] & 15) != 0 || M[i] <= 0 || M[i] * nbk > nb_total[i] || !cols[i]) return B200_ERR_ARG;
+        SkinnyJob & J = jobs.j[i];
+        const b200_gemv_ep * e = ep ? ep[i] : nullptr;
+        const int rc = e ? fill_ep(J.ep, e->n_steps, e->kind, e->scalar, e->store_f16) : fill_ep(J.ep, 0, no_kind, no_scalar, 0);
+        if (rc) return rc;
+        for (int n = 0; n < n_cols; ++n) {
+            if (!cols[i][n].dst) return B200_ERR_ARG;
+            J.cols.dst[n] = cols[i][n].dst;
+            for (int st = 0; st < J.ep.n_steps; ++st) {
+                J.cols.add[st][n] = cols[i][n].add[st];
+                if (J.ep.kind[st] == B200_EP_ADD && !J.cols.add[st][n]) return B200_ERR_ARG;
+            }
+        }
+        J.w = q_planes(wtype, w_planes[i], nb_total[i]);
+        J.M = M[i];
+    }
+    cudaStream_t st = as_stream(stream);
+#define B200_MULTI(T) \
+    (n_cols <= 8 ? launch_skinny_multi<T, 8, 2>(jobs, n_jobs, (int) nbk, xq, xd, n_cols, st) : \
+     n_cols <= 16 ? launch_skinny_multi<T, 8, 4>(jobs, n_jobs, (int) nbk, xq, xd, n_cols, st) : \
+                    launch_skinny_multi<T, 8, 8>(jobs, n_jobs, (int) nbk, xq, xd, n_cols, st))
+    if (wtype == B200_TYPE_Q5_0) return B200_MULTI(B200_TYPE_Q5_0);
+    if (wtype == B200_TYPE_Q8_0) return B200_MULTI(B200_TYPE_Q8_0);
+#undef B200_MULTI
+    return B200_ERR_ARG;
+}
+
 
 // ------------------------------------------------------------------------------------------------
 // Product with the activation scratch in a fixed device array (for callers that cannot allocate).
