@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Throughput benchmark of the whisper.cpp hot path on the B200 ggml backend plugin.
 
-Workload (BASELINE.json configs[3]): Whisper large-v3, Q5_0 weights (random init, quantised by the rules of
+Workload: Whisper large-v3, Q5_0 weights (random init, quantised by the rules of
 the reference tool), a batch of 64 seeded 30 s clips, each: log-mel -> encoder -> greedy decode of 224 tokens
 after the forced prefix [SOT, en, transcribe, notimestamps], driven through the unmodified whisper.h API
 (whisper_set_mel / whisper_encode / whisper_decode).  The batch is split evenly over the ranks (one rank per
