@@ -580,7 +580,7 @@ k_flash_attn_decode_stream(FaRows rows, int max_kv, int8_t * __restrict__ xq, fl
     auto fetch_k = [&](int c) {            // chunk c of K, pieces XOR-swizzled by the key index; nothing beyond the last chunk
         const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
         const unsigned base = (unsigned) __cvta_generic_to_shared(Ks + (size_t) (c % 3) * FA_DEC_CHUNK * 64);
-        for (int t = tid; t < kn * 8; t += FA_DEC_THREADS) {
+        for (int t = tid - 64; t < kn * 8; t += 64) {
             const int key = t >> 3, pc = t & 7;
             const char * src = kh + (int64_t) (k0 + key) * nbk1 + pc * 16;
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(base + key * 128 + ((pc ^ (key & 7)) << 4)), "l"(src) : "memory");
@@ -589,7 +589,7 @@ k_flash_attn_decode_stream(FaRows rows, int max_kv, int8_t * __restrict__ xq, fl
     auto fetch_v = [&](int c) {
         const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
         const unsigned base = (unsigned) __cvta_generic_to_shared(Vs + (size_t) (c % 3) * FA_DEC_CHUNK * 64);
-        for (int t = tid; t < kn * 8; t += FA_DEC_THREADS) {
+        for (int t = tid - 64; t < kn * 8; t += 64) {
             const char * src = vh + (int64_t) (k0 + (t >> 3)) * nbv1 + (t & 7) * 16;
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(base + t * 16), "l"(src) : "memory");
         }
@@ -666,12 +666,16 @@ k_flash_attn_decode_stream(FaRows rows, int max_kv, int8_t * __restrict__ xq, fl
         m_carry = fmaxf(m_carry, fmaxf(tot2, tot3));
     };
 
-    // copy groups: P0 = {K0, V0}, P1 = {K1, V1, K2}, then group c = {V(c+2), K(c+3)} committed in iteration c
-    fetch_k(0); fetch_v(0);
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    fetch_k(1); fetch_v(1); fetch_k(2);
-    asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 1;" ::: "memory");
+    // All copies are issued and awaited by the scorer warps (the chain warps do nothing but their chain); the CTA
+    // barrier that follows a wait publishes the data.  Copy groups: P0 = {K0, V0}, P1 = {K1, V1, K2}, then
+    // group c = {V(c+2), K(c+3)} committed in iteration c.
+    if (tid >= 64) {
+        fetch_k(0); fetch_v(0);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        fetch_k(1); fetch_v(1); fetch_k(2);
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+    }
     __syncthreads();                       // K0 has landed; Qs, the table and the cleared flags are visible
     if (tid >= 64) score_chunk(0);
 
@@ -679,12 +683,14 @@ k_flash_attn_decode_stream(FaRows rows, int max_kv, int8_t * __restrict__ xq, fl
     for (int c = 0; c < n_chunks; ++c) {
         const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
         // V(c) and K(c+1) have landed when at most the newest group is pending (everything for c == 0)
-        if (c == 0) asm volatile("cp.async.wait_group 0;" ::: "memory");
-        else        asm volatile("cp.async.wait_group 1;" ::: "memory");
-        __syncthreads();                   // scores of chunk c are written; chunk c-1 is consumed (its V stage and K(c)'s stage are free)
-        fetch_v(c + 2); fetch_k(c + 3);
-        asm volatile("cp.async.commit_group;" ::: "memory");
         if (tid >= 64) {
+            if (c == 0) asm volatile("cp.async.wait_group 0;" ::: "memory");
+            else        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        }
+        __syncthreads();                   // scores of chunk c are written; chunk c-1 is consumed (its V stage and K(c)'s stage are free)
+        if (tid >= 64) {
+            fetch_v(c + 2); fetch_k(c + 3);
+            asm volatile("cp.async.commit_group;" ::: "memory");
             if (c + 1 < n_chunks) score_chunk(c + 1);
         } else {
             const __half * vb = Vs + (size_t) (c % 3) * FA_DEC_CHUNK * 64 + tid;
@@ -700,6 +706,27 @@ k_flash_attn_decode_stream(FaRows rows, int max_kv, int8_t * __restrict__ xq, fl
                     S = __fadd_rn(S, vsu);                                          // ms == 1: fma(S, 1, vs) and S*1 + vs are both S + vs
                 }
                 i = FA_DEC_CHUNK;
+            }
+            for (; i + 8 <= kn; i += 8) {  // a chunk with new maxima (or the last, short one): groups of eight keys
+                float vs[8], vv[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    vs[u] = sc[k0 + i + u];
+                    vv[u] = __half2float(vb[(i + u) * 64]);
+                    if (__float_as_uint(vs[u]) == 0x80000000u) vv[u] = 0.0f;
+                }
+                if (!evt[(k0 + i) >> 3]) {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) { a = round_f16(__fmaf_rn(vv[u], vs[u], a)); S = __fadd_rn(S, vs[u]); }
+                } else {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const float ms = msv[k0 + i + u];
+                        if (ms != 1.0f) a = round_f16(__fmul_rn(a, ms));
+                        a = round_f16(__fmaf_rn(vv[u], vs[u], a));
+                        S = S_FMA ? __fmaf_rn(S, ms, vs[u]) : __fadd_rn(__fmul_rn(S, ms), vs[u]);
+                    }
+                }
             }
             for (; i < kn; ++i) {
                 const float ms = msv[k0 + i], vs1 = sc[k0 + i];
