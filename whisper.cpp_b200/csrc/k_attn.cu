@@ -544,10 +544,11 @@ k_flash_attn_decode(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * _
     }
 }
 
-// Streaming form of the kernel above for launches whose CTAs are all resident with the larger buffers: warps 2..3
-// score chunk c+1 (one key per thread, running maximum carried from chunk to chunk, exponentials) while warps 0..1
-// replay the F16 accumulation and the running sum over chunk c, so that the sequential chain is the only thing on
-// the critical path.  K and V arrive through separate three-stage rings of FA_DEC_CHUNK keys.
+// Streaming form of the kernel above for launches whose CTAs are all resident with the larger buffers.  Four warps,
+// four roles: warp 0 replays the F16 accumulation (two output dims per lane, so two independent chains fill each
+// other's latency) and the running sum over chunk c; warp 1 issues and awaits every cp.async; warps 2..3 score chunk
+// c+1 (one key per thread, running maximum carried from chunk to chunk, exponentials).  The sequential chain is the
+// only thing on the critical path.  K and V arrive through separate three-stage rings of FA_DEC_CHUNK keys.
 template <bool S_FMA>
 __global__ void __launch_bounds__(FA_DEC_THREADS)
 k_flash_attn_decode_stream(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * __restrict__ xd) {
@@ -562,7 +563,7 @@ k_flash_attn_decode_stream(FaRows rows, int max_kv, int8_t * __restrict__ xq, fl
     __half * Ks = Vs + 3 * FA_DEC_CHUNK * 64;                                                 // [3][FA_DEC_CHUNK][64], swizzled pieces
     __shared__ float s_tot[2];             // maxima of the two scorer warps over the chunk in hand
     __shared__ uint64_t s_exp_tab[32];
-    const int tid = threadIdx.x, lane = tid & 31;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t h = blockIdx.x;
     const int64_t nbk1 = rows.nbk1, nbv1 = rows.nbv1;
     const float scale = rows.scale;
@@ -577,26 +578,37 @@ k_flash_attn_decode_stream(FaRows rows, int max_kv, int8_t * __restrict__ xq, fl
     const __half * mp = (const __half *) R.mask;
     const int n_chunks = (n_kv + FA_DEC_CHUNK - 1) / FA_DEC_CHUNK;
 
-    auto fetch_k = [&](int c) {            // chunk c of K, pieces XOR-swizzled by the key index; nothing beyond the last chunk
+    // ---- warp 1: copies.  Lane l moves piece (l & 7) of keys (l >> 3) + 4 i, i = 0..15, of a chunk: source addresses
+    // advance by a constant per copy and per chunk, destinations are immediates (K pieces XOR-swizzled by the key).
+    const char * cp_k = kh + (int64_t) (lane >> 3) * nbk1 + (lane & 7) * 16;
+    const char * cp_v = vh + (int64_t) (lane >> 3) * nbv1 + (lane & 7) * 16;
+    const unsigned ks_u = (unsigned) __cvta_generic_to_shared(Ks), vs_u = (unsigned) __cvta_generic_to_shared(Vs);
+    auto fetch_k = [&](int c) {            // nothing beyond the last chunk
         const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
-        const unsigned base = (unsigned) __cvta_generic_to_shared(Ks + (size_t) (c % 3) * FA_DEC_CHUNK * 64);
-        for (int t = tid - 64; t < kn * 8; t += 64) {
-            const int key = t >> 3, pc = t & 7;
-            const char * src = kh + (int64_t) (k0 + key) * nbk1 + pc * 16;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(base + key * 128 + ((pc ^ (key & 7)) << 4)), "l"(src) : "memory");
+        const unsigned base = ks_u + (unsigned) (c % 3) * FA_DEC_CHUNK * 128;
+        const char * src = cp_k + (int64_t) k0 * nbk1;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int key = (lane >> 3) + 4 * i;
+            if (key < kn)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(base + key * 128 + (((lane & 7) ^ (key & 7)) << 4)), "l"(src + (int64_t) (4 * i) * nbk1) : "memory");
         }
     };
     auto fetch_v = [&](int c) {
         const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
-        const unsigned base = (unsigned) __cvta_generic_to_shared(Vs + (size_t) (c % 3) * FA_DEC_CHUNK * 64);
-        for (int t = tid - 64; t < kn * 8; t += 64) {
-            const char * src = vh + (int64_t) (k0 + (t >> 3)) * nbv1 + (t & 7) * 16;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(base + t * 16), "l"(src) : "memory");
+        const unsigned base = vs_u + (unsigned) (c % 3) * FA_DEC_CHUNK * 128;
+        const char * src = cp_v + (int64_t) k0 * nbv1;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int key = (lane >> 3) + 4 * i;
+            if (key < kn)
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(base + key * 128 + ((lane & 7) << 4)), "l"(src + (int64_t) (4 * i) * nbv1) : "memory");
         }
     };
 
-    float m_carry = -INFINITY;             // scorer threads: maximum over all earlier chunks
-    auto score_chunk = [&](int c) {        // the 64 threads of warps 2..3; thread j scores key k0 + j
+    // ---- warps 2..3: scores
+    float m_carry = -INFINITY;             // maximum over all earlier chunks
+    auto score_chunk = [&](int c) {        // thread j = tid - 64 scores key k0 + j
         const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
         const int j = tid - 64, ic = k0 + j;
         float s = -INFINITY;
@@ -653,11 +665,11 @@ k_flash_attn_decode_stream(FaRows rows, int max_kv, int8_t * __restrict__ xq, fl
         }
         float ex = __shfl_up_sync(0xffffffffu, pm, 1);
         if (lane == 0) ex = -INFINITY;
-        if (lane == 31) s_tot[(tid >> 5) - 2] = pm;
+        if (lane == 31) s_tot[warp - 2] = pm;
         asm volatile("bar.sync 1, 64;" ::: "memory");               // the two scorer warps only
         const float tot2 = s_tot[0], tot3 = s_tot[1];
         float m_before = fmaxf(m_carry, ex);
-        if (tid >= 96) m_before = fmaxf(m_before, tot2);
+        if (warp == 3) m_before = fmaxf(m_before, tot2);
         if (j < kn) {
             if (skip)              { msv[ic] = 1.0f; sc[ic] = -0.0f; }                  // skipped: ms = 1, vs = -0
             else if (s > m_before) { msv[ic] = expf_glibc(__fadd_rn(m_before, -s), s_exp_tab); sc[ic] = 1.0f; evt[ic >> 3] = 1; }
@@ -666,10 +678,9 @@ k_flash_attn_decode_stream(FaRows rows, int max_kv, int8_t * __restrict__ xq, fl
         m_carry = fmaxf(m_carry, fmaxf(tot2, tot3));
     };
 
-    // All copies are issued and awaited by the scorer warps (the chain warps do nothing but their chain); the CTA
-    // barrier that follows a wait publishes the data.  Copy groups: P0 = {K0, V0}, P1 = {K1, V1, K2}, then
-    // group c = {V(c+2), K(c+3)} committed in iteration c.
-    if (tid >= 64) {
+    // Copy groups (warp 1): P0 = {K0, V0}, P1 = {K1, V1, K2}, then group c = {V(c+2), K(c+3)} committed in iteration c.
+    // A wait by warp 1 followed by the CTA barrier publishes the data to the other warps.
+    if (warp == 1) {
         fetch_k(0); fetch_v(0);
         asm volatile("cp.async.commit_group;" ::: "memory");
         fetch_k(1); fetch_v(1); fetch_k(2);
@@ -677,78 +688,97 @@ k_flash_attn_decode_stream(FaRows rows, int max_kv, int8_t * __restrict__ xq, fl
         asm volatile("cp.async.wait_group 1;" ::: "memory");
     }
     __syncthreads();                       // K0 has landed; Qs, the table and the cleared flags are visible
-    if (tid >= 64) score_chunk(0);
+    if (warp >= 2) score_chunk(0);
 
-    float a = 0.0f, S = 0.0f;
+    float a0 = 0.0f, a1 = 0.0f, S = 0.0f;  // warp 0: dims 2*lane, 2*lane + 1
+#ifdef FA_DEC_PROFILE
+    long long p_wait = 0, p_work = 0, p_t0, p_t1, p_start = clock64();
+    const bool p_me = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0;
+#endif
     for (int c = 0; c < n_chunks; ++c) {
         const int k0 = c * FA_DEC_CHUNK, kn = min(FA_DEC_CHUNK, n_kv - k0);
-        // V(c) and K(c+1) have landed when at most the newest group is pending (everything for c == 0)
-        if (tid >= 64) {
+#ifdef FA_DEC_PROFILE
+        p_t0 = clock64();
+#endif
+        if (warp == 1) {                   // V(c) and K(c+1) have landed when at most the newest group is pending (all for c == 0)
             if (c == 0) asm volatile("cp.async.wait_group 0;" ::: "memory");
             else        asm volatile("cp.async.wait_group 1;" ::: "memory");
         }
         __syncthreads();                   // scores of chunk c are written; chunk c-1 is consumed (its V stage and K(c)'s stage are free)
-        if (tid >= 64) {
+#ifdef FA_DEC_PROFILE
+        p_t1 = clock64(); p_wait += p_t1 - p_t0;
+#endif
+        if (warp == 1) {
             fetch_v(c + 2); fetch_k(c + 3);
             asm volatile("cp.async.commit_group;" ::: "memory");
+        } else if (warp >= 2) {
             if (c + 1 < n_chunks) score_chunk(c + 1);
         } else {
-            const __half * vb = Vs + (size_t) (c % 3) * FA_DEC_CHUNK * 64 + tid;
+            const __half2 * vb = (const __half2 *) (Vs + (size_t) (c % 3) * FA_DEC_CHUNK * 64) + lane;      // key u: vb[u * 32]
+            auto step = [&](float vs, float ms, float2 v, bool rescale) {
+                if (__float_as_uint(vs) == 0x80000000u) { v.x = 0.0f; v.y = 0.0f; }      // skipped key: exact no-op whatever V holds
+                if (rescale && ms != 1.0f) {
+                    const float2 r = __half22float2(__floats2half2_rn(__fmul_rn(a0, ms), __fmul_rn(a1, ms)));
+                    a0 = r.x; a1 = r.y;
+                }
+                const float2 t = __half22float2(__floats2half2_rn(__fmaf_rn(v.x, vs, a0), __fmaf_rn(v.y, vs, a1)));
+                a0 = t.x; a1 = t.y;
+                if (rescale) S = S_FMA ? __fmaf_rn(S, ms, vs) : __fadd_rn(__fmul_rn(S, ms), vs);
+                else         S = __fadd_rn(S, vs);             // ms == 1: fma(S, 1, vs) and S*1 + vs are both S + vs
+            };
             int i = 0;
-            // a full chunk without a new maximum: one straight-line block of 64 dependent steps (see the kernel above)
+            // a full chunk without a new maximum: one straight-line block of 64 dependent steps, so that the loads and
+            // conversions of later keys are placed into the latency gaps of the two chains (a warp issues in order)
             if (kn == FA_DEC_CHUNK && *(const unsigned long long *) &evt[k0 >> 3] == 0ull) {
 #pragma unroll
-                for (int u = 0; u < FA_DEC_CHUNK; ++u) {
-                    const float vsu = sc[k0 + u];
-                    float vvu = __half2float(vb[u * 64]);
-                    if (__float_as_uint(vsu) == 0x80000000u) vvu = 0.0f;             // skipped key: exact no-op whatever V holds
-                    a = round_f16(__fmaf_rn(vvu, vsu, a));
-                    S = __fadd_rn(S, vsu);                                          // ms == 1: fma(S, 1, vs) and S*1 + vs are both S + vs
+                for (int u4 = 0; u4 < FA_DEC_CHUNK / 4; ++u4) {
+                    const float4 vs4 = *(const float4 *) &sc[k0 + u4 * 4];
+                    step(vs4.x, 1.0f, __half22float2(vb[(u4 * 4 + 0) * 32]), false);
+                    step(vs4.y, 1.0f, __half22float2(vb[(u4 * 4 + 1) * 32]), false);
+                    step(vs4.z, 1.0f, __half22float2(vb[(u4 * 4 + 2) * 32]), false);
+                    step(vs4.w, 1.0f, __half22float2(vb[(u4 * 4 + 3) * 32]), false);
                 }
                 i = FA_DEC_CHUNK;
             }
             for (; i + 8 <= kn; i += 8) {  // a chunk with new maxima (or the last, short one): groups of eight keys
-                float vs[8], vv[8];
+                float vs[8];
+                float2 vv[8];
 #pragma unroll
-                for (int u = 0; u < 8; ++u) {
-                    vs[u] = sc[k0 + i + u];
-                    vv[u] = __half2float(vb[(i + u) * 64]);
-                    if (__float_as_uint(vs[u]) == 0x80000000u) vv[u] = 0.0f;
-                }
+                for (int u = 0; u < 8; ++u) { vs[u] = sc[k0 + i + u]; vv[u] = __half22float2(vb[(i + u) * 32]); }
                 if (!evt[(k0 + i) >> 3]) {
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) { a = round_f16(__fmaf_rn(vv[u], vs[u], a)); S = __fadd_rn(S, vs[u]); }
+                    for (int u = 0; u < 8; ++u) step(vs[u], 1.0f, vv[u], false);
                 } else {
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        const float ms = msv[k0 + i + u];
-                        if (ms != 1.0f) a = round_f16(__fmul_rn(a, ms));
-                        a = round_f16(__fmaf_rn(vv[u], vs[u], a));
-                        S = S_FMA ? __fmaf_rn(S, ms, vs[u]) : __fadd_rn(__fmul_rn(S, ms), vs[u]);
-                    }
+                    for (int u = 0; u < 8; ++u) step(vs[u], msv[k0 + i + u], vv[u], true);
                 }
             }
-            for (; i < kn; ++i) {
-                const float ms = msv[k0 + i], vs1 = sc[k0 + i];
-                float vv1 = __half2float(vb[i * 64]);
-                if (__float_as_uint(vs1) == 0x80000000u) vv1 = 0.0f;
-                if (ms != 1.0f) a = round_f16(__fmul_rn(a, ms));
-                a = round_f16(__fmaf_rn(vv1, vs1, a));
-                S = S_FMA ? __fmaf_rn(S, ms, vs1) : __fadd_rn(__fmul_rn(S, ms), vs1);
-            }
+            for (; i < kn; ++i) step(sc[k0 + i], msv[k0 + i], __half22float2(vb[i * 32]), true);
         }
+#ifdef FA_DEC_PROFILE
+        p_work += clock64() - p_t1;
+#endif
     }
-    if (tid < 64) {
-        const float o = __fmul_rn(a, __fdiv_rn(1.0f, S));
-        R.dst[h * 64 + tid] = o;
-        if (xq != nullptr) {               // second output, as in the kernel above
-            float amax = fabsf(o);
+#ifdef FA_DEC_PROFILE
+    if (p_me && warp < 3) { g_fa_prof[warp * 2] = p_wait; g_fa_prof[warp * 2 + 1] = p_work; if (warp == 0) g_fa_prof[6] = clock64() - p_start; }
+#endif
+    if (warp == 0) {
+        const float S_inv = __fdiv_rn(1.0f, S);
+        float2 o;
+        o.x = __fmul_rn(a0, S_inv);
+        o.y = __fmul_rn(a1, S_inv);
+        *(float2 *) (R.dst + h * 64 + lane * 2) = o;
+        if (xq != nullptr) {               // second output, as in the kernel above: lanes 0..15 hold block 2h, lanes 16..31 block 2h+1
+            float amax = fmaxf(fabsf(o.x), fabsf(o.y));
 #pragma unroll
-            for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+            for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
             const float id = (amax != 0.0f) ? __fdiv_rn(127.f, amax) : 0.0f;
             const size_t kk = (size_t) gridDim.x * 64;
-            xq[blockIdx.y * kk + h * 64 + tid] = (int8_t) __float2int_rn(__fmul_rn(o, id));
-            if ((tid & 31) == 0) xd[blockIdx.y * (kk >> 5) + h * 2 + (tid >> 5)] = round_f16(__fdiv_rn(amax, 127.f));
+            char2 q;
+            q.x = (signed char) __float2int_rn(__fmul_rn(o.x, id));
+            q.y = (signed char) __float2int_rn(__fmul_rn(o.y, id));
+            *(char2 *) (xq + blockIdx.y * kk + h * 64 + lane * 2) = q;
+            if ((lane & 15) == 0) xd[blockIdx.y * (kk >> 5) + h * 2 + (lane >> 4)] = round_f16(__fdiv_rn(amax, 127.f));
         }
     }
 }
