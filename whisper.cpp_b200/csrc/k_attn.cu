@@ -730,13 +730,17 @@ k_flash_attn_decode_stream(FaRows rows, int max_kv, int8_t * __restrict__ xq, fl
             // a full chunk without a new maximum: one straight-line block of 64 dependent steps, so that the loads and
             // conversions of later keys are placed into the latency gaps of the two chains (a warp issues in order)
             if (kn == FA_DEC_CHUNK && *(const unsigned long long *) &evt[k0 >> 3] == 0ull) {
+                // blocks of 16 steps: long enough to hide the loads, short enough to stay in the instruction cache
+#pragma unroll 1
+                for (int ub = 0; ub < FA_DEC_CHUNK; ub += 16) {
 #pragma unroll
-                for (int u4 = 0; u4 < FA_DEC_CHUNK / 4; ++u4) {
-                    const float4 vs4 = *(const float4 *) &sc[k0 + u4 * 4];
-                    step(vs4.x, 1.0f, __half22float2(vb[(u4 * 4 + 0) * 32]), false);
-                    step(vs4.y, 1.0f, __half22float2(vb[(u4 * 4 + 1) * 32]), false);
-                    step(vs4.z, 1.0f, __half22float2(vb[(u4 * 4 + 2) * 32]), false);
-                    step(vs4.w, 1.0f, __half22float2(vb[(u4 * 4 + 3) * 32]), false);
+                    for (int u4 = 0; u4 < 4; ++u4) {
+                        const float4 vs4 = *(const float4 *) &sc[k0 + ub + u4 * 4];
+                        step(vs4.x, 1.0f, __half22float2(vb[(ub + u4 * 4 + 0) * 32]), false);
+                        step(vs4.y, 1.0f, __half22float2(vb[(ub + u4 * 4 + 1) * 32]), false);
+                        step(vs4.z, 1.0f, __half22float2(vb[(ub + u4 * 4 + 2) * 32]), false);
+                        step(vs4.w, 1.0f, __half22float2(vb[(ub + u4 * 4 + 3) * 32]), false);
+                    }
                 }
                 i = FA_DEC_CHUNK;
             }
