@@ -184,30 +184,48 @@ k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
         }
         __syncwarp();
 
-        // V rows of the 32 keys (two dims per lane), shared by the FA_R chains; reuse the key registers
-        __half2 vraw[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            if (!HAS_SKIP || ic0 + i < n_kv) vraw[i] = *(const __half2 *) (vh + (ic0 + i) * nbv1 + lane * 4);
-            else                             vraw[i] = __floats2half2_rn(0.0f, 0.0f);
-        }
-#pragma unroll
-        for (int i0 = 0; i0 < 32; i0 += 4) {
-            float4 vs4[FA_R], ms4[FA_R];
-#pragma unroll
-            for (int r = 0; r < FA_R; ++r) {
-                vs4[r] = *(const float4 *) &VS[warp][r][i0];
-                ms4[r] = *(const float4 *) &MS[warp][r][i0];
-            }
+        // V rows of the 32 keys (two dims per lane), shared by the FA_R chains: four keys at a time, the next four are
+        // requested while these are used.  The loop is kept rolled (two groups per trip): the fully unrolled form is
+        // tens of kilobytes of code and the warps then wait for instruction fetch.
+        auto load4 = [&](int i0, __half2 (&v)[4]) {
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const float2 vf = __half22float2(vraw[i0 + u]);
+                if (!HAS_SKIP || ic0 + i0 + u < n_kv) v[u] = *(const __half2 *) (vh + (ic0 + i0 + u) * nbv1 + lane * 4);
+                else                                  v[u] = __floats2half2_rn(0.0f, 0.0f);
+            }
+        };
+        auto use4 = [&](int i0, const __half2 (&v)[4]) {
+            float4 vs4[FA_R];
+#pragma unroll
+            for (int r = 0; r < FA_R; ++r) vs4[r] = *(const float4 *) &VS[warp][r][i0];
+            if (evt_any == 0) {            // no row met a new maximum in this block: ms == 1 everywhere
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float2 vf = __half22float2(v[u]);
+#pragma unroll
+                    for (int r = 0; r < FA_R; ++r) {
+                        const float vs = u == 0 ? vs4[r].x : u == 1 ? vs4[r].y : u == 2 ? vs4[r].z : vs4[r].w;
+                        float vx = vf.x, vy = vf.y;
+                        if (HAS_SKIP && __float_as_uint(vs) == 0x80000000u) { vx = 0.0f; vy = 0.0f; }    // skipped key: exact no-op
+                        S[r] = __fadd_rn(S[r], vs);          // ms == 1: fma(S, 1, vs) == S + vs
+                        const float2 t = __half22float2(__floats2half2_rn(__fmaf_rn(vx, vs, a0[r]), __fmaf_rn(vy, vs, a1[r])));
+                        a0[r] = t.x; a1[r] = t.y;
+                    }
+                }
+                return;
+            }
+            float4 ms4[FA_R];
+#pragma unroll
+            for (int r = 0; r < FA_R; ++r) ms4[r] = *(const float4 *) &MS[warp][r][i0];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const float2 vf = __half22float2(v[u]);
 #pragma unroll
                 for (int r = 0; r < FA_R; ++r) {
                     const float vs = u == 0 ? vs4[r].x : u == 1 ? vs4[r].y : u == 2 ? vs4[r].z : vs4[r].w;
                     const float ms = u == 0 ? ms4[r].x : u == 1 ? ms4[r].y : u == 2 ? ms4[r].z : ms4[r].w;
                     float vx = vf.x, vy = vf.y;
-                    if (HAS_SKIP && __float_as_uint(vs) == 0x80000000u) { vx = 0.0f; vy = 0.0f; }    // skipped key: exact no-op
+                    if (HAS_SKIP && __float_as_uint(vs) == 0x80000000u) { vx = 0.0f; vy = 0.0f; }
                     if ((evt_any >> r) & 1u) {
                         if (ms != 1.0f) {
                             const float2 t = __half22float2(__floats2half2_rn(__fmul_rn(a0[r], ms), __fmul_rn(a1[r], ms)));
@@ -215,12 +233,21 @@ k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
                         }
                         S[r] = S_FMA ? __fmaf_rn(S[r], ms, vs) : __fadd_rn(__fmul_rn(S[r], ms), vs);
                     } else {
-                        S[r] = __fadd_rn(S[r], vs);          // ms == 1: fma(S, 1, vs) == S + vs
+                        S[r] = __fadd_rn(S[r], vs);
                     }
                     const float2 t = __half22float2(__floats2half2_rn(__fmaf_rn(vx, vs, a0[r]), __fmaf_rn(vy, vs, a1[r])));
                     a0[r] = t.x; a1[r] = t.y;
                 }
             }
+        };
+        __half2 va[4], vb4[4];
+        load4(0, va);
+#pragma unroll 1
+        for (int i0 = 0; i0 < 32; i0 += 8) {
+            load4(i0 + 4, vb4);
+            use4(i0, va);
+            if (i0 + 8 < 32) load4(i0 + 8, va);
+            use4(i0 + 4, vb4);
         }
         __syncwarp();
     }
