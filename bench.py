@@ -332,7 +332,7 @@ def main():
                     "note": LIMITER.get(top)}
 
     cpu_base = None
-    if rank == 0 and not args.no_cpu_baseline:
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:      # reported at N = 1 only
         cw = pkg.Whisper(path, use_gpu=False, flash_attn=True, threads=cores)
         t0 = time.perf_counter()
         cw.greedy_batch(N_NEW, pcm=pcm[:1], device_mel=False)

@@ -497,16 +497,20 @@ k_flash_attn_decode(FaRows rows, int max_kv, int8_t * __restrict__ xq, float * _
             if (tid < 64) {
                 const __half * vb = Vs + (size_t) (c % STAGES) * FA_DEC_CHUNK * 64 + tid;
                 int i = 0;
-                // Common case, a full chunk without a new maximum: one straight-line block of 64 dependent steps, so that the
+                // Common case, a full chunk without a new maximum: straight-line blocks of dependent steps, so that the
                 // compiler can place the shared-memory loads and conversions of later keys into the latency gaps of the chain
                 // (a warp issues in order; with loops or branches in between it would wait for the loads instead).
                 if (kn == FA_DEC_CHUNK && *(const unsigned long long *) &evt[k0 >> 3] == 0ull) {
+                    // blocks of 16 steps: long enough to hide the loads, short enough to stay in the instruction cache
+#pragma unroll 1
+                    for (int ub = 0; ub < FA_DEC_CHUNK; ub += 16) {
 #pragma unroll
-                    for (int u = 0; u < FA_DEC_CHUNK; ++u) {
-                        const float vsu = sc[k0 + u];
-                        float vvu = __half2float(vb[u * 64]);
-                        if (__float_as_uint(vsu) == 0x80000000u) vvu = 0.0f;         // skipped key: exact no-op whatever V holds
-                        a = round_f16(__fmaf_rn(vvu, vsu, a));
+                        for (int u = 0; u < 16; ++u) {
+                            const float vsu = sc[k0 + ub + u];
+                            float vvu = __half2float(vb[(ub + u) * 64]);
+                            if (__float_as_uint(vsu) == 0x80000000u) vvu = 0.0f;     // skipped key: exact no-op whatever V holds
+                            a = round_f16(__fmaf_rn(vvu, vsu, a));
+                        }
                     }
                     i = FA_DEC_CHUNK;
                 }
