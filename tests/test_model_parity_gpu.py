@@ -99,3 +99,23 @@ def test_concurrent_states_are_batched_and_match_the_oracle(pkg, model_dir):
     gpu.close()
     assert np.array_equal(got, want), f"token ids differ under batching:\n{got}\n{want}"
     assert g1 - g0 > b1 - b0 > 0, f"no decode steps were merged (batches {b1 - b0}, graphs {g1 - g0})"
+
+
+@pytest.mark.parametrize("beam", [1, 5])
+def test_whisper_full_beam_search_token_ids(pkg, model_dir, beam):
+    """whisper_full end to end (host log-mel, encoder, beam search with several decoders per step, KV cache sequence
+    copies, the host sampler): the plugin's logits are bit-identical to the reference CPU backend's, so every beam takes
+    the same decisions and the emitted token ids are equal.  Also with the mel computed on the device front-end."""
+    path = os.path.join(model_dir, "tiny-q8_0.bin")
+    if not os.path.exists(path):
+        pkg.synth.write_model(path, "tiny", "q8_0", seed=0)
+    pcm = pkg.synth.pcm_f32(pkg.synth.make_clip(7))[: 16000 * 11]
+    cpu = pkg.Whisper(path, use_gpu=False, flash_attn=True)
+    want = cpu.full(pcm, beam_size=beam, max_tokens=48)
+    cpu.close()
+    gpu = pkg.Whisper(path, use_gpu=True, flash_attn=True)
+    launches0 = pkg.kernels_lib().b200_launch_count()
+    got = gpu.full(pcm, beam_size=beam, max_tokens=48)
+    assert pkg.kernels_lib().b200_launch_count() > launches0
+    gpu.close()
+    assert len(want) > 0 and np.array_equal(want, got), f"beam {beam}: {want[:16]} vs {got[:16]}"
