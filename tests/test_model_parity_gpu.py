@@ -44,7 +44,7 @@ def run_pair(pkg, model_dir, arch, wtype, flash, n_new=32, seed=1):
             w.set_mel(mel)
             out[name]["free_tokens"] = w.greedy(n_new)[0]
             # the plugin, not the CPU backend, must have executed the graphs
-            n_layers = {"tiny": 4, "base": 6}[arch]
+            n_layers = {"tiny": 4, "base": 6, "large-v3": 32}[arch]
             assert backend_stat("b200_stat_nodes", True) - nodes0 > 2 * (20 * n_layers * (n_new + 1))
             assert pkg.kernels_lib().b200_launch_count() - launches0 > 0
         w.close()
@@ -119,3 +119,10 @@ def test_whisper_full_beam_search_token_ids(pkg, model_dir, beam):
     assert pkg.kernels_lib().b200_launch_count() > launches0
     gpu.close()
     assert len(want) > 0 and np.array_equal(want, got), f"beam {beam}: {want[:16]} vs {got[:16]}"
+
+
+def test_large_v3_q5_0_benchmark_shapes(pkg, model_dir):
+    """The benchmark's own model size (d = 1280, 32 + 32 layers, 128 mel bins, vocabulary 51866): encoder output and the
+    logits of a few teacher-forced steps against the reference CPU backend; this is where the tensor-pipe product runs at
+    its real shapes (1280 x 1280, 5120 x 1280, 1280 x 5120 by 1500 columns)."""
+    check(run_pair(pkg, model_dir, "large-v3", "q5_0", True, n_new=4), "large-v3 q5_0 flash")
