@@ -294,7 +294,7 @@ def main():
         t_serial = timing_table(lib)
         # decode loop of ONE group (the plugin merges up to 16 states): the states meet after their prompt step and
         # timing is switched on there, so encoders and other groups do not run beside the kernels that are timed
-        n_batched = min(16, n_states, clips_rank)
+        n_batched = min(12, n_states, clips_rank)
         grp = pkg.Whisper.__new__(pkg.Whisper)
         grp.__dict__.update(w.__dict__)
         grp.states = w.states[:n_batched]

@@ -1142,7 +1142,7 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
     static const bool fuse     = getenv("GGML_B200_NO_FUSION") == nullptr;
     static const bool batching = getenv("GGML_B200_NO_BATCHING") == nullptr;
     static const int  window_us = getenv("GGML_B200_BATCH_WINDOW_US") ? atoi(getenv("GGML_B200_BATCH_WINDOW_US")) : 300;
-    static const int  max_group = getenv("GGML_B200_MAX_GROUP") && atoi(getenv("GGML_B200_MAX_GROUP")) > 0 ? atoi(getenv("GGML_B200_MAX_GROUP")) : 16;
+    static const int  max_group = getenv("GGML_B200_MAX_GROUP") && atoi(getenv("GGML_B200_MAX_GROUP")) > 0 ? atoi(getenv("GGML_B200_MAX_GROUP")) : 12;
     const bool timing = g_timing_on.load() != 0;
     device_batcher & B = g_batchers[ctx->device];
 
