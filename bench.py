@@ -13,8 +13,10 @@ One "step" = one pass over the rank's share of the batch.
   e2e   : the same from host PCM buffers: PCM -> device log-mel -> host mel -> whisper_set_mel -> encode ->
           decode -> token ids on the host, everything inside the timed region.
 
-`--impl reference` times the reference's own CPU backend (oracle/_ref, all host cores) on a bounded sample of
-the same workload (one clip per step).
+`--impl reference` times the reference's own CPU backend (the unmodified host libraries of baseline/_ref with the
+CPU variant that suits the host, all host cores) on a bounded sample of the same workload (one clip per step).
+`--impl oracle-tokens` (internal) runs clip 0 on the parity oracle (oracle/_ref, pinned AVX2 arithmetic) in a process
+of its own and saves its token ids: the main run compares the ids of the same clip from its timed steps with them.
 """
 from __future__ import annotations
 
@@ -29,29 +31,40 @@ import time
 
 import numpy as np
 
+import importlib.util
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, os.path.join(ROOT, "tests"))
-from conftest import load_pkg  # noqa: E402  (path-based import of the dotted package directory)
+
+
+def load_pkg():
+    """The package directory name contains a dot, so it is loaded by path under an importable name."""
+    if "whisper_cpp_b200" not in sys.modules:
+        pkg_dir = os.path.join(ROOT, "whisper.cpp_b200")
+        spec = importlib.util.spec_from_file_location("whisper_cpp_b200", os.path.join(pkg_dir, "__init__.py"),
+                                                      submodule_search_locations=[pkg_dir])
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules["whisper_cpp_b200"] = mod
+        spec.loader.exec_module(mod)
+    return sys.modules["whisper_cpp_b200"]
+
 
 N_NEW = 224
 CLIP_SECONDS = 30.0
 TOTAL_CLIPS = 64
 
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one representative launch of each kernel class, from the
-# ncu captures summarised under profiles/ (small cases of the same kernels; traffic grows with the bytes streamed).
-# what actually limits each class (ncu counters, profiles/): the reference's summation orders are replayed exactly, which keeps
-# the attention kernels and the float chain of the products off the MMA accumulators
+# What limits each kernel class (ncu counters of small cases of the same kernels): the reference's summation orders are
+# replayed exactly, which keeps the attention kernels and the float chain of the products off the MMA accumulators.
 LIMITER = {
-    "flash_attn_ext":    "F16 accumulation chain and 32-way score sums replayed exactly: instruction issue 49 %, tensor pipe unused by design",
-    "mul_mat_q":         "integer lane sums on the tensor pipe (f16 MMA, 44 % busy), float chain on the FMA pipe; 7/8 of each MMA are zero padding",
+    "flash_attn_ext":    "F16 accumulation chain and 32-way score sums replayed exactly: instruction issue, tensor pipe unused by design",
+    "mul_mat_q":         "tcgen05 lane sums (fresh tensor-memory accumulator per 32-block), float chain of 8 FMAs per block and output on the FMA pipe",
     "mul_mat_vec_q":     "launch and load latency of small dependent launches, not bandwidth",
-    "flash_attn_decode": "sequential F16 chain over the keys of each (row, head); 46 % of HBM peak at 32 rows",
+    "flash_attn_decode": "sequential F16 chain over the keys of each (row, head)",
 }
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one representative launch of each class, from an ncu capture
 TRAFFIC_NCU = {
     "mul_mat_vec_q":     {"bytes": 1.175e6, "launch": "1280 x 1280 Q5_0 weights x 16 columns (algorithmic 1.23e6: columns and output stay in L2)"},
     "flash_attn_decode": {"bytes": 251.9e6, "launch": "32 rows x 20 heads x 1536 keys (algorithmic 251.7e6)"},
     "flash_attn_ext":    {"bytes": 15.6e6,  "launch": "1500 x 1536 keys x 20 heads (Q + K/V once; K/V re-reads hit L2)"},
-    "mul_mat_q":         {"bytes": 7.6e6,   "launch": "1280 x 1280 x 1500 columns on the tensor pipe (packed weights 3.5e6 + packed activations 4.1e6, each once)"},
 }
 
 
@@ -126,13 +139,15 @@ def timing_table(lib):
 
 
 def run_reference(args, pkg):
-    """The reference's own CPU implementation (unmodified whisper.cpp + ggml CPU backend, AVX2 build), rank 0 only."""
+    """The reference's own CPU implementation (unmodified whisper.cpp + ggml CPU backend, the variant that suits this
+    host), rank 0 only.  No library of this repository's kernels is loaded in this process."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     cores = len(os.sched_getaffinity(0))
     path = model_file(pkg, args.arch, args.wtype, 0, lambda: None)
-    w = pkg.Whisper(path, use_gpu=False, flash_attn=True, threads=cores)
+    w = pkg.Whisper(path, use_gpu=False, flash_attn=True, threads=cores, oracle=False)
+    info = w.lib.drv_system_info().decode()
     pcm = make_pcm(pkg, 1, 1000)
     times = []
     for s in range(args.warmup + args.steps):
@@ -144,7 +159,8 @@ def run_reference(args, pkg):
     w.close()
     total = sum(times)
     value = CLIP_SECONDS * len(times) / total
-    sample = f"1 clip per step (log-mel + encoder + {N_NEW} greedy tokens), {cores} threads"
+    sample = (f"1 clip per step (log-mel + encoder + {N_NEW} greedy tokens), {cores} threads, {args.warmup} warm-up + {len(times)} timed steps; "
+              f"{info.strip()}")
     print(json.dumps({
         "impl": "reference", "metric": "audio_seconds_per_second", "value": value, "unit": "audio-s/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * total / len(times), "higher_is_better": True,
@@ -156,25 +172,72 @@ def run_reference(args, pkg):
     }))
 
 
+def run_oracle_tokens(args, pkg):
+    """Clip 0 of the benchmark batch on the parity oracle (pinned AVX2 build of the reference CPU backend)."""
+    cores = len(os.sched_getaffinity(0))
+    path = model_file(pkg, args.arch, args.wtype, 0, lambda: None)
+    w = pkg.Whisper(path, use_gpu=False, flash_attn=True, threads=cores)
+    toks, _ = w.greedy_batch(N_NEW, pcm=make_pcm(pkg, 1, 1000), device_mel=False)
+    w.close()
+    np.save(args.out, toks[0])
+
+
+def child(args, impl, extra, timeout=1800):
+    """Runs this script again as `--impl <impl>` in a process of its own and returns its stdout."""
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", impl, "--arch", args.arch, "--wtype", args.wtype, "--n-new", str(N_NEW)] + extra
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=env)
+    if r.returncode != 0:
+        raise RuntimeError(f"{' '.join(cmd)} failed: {r.stderr[-2000:]}")
+    return r.stdout
+
+
+def run_whisper_bench(path, plugin, pkg_dir, host_dir):
+    """The reference's own benchmark tool (examples/bench/bench.cpp), unmodified, on the plugin: Enc / Dec / Bch5 / PP in
+    ms as scripts/bench-all.sh reports them (encode per run, decode per token, batched per token, prompt per token)."""
+    import re
+    env = dict(os.environ, LD_PRELOAD=os.path.join(pkg_dir, "libb200_autoload.so"), GGML_BACKEND_PATH=plugin)
+    try:
+        r = subprocess.run([os.path.join(host_dir, "whisper-bench"), "-m", path, "-t", "1", "-fa"], capture_output=True, text=True, timeout=600, env=env)
+    except Exception as e:      # noqa: BLE001
+        return {"error": str(e)}
+    out = r.stdout + r.stderr
+    if r.returncode != 0:
+        return {"error": out[-400:]}
+    res = {}
+    for key, name in (("encode", "enc_ms"), ("decode", "dec_ms"), ("batchd", "bch5_ms"), ("prompt", "pp_ms")):
+        m = re.search(rf"{key} time =\s*[\d.]+ ms /\s*\d+ runs \(\s*([\d.]+) ms per run\)", out)
+        res[name] = float(m.group(1)) if m else None
+    res["device"] = "B200 plugin" if "B200" in out else "unknown (plugin not reported in the tool's log)"
+    res["published_v100_large_v2_q5_0"] = {"enc_ms": 89.24, "dec_ms": 6.48, "bch5_ms": 1.48, "pp_ms": 0.11}
+    return res
+
+
 def main():
     global N_NEW
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "oracle-tokens"])
+    ap.add_argument("--out", default="", help="--impl oracle-tokens: where the token ids go")
     ap.add_argument("--arch", default="large-v3")
     ap.add_argument("--wtype", default="q5_0")
     ap.add_argument("--clips", type=int, default=TOTAL_CLIPS, help="clips in the whole batch (all ranks)")
     ap.add_argument("--states", type=int, default=0, help="whisper_states (host threads / streams) per GPU; 0 = auto")
     ap.add_argument("--n-new", type=int, default=N_NEW, help="greedy tokens per clip (224 = the benchmark workload; smaller only for profiling)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--quick", action="store_true", help="timed arms only: no per-operator passes, CPU legs or whisper-bench (parameter sweeps)")
+    ap.add_argument("--no-side-output", action="store_true", help="sample from the logits rows read back to the host instead of the plugin's top-k side output")
     args = ap.parse_args()
     N_NEW = args.n_new
     pkg = load_pkg()
 
     if args.impl == "reference":
         run_reference(args, pkg)
+        return
+    if args.impl == "oracle-tokens":
+        run_oracle_tokens(args, pkg)
         return
 
     rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
@@ -204,14 +267,19 @@ def main():
         torch.cuda.synchronize()
 
     cores = len(os.sched_getaffinity(0))
-    # one whisper_state per clip, at most 64: their decode steps are merged by the plugin in groups of up to 16 states, and
-    # several groups in flight keep the device busy while the host threads of the others build their next step
+    # one whisper_state per clip, at most 64: their decode steps are merged by the plugin into groups, and several groups
+    # in flight keep the device busy while the host threads of the others build their next step
     n_states = args.states or min(64, max(1, args.clips // world))
     path = model_file(pkg, args.arch, args.wtype, rank, barrier)
     clips_rank = args.clips // world
     pcm = make_pcm(pkg, clips_rank, 1000 + rank * clips_rank)
     w = pkg.Whisper(path, use_gpu=True, flash_attn=True, gpu_device=local, n_states=n_states, threads=1)
     lib = w.lib
+    # greedy sampling from the plugin's logits side output (top-2 per step) instead of reading 200 KB of logits per state
+    # and step back to the host; the full-logits path stays available (--no-side-output)
+    side_output = not args.no_side_output
+    if side_output:
+        pkg.host.logits_side_output(2, skip_readback=True)
 
     def stat(name):
         return C.CFUNCTYPE(C.c_int64)(lib.drv_backend_proc(b"B200", name.encode()))()
@@ -245,26 +313,26 @@ def main():
                 barrier()
                 sampler.start()
                 l0, h0, d0 = kl.b200_launch_count(), stat("b200_stat_h2d"), stat("b200_stat_d2h")
-                ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                ev0.record()
                 t0 = time.perf_counter()
+            # every call returns when the last state has synchronised its stream and read its last logits back: the host
+            # clock brackets all device work of the step (the plugin's streams are not torch's, so torch events see nothing)
             if kind == "value":
-                w.greedy_batch(N_NEW, mels=mels)
+                toks, _ = w.greedy_batch(N_NEW, mels=mels)
             else:
-                w.greedy_batch(N_NEW, pcm=pcm, device_mel=True)
+                toks, _ = w.greedy_batch(N_NEW, pcm=pcm, device_mel=True)
+            if s >= args.warmup:
+                timed_tokens.append(toks[0].copy())
         barrier()
-        ev1.record()
-        torch.cuda.synchronize()
         dt = time.perf_counter() - t0
-        dev_s = ev0.elapsed_time(ev1) / 1000.0
         sampler.stop_flag.set()
         sampler.join()
         l1, h1, d1 = kl.b200_launch_count(), stat("b200_stat_h2d"), stat("b200_stat_d2h")
-        t = torch.tensor([max(dt, dev_s)], device="cuda", dtype=torch.float64)
+        t = torch.tensor([dt], device="cuda", dtype=torch.float64)
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item()), l1 - l0, h1 - h0, d1 - d0, sampler.summary()
 
+    timed_tokens = []      # clip 0 of every timed step (both arms)
     sec_v, launches, _, _, clocks = run_steps("value")
     sec_e, _, h2d, d2h, _ = run_steps("e2e")
     audio = CLIP_SECONDS * clips_rank * world * args.steps
@@ -281,7 +349,8 @@ def main():
     # stepping together, as in the timed region.  Times are reported per clip.
     roof = None
     per_clip = {}
-    if rank == 0:
+    encoder_ms = None
+    if rank == 0 and not args.quick:
         en = C.CFUNCTYPE(None, C.c_int)(lib.drv_backend_proc(b"B200", b"b200_timing_enable"))
         rs = C.CFUNCTYPE(None)(lib.drv_backend_proc(b"B200", b"b200_timing_reset"))
         one = pkg.Whisper.__new__(pkg.Whisper)  # the same context with a single state
@@ -292,9 +361,19 @@ def main():
         one.greedy_batch(min(N_NEW, 4), mels=mels[:n_serial])
         en(0)
         t_serial = timing_table(lib)
-        # decode loop of ONE group (the plugin merges up to 16 states): the states meet after their prompt step and
+        # encoder alone: whisper_encode (conv + encoder + cross graphs) of one state with nothing else on the device; the call
+        # returns after the backend has synchronised, so the host clock covers launch + device time of the three graphs
+        one.set_mel(mels[0])
+        enc_ms = []
+        for _ in range(6):
+            t0 = time.perf_counter()
+            if lib.drv_encode(one.ctx, one.states[0], 0, 1) != 0:
+                raise SystemExit("whisper_encode failed")
+            enc_ms.append(1000.0 * (time.perf_counter() - t0))
+        encoder_ms = float(np.median(enc_ms[1:]))
+        # decode loop of ONE group (the plugin merges the states of a group): the states meet after their prompt step and
         # timing is switched on there, so encoders and other groups do not run beside the kernels that are timed
-        n_batched = min(12, n_states, clips_rank)
+        n_batched = min(int(os.environ.get("GGML_B200_MAX_GROUP", "12")), n_states, clips_rank)
         grp = pkg.Whisper.__new__(pkg.Whisper)
         grp.__dict__.update(w.__dict__)
         grp.states = w.states[:n_batched]
@@ -331,16 +410,27 @@ def main():
                     "share_of_gpu_time": r["ms"] / sum(v["ms"] for v in per_clip.values()), "timed": r["timed"],
                     "note": LIMITER.get(top)}
 
-    cpu_base = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:      # reported at N = 1 only
-        cw = pkg.Whisper(path, use_gpu=False, flash_attn=True, threads=cores)
-        t0 = time.perf_counter()
-        cw.greedy_batch(N_NEW, pcm=pcm[:1], device_mel=False)
-        dt = time.perf_counter() - t0
-        cw.close()
-        cpu_base = {"value": CLIP_SECONDS / dt, "unit": "audio-s/s", "cores": cores, "kind": "reference",
-                    "sample": f"1 clip (log-mel + encoder + {N_NEW} greedy tokens) on the reference CPU backend, {cores} threads, {dt:.1f} s"}
-    w.close()
+    cpu_base, parity, wbench = None, None, None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.quick:      # reported at N = 1 only
+        # the reference arm in a process of its own (its host libraries never share a process with the product's):
+        # one warm-up clip, two timed clips
+        line = [ln for ln in child(args, "reference", ["--steps", "2", "--warmup", "1"]).splitlines() if ln.startswith("{")][-1]
+        cpu_base = json.loads(line)["cpu_baseline"]
+        # parity inside the run: clip 0 of every timed step against the parity oracle's ids for the same clip
+        tok_file = f"/tmp/b200_bench_oracle_tokens_{os.getpid()}.npy"
+        child(args, "oracle-tokens", ["--out", tok_file])
+        want = np.load(tok_file)
+        os.remove(tok_file)
+        equal = min(int((t == want).sum()) for t in timed_tokens)
+        parity = {"clip": 0, "tokens_equal": equal, "of": int(len(want)), "timed_steps_checked": len(timed_tokens),
+                  "distinct_token_ids": int(len(set(want.tolist()))),
+                  "against": "reference CPU backend, pinned AVX2 build (oracle/_ref), same clip, own process"}
+    if rank == 0 and world == 1 and not args.quick:
+        w.close()
+        w = None
+        wbench = run_whisper_bench(path, pkg.host.PLUGIN_PATH, pkg.PKG_DIR, pkg.HOST_DIR)
+    if w is not None:
+        w.close()
 
     if rank == 0:
         print(json.dumps({
@@ -350,10 +440,13 @@ def main():
             "data": "synthetic",
             "config": {"workload": f"whisper {args.arch} {args.wtype}: encode + greedy {N_NEW} tokens per 30 s clip",
                        "clips_total": clips_rank * world, "clips_per_gpu": clips_rank, "states_per_gpu": n_states, "flash_attn": True,
+                       "sampling": "greedy from the plugin's top-k side output (b200_last_topk), logits read-back off" if side_output
+                                   else "greedy from the logits rows read back to the host",
                        "l2": "inputs larger than L2: 1.1 GB of weights are streamed per decode step per state"},
             "e2e": {"value": e2e, "unit": "audio-s/s", "h2d_bytes_per_step": int(h2d_step), "d2h_bytes_per_step": int(d2h_step),
                     "ms_per_step": 1000.0 * sec_e / args.steps},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu_base,
+            "parity_in_run": parity, "encoder_ms_per_30s": encoder_ms, "whisper_bench": wbench,
             "kernel_classes_per_clip": {k: {"launch_groups": round(v["launch_groups"], 1), "ms": round(v["ms"], 3), "timed": v["timed"]}
                                         for k, v in sorted(per_clip.items(), key=lambda kv: -kv[1]["ms"])},
         }))

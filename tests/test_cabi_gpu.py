@@ -130,6 +130,51 @@ def test_mul_mat_mma_tensor_pipe_path(K, pkg, wtype, Kd, M, N):
     assert K.b200_mul_mat_mma_ep(ptr(wh), ptr(wd), i64(M), i64(96), ptr(xh), ptr(xd), i64(N), ptr(a), i64(M), None, None) != 0   # K % 128
 
 
+
+@pytest.mark.parametrize("wtype", [6, 8])
+@pytest.mark.parametrize("Kd,M,N", [(384, 96, 40), (1280, 130, 73), (512, 64, 72), (2048, 70, 9), (128, 200, 150), (32, 128, 32),
+                                    (1280, 1280, 333), (5120, 257, 64)])
+def test_mul_mat_tc_tcgen05_path(K, pkg, wtype, Kd, M, N):
+    """tcgen05 / tensor-memory product (weights read as planes, Q5_0 unpacked in the shared-memory stage) against the
+    restatement, bit for bit: ragged M / N tiles, one-block K, several tiles per CTA, and the fused epilogue steps."""
+    w, x = rnd(23, M, Kd, scale=0.02), rnd(24, N, Kd) * np.linspace(1e-3, 30, N, dtype=np.float32)[:, None]
+    x[N // 2] = 0
+    blocks, planes, nb = planes_of(K, pkg, wtype, w)
+    d_planes, dx, dst = dev(planes), dev(x), torch.zeros((N, M), device="cuda")
+    qs, d = torch.empty((N, Kd), dtype=torch.int8, device="cuda"), torch.empty((N, Kd // 32), device="cuda")
+    sync_ok(K.b200_quantize_q8_0(ptr(dx), i64(N), i64(Kd), i64(Kd * 4), ptr(qs), ptr(d), None))
+    sync_ok(K.b200_mul_mat_tc_ep(wtype, ptr(d_planes), i64(nb), i64(M), i64(Kd), ptr(qs), ptr(d), i64(N), ptr(dst), i64(M), None, None))
+    assert K.b200_mul_mat_tc_status() == 0, "a device-side wait ran out"
+    if M * N * Kd <= 130 * 73 * 1280:
+        ref = O.mul_mat_q(wtype, blocks, M, Kd, x)
+    else:       # large cases: the dp4a kernel (itself checked against the restatement above) is the reference
+        r = torch.zeros((N, M), device="cuda")
+        sync_ok(K.b200_mul_mat_q(wtype, ptr(d_planes), i64(nb), i64(M), i64(Kd), ptr(qs), ptr(d), i64(N), ptr(r), i64(M), None))
+        ref = r.cpu().numpy()
+    assert bits_equal(dst.cpu().numpy(), ref)
+    bias, res = dev(rnd(25, M)), dev(rnd(26, N, M))
+    ep = Epilogue()
+    ep.n_steps = 3
+    ep.step[0].kind, ep.step[0].ptr, ep.step[0].stride_n = 1, bias.data_ptr(), 0
+    ep.step[1].kind = 3
+    ep.step[2].kind, ep.step[2].ptr, ep.step[2].stride_n = 1, res.data_ptr(), M
+    a, b = torch.zeros((N, M), device="cuda"), torch.zeros((N, M), device="cuda")
+    sync_ok(K.b200_mul_mat_tc_ep(wtype, ptr(d_planes), i64(nb), i64(M), i64(Kd), ptr(qs), ptr(d), i64(N), ptr(a), i64(M), C.byref(ep), None))
+    sync_ok(K.b200_mul_mat_q_ep(wtype, ptr(d_planes), i64(nb), i64(M), i64(Kd), ptr(qs), ptr(d), i64(N), ptr(b), i64(M), C.byref(ep), None))
+    assert bits_equal(a.cpu().numpy(), b.cpu().numpy())
+    # F16 store (the CPY into the K/V cache) with a scale step
+    ep2 = Epilogue()
+    ep2.n_steps, ep2.store_f16 = 1, 1
+    ep2.step[0].kind, ep2.step[0].scalar = 2, 0.3535533845424652
+    a16, b16 = torch.zeros((N, M), dtype=torch.float16, device="cuda"), torch.zeros((N, M), dtype=torch.float16, device="cuda")
+    sync_ok(K.b200_mul_mat_tc_ep(wtype, ptr(d_planes), i64(nb), i64(M), i64(Kd), ptr(qs), ptr(d), i64(N), ptr(a16), i64(M), C.byref(ep2), None))
+    sync_ok(K.b200_mul_mat_q_ep(wtype, ptr(d_planes), i64(nb), i64(M), i64(Kd), ptr(qs), ptr(d), i64(N), ptr(b16), i64(M), C.byref(ep2), None))
+    assert np.array_equal(a16.cpu().numpy().view(np.uint16), b16.cpu().numpy().view(np.uint16))
+    assert K.b200_mul_mat_tc_status() == 0
+    assert K.b200_mul_mat_tc_ep(wtype, ptr(d_planes), i64(nb), i64(M), i64(Kd + 16), ptr(qs), ptr(d), i64(N), ptr(a), i64(M), None, None) != 0   # K % 32
+    assert K.b200_mul_mat_tc_ep(wtype, None, i64(nb), i64(M), i64(Kd), ptr(qs), ptr(d), i64(N), ptr(a), i64(M), None, None) != 0            # NULL weights
+
+
 def test_mul_mat_q_rejects_bad_arguments(K):
     assert K.b200_mul_mat_vec_q(6, None, i64(0), i64(4), i64(48), None, i64(0), i64(1), None, i64(4), None) != 0   # K % 32
     assert K.b200_mul_mat_vec_q(6, None, i64(0), i64(4), i64(64), None, i64(0), i64(9), None, i64(4), None) != 0   # N > 8
@@ -395,3 +440,35 @@ def test_decode_rows_attention_and_layer_norm_rows(K):
     rq, rd = O.quantize_row_q8_0(dy.cpu().numpy()[::-1].copy())       # row i of the launch wrote dy[4 - i]
     assert np.array_equal(xq.cpu().numpy().reshape(-1), rq) and bits_equal(xd.cpu().numpy().reshape(-1), rd)
     assert K.b200_layer_norm_rows_q(lr, 5, ptr(dg), ptr(db), i64(1290), C.c_float(1e-5), ptr(xq), ptr(xd), None) != 0
+
+
+class TopkResult(C.Structure):
+    _fields_ = [("n", C.c_int32), ("k", C.c_int32), ("max", C.c_float), ("logsumexp", C.c_float), ("ids", C.c_int32 * 8), ("vals", C.c_float * 8)]
+
+
+@pytest.mark.parametrize("n,k,n_rows", [(51866, 5, 3), (1024, 8, 1), (70000, 1, 64), (40, 8, 2)])
+def test_topk_rows(K, n, k, n_rows):
+    """Top-k / max / log-sum-exp side output of logits rows against a host scan (ties resolved towards the lower index,
+    as the reference's forward scan does)."""
+    rng = np.random.default_rng(n + k)
+    x = rng.standard_normal((n_rows, n)).astype(np.float32) * 4
+    x[0, 7] = x[0, n - 3] = x[0].max() + 1          # a tie for the maximum
+    if n_rows > 1:
+        x[1, : min(n, 20)] = 2.5                    # a run of equal values
+    dx = dev(x)
+    out = torch.zeros((n_rows, C.sizeof(TopkResult)), dtype=torch.uint8, device="cuda")
+    rows = (vp * n_rows)(*[dx[i].data_ptr() for i in range(n_rows)])
+    outs = (vp * n_rows)(*[out[i].data_ptr() for i in range(n_rows)])
+    sync_ok(K.b200_topk_rows(rows, outs, n_rows, i64(n), k, None))
+    raw = out.cpu().numpy()
+    for i in range(n_rows):
+        r = TopkResult.from_buffer_copy(raw[i].tobytes())
+        order = np.lexsort((np.arange(n), -x[i].astype(np.float64)))[:k]
+        assert r.n == n and r.k == k
+        assert list(r.ids)[:k] == order.tolist(), f"row {i}: {list(r.ids)[:k]} vs {order.tolist()}"
+        assert np.array_equal(np.array(list(r.vals)[:k], np.float32), x[i][order])
+        assert r.max == x[i].max()
+        lse = float(np.log(np.exp(x[i].astype(np.float64) - float(x[i].max())).sum()) + float(x[i].max()))
+        assert abs(r.logsumexp - lse) <= 1e-5 * max(1.0, abs(lse))
+    assert K.b200_topk_rows(rows, outs, n_rows, i64(n), 9, None) != 0       # k beyond the maximum
+    assert K.b200_topk_rows(rows, outs, 65, i64(n), 1, None) != 0           # too many rows

@@ -19,11 +19,16 @@ PKG = os.path.join(ROOT, "whisper.cpp_b200")
 def test_kernel_library_exports_every_declared_symbol(pkg):
     lib = pkg.kernels_lib()
     header = open(os.path.join(ROOT, "include", "b200_whisper.h")).read()
-    names = sorted(set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", header)))
+    code = re.sub(r"/\*.*?\*/", "", header, flags=re.S)           # declarations only; comments name plugin procs too
+    names = sorted(set(re.findall(r"\b(b200_[a-z0-9_]+)\s*\(", code)))
     assert len(names) >= 20
     missing = [n for n in names if not hasattr(lib, n)]
     assert not missing, f"declared but not exported: {missing}"
     assert b"sm_100a" in lib.b200_version()
+    # the optional entry points the header documents for the plugin are exported by the plugin
+    out = subprocess.run(["nm", "-D", "--defined-only", os.path.join(PKG, "libggml-b200.so")], capture_output=True, text=True).stdout
+    for proc in ("b200_logits_side_output", "b200_last_topk"):
+        assert proc in header and f" {proc}" in out
 
 
 def test_plugin_exports_entry_points_and_refuses_without_gpu():
@@ -83,3 +88,24 @@ def test_sharding_two_ranks_gloo(tmp_path):
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
                         "--master-port", "29531", str(script)], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr[-2000:]
+
+
+def test_static_scratch_entry_point_rejects_bad_arguments_without_a_device(pkg):
+    """b200_mul_mat_q_static validates everything before its first launch, so bad arguments come back as error codes on
+    a machine without a GPU as well (no device access happens)."""
+    lib = pkg.kernels_lib()
+    i64, vp = C.c_int64, C.c_void_p
+    buf = np.zeros(1 << 16, np.uint8)
+    p = buf.ctypes.data + (-buf.ctypes.data % 256)
+    ok = dict(w=vp(p), nb=i64(64 * 2), M=i64(64), K=i64(64), x=vp(p + 4096), xs=i64(256), N=i64(4), dst=vp(p + 8192), ds=i64(64))
+
+    def call(**kw):
+        a = dict(ok, **kw)
+        return lib.b200_mul_mat_q_static(6, a["w"], a["nb"], a["M"], a["K"], a["x"], a["xs"], a["N"], a["dst"], a["ds"], None)
+    assert call(x=None) == 10001 and call(dst=None) == 10001 and call(w=None) == 10001
+    assert call(w=vp(p + 4)) == 10001                      # weights not 16-byte aligned
+    assert call(xs=i64(128)) == 10001                      # row stride shorter than a row
+    assert call(ds=i64(32)) == 10001                       # destination stride shorter than M
+    assert call(nb=i64(64)) == 10001                       # weight tensor smaller than M x K
+    assert call(N=i64(1 << 60)) == 10003                   # absurd N: too large, and no overflow on the way
+    assert call(K=i64(48)) == 10001

@@ -6,4 +6,4 @@ The product is two shared libraries built from csrc/:
 plus libb200_driver.so, a flat C wrapper over whisper.h used by the Python harness (host.py).
 """
 from . import synth  # noqa: F401
-from .host import Whisper, kernels_lib, load_plugin, PKG_DIR, REF_DIR  # noqa: F401
+from .host import Whisper, kernels_lib, load_plugin, PKG_DIR, REF_DIR, HOST_DIR  # noqa: F401

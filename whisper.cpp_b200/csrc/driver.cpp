@@ -36,6 +36,14 @@ void drv_set_quiet(int quiet) {
     else       whisper_log_set(nullptr, nullptr);
 }
 
+// Host libraries built with dynamically loaded backends (baseline/Makefile) find their CPU backend variants next to
+// the executable; a process whose executable is an interpreter points the registry at the library directory instead.
+// Returns the number of registered backends afterwards.
+int drv_load_host_backends(const char * dir) {
+    ggml_backend_load_all_from_path(dir);
+    return (int) ggml_backend_reg_count();
+}
+
 // Registers the plugin; returns the number of devices it exposes (0 = load failed / no GPU).
 int drv_load_backend(const char * path) {
     ggml_backend_reg_t reg = ggml_backend_load(path);
@@ -116,6 +124,48 @@ int64_t drv_probe_embd_enc(void * st, float * out, int64_t cap) {
 #endif
 }
 
+// Scheduler evidence (probe build only): number of splits of the last graph each of the state's four schedulers ran
+// (conv, encoder, cross, decoder).  One split = the whole graph went to a single backend.
+int drv_probe_splits(void * st, int * out4) {
+#ifdef DRV_WITH_PROBE
+    struct whisper_state * s = (struct whisper_state *) st;
+    out4[0] = ggml_backend_sched_get_n_splits(s->sched_conv.sched);
+    out4[1] = ggml_backend_sched_get_n_splits(s->sched_encode.sched);
+    out4[2] = ggml_backend_sched_get_n_splits(s->sched_cross.sched);
+    out4[3] = ggml_backend_sched_get_n_splits(s->sched_decode.sched);
+    return 0;
+#else
+    (void) st; (void) out4;
+    return -1;
+#endif
+}
+
+// Number of computing nodes (not views, not empty) of a graph as whisper.cpp builds it for this state (probe build only):
+// which = 0 conv, 1 encoder, 2 cross, 3 decoder for the batch of the state's last whisper_decode call.  Only the graph
+// description is rebuilt in the scheduler's metadata buffer; nothing is allocated or computed.
+int64_t drv_probe_graph_nodes(void * vctx, void * st, int which) {
+#ifdef DRV_WITH_PROBE
+    struct whisper_context * ctx = (struct whisper_context *) vctx;
+    struct whisper_state * s = (struct whisper_state *) st;
+    struct ggml_cgraph * g = nullptr;
+    if (which == 0)      g = whisper_build_graph_conv(*ctx, *s);
+    else if (which == 1) g = whisper_build_graph_encoder(*ctx, *s);
+    else if (which == 2) g = whisper_build_graph_cross(*ctx, *s);
+    else if (which == 3) g = whisper_build_graph_decoder(*ctx, *s, s->batch, false, false);
+    if (!g) return -2;
+    int64_t n = 0;
+    for (int i = 0; i < ggml_graph_n_nodes(g); ++i) {
+        const struct ggml_tensor * t = ggml_graph_node(g, i);
+        const bool view = t->op == GGML_OP_NONE || t->op == GGML_OP_RESHAPE || t->op == GGML_OP_VIEW || t->op == GGML_OP_PERMUTE || t->op == GGML_OP_TRANSPOSE;
+        if (!view && !ggml_is_empty(t)) ++n;
+    }
+    return n;
+#else
+    (void) vctx; (void) st; (void) which;
+    return -1;
+#endif
+}
+
 static int argmax_f32(const float * x, int n) {
     int best = 0;
     float bv = x[0];
@@ -156,6 +206,13 @@ static void decode_phase_meet() {
     else g_phase_cv.wait(lk, [&] { return g_phase_arrived >= g_phase_parties || !g_phase_hook; });
 }
 
+// Optional: sample from the plugin's logits side output (get_proc_address "b200_last_topk", include/b200_whisper.h)
+// instead of scanning the row whisper_get_logits returns.  fn = NULL switches back to the host scan.
+struct drv_topk_result { int32_t n, k; float max, logsumexp; int32_t ids[8]; float vals[8]; };
+typedef int (*drv_last_topk_fn)(int row, drv_topk_result * out);
+static drv_last_topk_fn g_last_topk = nullptr;
+void drv_set_last_topk(void * fn) { g_last_topk = (drv_last_topk_fn) fn; }
+
 int drv_greedy(void * vctx, void * vst, int n_new, int threads, const int * force, int * out, float * margins, float * logits_out) {
     struct whisper_context * ctx = (struct whisper_context *) vctx;
     struct whisper_state *   st  = (struct whisper_state *) vst;
@@ -172,6 +229,17 @@ int drv_greedy(void * vctx, void * vst, int n_new, int threads, const int * forc
     for (int i = 0; i < n_new; ++i) {
         // logits of the last fed token: row n_tokens-1 of the state's logits buffer
         const float * lg = whisper_get_logits_from_state(st) + (i == 0 ? (size_t) 3 * n_vocab : 0);
+        if (g_last_topk && !logits_out) {
+            drv_topk_result r;
+            if (g_last_topk(i == 0 ? 3 : 0, &r) != 0 || r.n != n_vocab || r.k < 2) return -4;
+            out[i] = r.ids[0];
+            if (margins) margins[i] = r.vals[0] - r.vals[1];
+            if (i + 1 == n_new) break;
+            const int feed = force ? force[i] : r.ids[0];
+            if (whisper_decode_with_state(ctx, st, &feed, 1, n_past, threads) != 0) return -3;
+            ++n_past;
+            continue;
+        }
         const int tok = argmax_f32(lg, n_vocab);
         out[i] = tok;
         if (margins) {
@@ -239,13 +307,12 @@ int drv_read_filters(const char * model_path, float * out, int cap, int * n_mel,
     return rc;
 }
 
-// B200 mel front-end of libb200_kernels.so (include/b200_whisper.h)
-void * b200_mel_create(int device, const float * filters_host, int n_mel);
-int    b200_mel_compute(void * plan, const float * pcm_host, int64_t n_samples, float * out_host, int64_t out_capacity, int * n_len, int * n_len_org);
-void   b200_mel_destroy(void * plan);
-
-void * drv_mel_create(int device, const float * filters, int n_mel) { return b200_mel_create(device, filters, n_mel); }
-void   drv_mel_destroy(void * plan) { b200_mel_destroy(plan); }
+// The device log-mel front-end (b200_mel_compute of libb200_kernels.so, include/b200_whisper.h) is handed in as a
+// function pointer by the caller that loaded the kernel library, so that this driver links nothing but the
+// reference's own host libraries.
+typedef int (*drv_mel_compute_fn)(void * plan, const float * pcm_host, int64_t n_samples, float * out_host, int64_t out_capacity, int * n_len, int * n_len_org);
+static drv_mel_compute_fn g_mel_compute = nullptr;
+void drv_set_mel_compute(void * fn) { g_mel_compute = (drv_mel_compute_fn) fn; }
 
 // A batch of clips on one context: n_states worker threads, each with its own whisper_state (and so
 // its own backend stream), pull clips from a shared counter.  Input is either PCM
@@ -267,10 +334,11 @@ int drv_greedy_batch(void * vctx, void ** states, int n_states, void ** mel_plan
             if (pcm) {
                 const float * x = pcm + (size_t) c * n_samples;
                 if (mel_plans) {
+                    if (!g_mel_compute) { err = -12; break; }
                     const int64_t cap = (int64_t) n_mel * ((n_samples + 480000 + 400 - 400) / 160);
                     if ((int64_t) melbuf.size() < cap) melbuf.resize(cap);
                     int nl = 0, nlo = 0;
-                    const int e = b200_mel_compute(mel_plans[w], x, n_samples, melbuf.data(), cap, &nl, &nlo);
+                    const int e = g_mel_compute(mel_plans[w], x, n_samples, melbuf.data(), cap, &nl, &nlo);
                     if (e) { err = -20 - (e & 0xff); break; }
                     if (whisper_set_mel_with_state(ctx, st, melbuf.data(), nl, n_mel) != 0) { err = -10; break; }
                 } else {

@@ -1303,6 +1303,11 @@ extern "C" int b200_mul_mat_q_static(int wtype, const void * w_planes, int64_t n
                                      float * dst, int64_t dst_stride, void * stream) {
     if (K % 32 != 0 || M <= 0 || N <= 0 || K <= 0) return B200_ERR_ARG;
     if (wtype != B200_TYPE_Q5_0 && wtype != B200_TYPE_Q8_0) return B200_ERR_ARG;
+    if (N > B200_STATIC_SCRATCH_BYTES / K) {             // also keeps N * K from overflowing
+        fprintf(stderr, "b200_mul_mat_q_static: %lld activation rows of %lld values do not fit the fixed array of %d bytes\n",
+                (long long) N, (long long) K, B200_STATIC_SCRATCH_BYTES);
+        return B200_ERR_TOO_LARGE;
+    }
     const int64_t q_bytes = N * K, d_bytes = N * (K / 32) * 4;
     const int64_t q_pad = (q_bytes + 255) & ~(int64_t) 255;
     if (q_pad + d_bytes > B200_STATIC_SCRATCH_BYTES) {
@@ -1310,6 +1315,11 @@ extern "C" int b200_mul_mat_q_static(int wtype, const void * w_planes, int64_t n
                 (long long) N, (long long) K, (long long) (q_pad + d_bytes), B200_STATIC_SCRATCH_BYTES);
         return B200_ERR_TOO_LARGE;
     }
+    // everything else is checked before the first launch: a bad argument never costs a kernel on the device
+    if (!x || !dst || !w_planes) return B200_ERR_ARG;
+    if (((uintptr_t) w_planes & 15) != 0 || ((uintptr_t) x & 3) != 0) return B200_ERR_ARG;
+    if (x_stride_bytes < 4 * K || (x_stride_bytes & 3) != 0 || dst_stride < M) return B200_ERR_ARG;
+    if (M > nb_total / (K / 32)) return B200_ERR_ARG;
     unsigned char * scratch = nullptr;
     int e = static_scratch_address(&scratch);
     if (e) return e;

@@ -2,6 +2,13 @@
 
 Nothing here computes: every call lands either in the unmodified whisper.cpp host library or in
 libb200_kernels.so.  Loading fails loudly when a library is missing.
+
+Two builds of the driver exist and a process uses exactly one of them:
+  product  libb200_driver.so, linked against the unmodified reference host libraries in baseline/_ref - what an
+           application that loads the plugin looks like (bench.py, smoke);
+  oracle   oracle/_ref/libb200_driver_probe.so with the checker's own copy of the reference libraries - the CPU
+           backend used as parity oracle, and the probe into whisper_state internals that the tests read.
+Loading both would put two copies of libggml / libwhisper into one process, so the second request is refused.
 """
 from __future__ import annotations
 
@@ -11,7 +18,8 @@ import os
 import numpy as np
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-REF_DIR = os.path.join(os.path.dirname(PKG_DIR), "oracle", "_ref")
+REF_DIR = os.path.join(os.path.dirname(PKG_DIR), "oracle", "_ref")        # checker: oracle CPU backend + probe driver
+HOST_DIR = os.path.join(os.path.dirname(PKG_DIR), "baseline", "_ref")     # product: host libraries the driver links
 PLUGIN_PATH = os.path.join(PKG_DIR, "libggml-b200.so")
 
 _kernels = None
@@ -34,6 +42,9 @@ def kernels_lib() -> C.CDLL:
 
 def _driver(probe: bool) -> C.CDLL:
     if probe not in _drivers:
+        if (not probe) in _drivers:
+            raise RuntimeError("this process already loaded the other build of the driver (product vs oracle/probe); "
+                               "two copies of the reference host libraries must not share a process")
         path = os.path.join(REF_DIR, "libb200_driver_probe.so") if probe else os.path.join(PKG_DIR, "libb200_driver.so")
         if not os.path.exists(path):
             raise RuntimeError(f"{path} is missing: run `make -C oracle` and `make -C {PKG_DIR}/csrc`")
@@ -46,6 +57,9 @@ def _driver(probe: bool) -> C.CDLL:
         lib.drv_state_new.argtypes = [vp]
         lib.drv_state_free.argtypes = [vp]
         lib.drv_load_backend.argtypes = [C.c_char_p]
+        lib.drv_load_host_backends.argtypes = [C.c_char_p]
+        if not probe and lib.drv_load_host_backends(HOST_DIR.encode()) < 1:
+            raise RuntimeError(f"no CPU backend variant could be loaded from {HOST_DIR} (run `make -C baseline`)")
         lib.drv_backend_proc.restype = vp
         lib.drv_backend_proc.argtypes = [C.c_char_p, C.c_char_p]
         for f in ("drv_n_vocab", "drv_n_mels", "drv_n_audio_state", "drv_n_audio_ctx"):
@@ -67,9 +81,11 @@ def _driver(probe: bool) -> C.CDLL:
         lib.drv_greedy_batch.argtypes = [vp, C.POINTER(vp), ci, C.c_void_p, C.c_void_p, ci, C.c_void_p, ci, ci, ci, ci, ci,
                                          C.c_void_p, C.POINTER(C.c_double)]
         lib.drv_read_filters.argtypes = [C.c_char_p, C.c_void_p, ci, C.POINTER(ci), C.POINTER(ci)]
-        lib.drv_mel_create.restype = vp
-        lib.drv_mel_create.argtypes = [ci, C.c_void_p, ci]
-        lib.drv_mel_destroy.argtypes = [vp]
+        lib.drv_set_mel_compute.argtypes = [vp]
+        lib.drv_set_last_topk.argtypes = [vp]
+        lib.drv_probe_splits.argtypes = [vp, C.POINTER(ci)]
+        lib.drv_probe_graph_nodes.restype = C.c_int64
+        lib.drv_probe_graph_nodes.argtypes = [vp, vp, ci]
         lib.drv_system_info.restype = C.c_char_p
         _drivers[probe] = lib
     return _drivers[probe]
@@ -86,6 +102,34 @@ def load_plugin(probe: bool = False) -> int:
     return _drivers[key]
 
 
+class TopkResult(C.Structure):
+    """b200_topk_result of include/b200_whisper.h"""
+    _fields_ = [("n", C.c_int32), ("k", C.c_int32), ("max", C.c_float), ("logsumexp", C.c_float),
+                ("ids", C.c_int32 * 8), ("vals", C.c_float * 8)]
+
+
+def logits_side_output(top_k: int, skip_readback: bool = False, probe: bool = False, use_in_driver: bool = True):
+    """Switches the plugin's logits side output on (top_k > 0) or off; with use_in_driver the driver's greedy loop samples
+    from it (b200_last_topk) instead of scanning whisper_get_logits on the host."""
+    lib = _driver(probe)
+    fn = lib.drv_backend_proc(b"B200", b"b200_logits_side_output")
+    last = lib.drv_backend_proc(b"B200", b"b200_last_topk")
+    if not fn or not last:
+        raise RuntimeError("the plugin does not offer the logits side output (plugin not loaded?)")
+    C.CFUNCTYPE(None, C.c_int, C.c_int)(fn)(int(top_k), int(bool(skip_readback)))
+    lib.drv_set_last_topk(C.c_void_p(last if (top_k > 0 and use_in_driver) else None))
+
+
+def last_topk(row: int = 0, probe: bool = False) -> TopkResult:
+    lib = _driver(probe)
+    last = lib.drv_backend_proc(b"B200", b"b200_last_topk")
+    r = TopkResult()
+    rc = C.CFUNCTYPE(C.c_int, C.c_int, C.POINTER(TopkResult))(last)(row, C.byref(r))
+    if rc != 0:
+        raise RuntimeError(f"b200_last_topk failed: {rc}")
+    return r
+
+
 def backend_stat(name: str, probe: bool = False) -> int:
     lib = _driver(probe)
     p = lib.drv_backend_proc(b"B200", name.encode())
@@ -95,10 +139,15 @@ def backend_stat(name: str, probe: bool = False) -> int:
 
 
 class Whisper:
-    """One whisper_context (+ states) on the CPU backend (use_gpu=False, the oracle) or on the B200 plugin."""
+    """One whisper_context (+ states) on the B200 plugin (use_gpu=True) or on the reference CPU backend (use_gpu=False:
+    the oracle build unless oracle=False).  probe=True selects the oracle/probe build of the driver for a plugin run."""
 
     def __init__(self, model_path: str, use_gpu: bool, flash_attn: bool = True, gpu_device: int = 0,
-                 probe: bool = False, n_states: int = 1, threads: int | None = None, quiet: bool = True):
+                 probe: bool = False, n_states: int = 1, threads: int | None = None, quiet: bool = True,
+                 oracle: bool | None = None):
+        # oracle=False with use_gpu=False: the reference CPU path through the product's host libraries (best CPU variant
+        # for this host) - what `bench.py --impl reference` times; the parity oracle is the pinned AVX2 build instead
+        probe = probe or (oracle if oracle is not None else not use_gpu)
         self.lib = _driver(probe)
         self.probe = probe
         self.model_path = model_path
@@ -122,7 +171,7 @@ class Whisper:
 
     def close(self):
         for p in self.mel_plans:
-            self.lib.drv_mel_destroy(p)
+            kernels_lib().b200_mel_destroy(C.c_void_p(p))
         self.mel_plans = []
         for s in self.states:
             self.lib.drv_state_free(s)
@@ -195,9 +244,15 @@ class Whisper:
     def _ensure_mel_plans(self):
         if not self.mel_plans:
             f = self.filters()
-            self.mel_plans = [self.lib.drv_mel_create(self.gpu_device, f.ctypes.data, f.shape[0]) for _ in self.states]
+            kl = kernels_lib()
+            kl.b200_mel_create.restype = C.c_void_p
+            kl.b200_mel_create.argtypes = [C.c_int, C.c_void_p, C.c_int]
+            kl.b200_mel_destroy.argtypes = [C.c_void_p]
+            self.mel_plans = [kl.b200_mel_create(self.gpu_device, f.ctypes.data, f.shape[0]) for _ in self.states]
             if not all(self.mel_plans):
                 raise RuntimeError("b200_mel_create failed (no CUDA device?)")
+            # the driver's worker threads call the device front-end through this pointer
+            self.lib.drv_set_mel_compute(C.cast(kl.b200_mel_compute, C.c_void_p))
 
     def greedy_batch(self, n_new: int, mels: np.ndarray | None = None, pcm: np.ndarray | None = None, device_mel: bool = True):
         """Encode + greedy-decode a batch of clips spread over all states.
@@ -224,6 +279,20 @@ class Whisper:
         if e != 0:
             raise RuntimeError(f"drv_greedy_batch failed: {e}")
         return toks, secs.value
+
+    def sched_splits(self, state: int = 0):
+        """Splits of the last conv / encoder / cross / decoder graph of a state (probe build); 1 = one backend ran it all."""
+        a = (C.c_int * 4)()
+        if self.lib.drv_probe_splits(self.states[state], a) != 0:
+            raise RuntimeError("scheduler probe unavailable; use probe=True")
+        return list(a)
+
+    def graph_nodes(self, which: int, state: int = 0) -> int:
+        """Computing nodes of the conv (0) / encoder (1) / cross (2) / last decoder (3) graph of a state (probe build)."""
+        n = self.lib.drv_probe_graph_nodes(self.ctx, self.states[state], which)
+        if n < 0:
+            raise RuntimeError(f"graph probe unavailable ({n}); use probe=True")
+        return int(n)
 
     def full(self, pcm: np.ndarray | None, beam_size: int = 1, max_tokens: int = 0, state: int = 0):
         out = np.zeros(1024, np.int32)

@@ -13,8 +13,20 @@ import sys
 
 import torch
 
-sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "tests"))
-from conftest import load_pkg  # noqa: E402
+import importlib.util  # noqa: E402
+
+
+def load_pkg():
+    """This file's own package, loaded by path (the directory name contains a dot)."""
+    if "whisper_cpp_b200" not in sys.modules:
+        pkg_dir = os.path.dirname(os.path.abspath(__file__))
+        spec = importlib.util.spec_from_file_location("whisper_cpp_b200", os.path.join(pkg_dir, "__init__.py"),
+                                                      submodule_search_locations=[pkg_dir])
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules["whisper_cpp_b200"] = mod
+        spec.loader.exec_module(mod)
+    return sys.modules["whisper_cpp_b200"]
+
 
 i64, vp = C.c_int64, C.c_void_p
 
@@ -86,6 +98,13 @@ def main():
 
         t = timeit(cols_q)
         print(f"  mul_mat_cols_q {name:7s} M={M:6d} K={Kd:5d}: {t:8.1f} us   {nb * 22 / t / 1e3:7.1f} GB/s of weights")
+        if NC >= 9:
+            def tc():
+                p = planes[it[0] % ncopy]
+                it[0] += 1
+                assert K.b200_mul_mat_tc_ep(6, ptr(p), i64(nb), i64(M), i64(Kd), ptr(xq), ptr(xd), i64(NC), ptr(out), i64(M), None, None) == 0
+            t = timeit(tc)
+            print(f"  mul_mat_tc     {name:7s} M={M:6d} K={Kd:5d}: {t:8.1f} us   {nb * 22 / t / 1e3:7.1f} GB/s of weights (tcgen05, {NC} columns)")
         print(f"  quantize_cols  K={Kd}: {timeit(lambda: K.b200_quantize_cols(xs, NC, i64(Kd), ptr(xq), ptr(xd), None)):.1f} us")
         if NC <= 8:
             def vec():
@@ -122,6 +141,8 @@ def main():
         assert K.b200_quantize_q8_0(ptr(x), i64(N), i64(Kd), i64(Kd * 4), ptr(xq), ptr(xd), None) == 0
         t = timeit(lambda: K.b200_mul_mat_q(6, ptr(p), i64(nb), i64(M), i64(Kd), ptr(xq), ptr(xd), i64(N), ptr(out), i64(M), None), 10)
         print(f"  mul_mat_q {name:6s}: {t:8.1f} us   {2 * M * N * Kd / t / 1e6:7.2f} TFLOP/s")
+        t = timeit(lambda: K.b200_mul_mat_tc_ep(6, ptr(p), i64(nb), i64(M), i64(Kd), ptr(xq), ptr(xd), i64(N), ptr(out), i64(M), None, None), 10)
+        print(f"  mul_mat_tc {name:6s}: {t:7.1f} us   {2 * M * N * Kd / t / 1e6:7.2f} TFLOP/s  (tcgen05 + tensor memory)")
         wh, wd = torch.empty((nb, 16), dtype=torch.int32, device="cuda"), torch.empty(nb, device="cuda")
         xh, xdh = torch.empty((N * Kd // 32, 16), dtype=torch.int32, device="cuda"), torch.empty(N * Kd // 32, device="cuda")
         xf = torch.randn((N, Kd), device="cuda")
@@ -138,6 +159,7 @@ def main():
     o = torch.zeros((n_q, H, 64), device="cuda")
     t = timeit(lambda: K.b200_flash_attn_ext(ptr(q), i64(H * 256), i64(256), ptr(k), i64(H * 128), i64(128), ptr(v), i64(H * 128), i64(128), None, i64(0),
                                              ptr(o), i64(n_q), i64(n_kv), i64(H), C.c_float(0.125), None), 5)
+    assert K.b200_mul_mat_tc_status() == 0, "a device-side wait of the tcgen05 product ran out"
     print(f"  flash_attn_ext 1500 x 1536 x 20 heads: {t:8.1f} us   {4 * 64 * n_q * n_kv * H / t / 1e6:7.2f} TFLOP/s")
 
 
