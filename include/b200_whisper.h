@@ -131,6 +131,25 @@ int b200_mul_mat_mma_ep(const void * wh, const float * wd, int64_t M, int64_t K,
                         const void * xh, const float * xd, int64_t N,
                         void * dst, int64_t dst_stride, const b200_epilogue * ep, void * stream);
 
+/* The same product once more (ggml_compute_forward_mul_mat, ggml/src/ggml-cpu/ggml-cpu.c:1266-1458, with
+ * ggml_vec_dot_q5_0_q8_0 / ggml_vec_dot_q8_0_q8_0, ggml-cpu-quants.c:3076-3100, 3869-3886; same bits) on the
+ * fifth-generation tensor cores: tcgen05.mma with a fresh tensor-memory accumulator per 32-block gives the eight
+ * exact integer lane sums of every (row, column, block), epilogue warps drain tensor memory into the reference's
+ * float chain.  Arguments as b200_mul_mat_q_ep: weights as planes (no repacked copy is needed, Q5_0 is unpacked in
+ * the shared-memory stage), activations quantised by b200_quantize_q8_0.  Any M, N >= 1, K % 32 == 0.
+ * b200_mul_mat_tc_status: 0, or the code of a device-side wait that ran out in an earlier launch (the launch then
+ * returned without finishing its tiles); synchronises with the device. */
+int b200_mul_mat_tc_ep(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                       const int8_t * xq, const float * xd, int64_t N,
+                       void * dst, int64_t dst_stride, const b200_epilogue * ep, void * stream);
+int b200_mul_mat_tc_status(void);
+/* The same with every column described on its own (cols[n].dst / cols[n].add as in b200_mul_mat_cols_q, cols[n].x is
+ * ignored; at most 64 columns): single-token decode steps of many whisper_states in one pass over the weights.  No
+ * counterpart in the reference, which decodes state by state. */
+int b200_mul_mat_tc_cols(int wtype, const void * w_planes, int64_t nb_total, int64_t M, int64_t K,
+                         const int8_t * xq, const float * xd, const b200_gemv_col * cols, int n_cols,
+                         const b200_gemv_ep * ep, void * stream);
+
 /* NORM -> MUL(gamma) -> ADD(beta) in one pass (ops.cpp:3109-3158 followed by binary-ops.cpp:50-137), each of the
  * three roundings kept: y = ((x - mean) * rstd) * gamma + beta. */
 int b200_layer_norm(const float * x, const float * gamma, const float * beta, float * y, int64_t ne00, int64_t nrows,
@@ -144,8 +163,9 @@ int b200_layer_norm(const float * x, const float * gamma, const float * beta, fl
  * work - quantise N rows of f32 activations (row stride in bytes), then the Q5_0/Q8_0 product - with the
  * scratch held in a fixed device array that is part of this library's image (b200_static_scratch_bytes()
  * bytes, resident on every GPU that loads the library until the process exits).  It calls no allocator.
- *  - N*K + 4*N*K/32 bytes (plus padding to 256) must fit; otherwise B200_ERR_TOO_LARGE is returned and nothing
- *    is launched.
+ *  - N*K + 4*N*K/32 bytes (plus padding to 256) must fit; otherwise B200_ERR_TOO_LARGE is returned.  All
+ *    arguments (NULL pointers, alignment, strides, weight extent) are checked first: an error return means nothing
+ *    was launched.
  *  - The first call on each device looks up the array's device address (with that device current); make that
  *    first call outside any stream capture.
  *  - All calls share the one array and it keeps the previous call's contents.  Every byte a call reads is
@@ -217,6 +237,14 @@ int b200_cpy(const void * src, int src_type, const int64_t * nes, const int64_t 
 int b200_get_rows(int type, const void * table, int64_t nb_total_or_row_stride, int64_t ne00,
                   const int32_t * ids, int64_t n_ids, float * dst, void * stream);
 
+/* Side output for the host sampler (whisper_process_logits / whisper_sample_token / whisper_sample_token_topk,
+ * src/whisper.cpp:5015-5430, which scan a full row of n_vocab logits per decoder and step): per row of n values the k
+ * largest with their indices (ties: lower index first, as the reference's forward scan with `>` resolves them), the
+ * maximum and log(sum(exp(x - max))) + max.  rows[i] / out[i] are device pointers, at most 64 rows per call. */
+#define B200_TOPK_MAX 8
+typedef struct { int32_t n, k; float max, logsumexp; int32_t ids[B200_TOPK_MAX]; float vals[B200_TOPK_MAX]; } b200_topk_result;
+int b200_topk_rows(const float * const * rows, b200_topk_result * const * out, int n_rows, int64_t n, int k, void * stream);
+
 /* IM2COL 1-D, F16 output (ops.cpp:5784-5855): x f32 [IW, IC] (row stride bytes) ->
  * dst f16 [IC*KW, OW]. */
 int b200_im2col_1d_f16(const float * x, int64_t x_stride_bytes, int64_t IW, int64_t IC, int64_t KW,
@@ -244,6 +272,20 @@ void * b200_mel_create(int device, const float * filters_host, int n_mel);
 int    b200_mel_compute(void * plan, const float * pcm_host, int64_t n_samples, float * out_host, int64_t out_capacity,
                         int * n_len, int * n_len_org);
 void   b200_mel_destroy(void * plan);
+
+/* ---- optional entry points of the plugin (libggml-b200.so), obtained with
+ * ggml_backend_reg_get_proc_address(ggml_backend_reg_by_name("B200"), name)  (ggml/include/ggml-backend.h:190):
+ *
+ *   void b200_logits_side_output(int top_k, int skip_readback)
+ *       top_k > 0: after every decoder graph (its last node is the logits product, src/whisper.cpp:2830) the plugin also
+ *       leaves b200_topk_rows of every logits row in a small device buffer of the backend instance that ran the graph.
+ *       skip_readback != 0: ggml_backend_tensor_get on a logits tensor returns at once without copying - for callers
+ *       that sample from the side output only; whisper_get_logits() then holds stale data.  Default: off, off.
+ *   int b200_last_topk(int row, b200_topk_result * out)
+ *       side output of logits row `row` of the last decoder graph computed on the CALLING thread (whisper_decode is
+ *       synchronous, so that is the state the thread just stepped); waits for that graph, copies one result to the host.
+ *       Returns 0, or B200_ERR_ARG when there is no such row.
+ * No counterpart in the reference, which samples from the full row on the host. */
 
 /* Library info: number of kernel launches issued so far by this process (all entry points). */
 int64_t b200_launch_count(void);

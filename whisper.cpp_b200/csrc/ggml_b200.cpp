@@ -79,6 +79,12 @@ int64_t b200_stat_host_ns_compute(void) { return g_host_ns_compute.load(); }
 int64_t b200_stat_host_ns_sync(void)    { return g_host_ns_sync.load(); }
 }
 
+// Logits side output (off by default; switched through get_proc_address, see b200_whisper.h)
+static std::atomic<int> g_topk_k{0};
+static std::atomic<int> g_skip_logits_readback{0};
+static std::mutex g_logits_mu;
+static std::unordered_map<const void *, int> g_logits_ptrs;     // device addresses of logits tensors seen by graph_compute
+
 // ---------------------------------------------------------------------------------------------
 // buffer
 // ---------------------------------------------------------------------------------------------
@@ -172,6 +178,10 @@ static void b200_buffer_set_tensor(ggml_backend_buffer_t buffer, struct ggml_ten
 
 static void b200_buffer_get_tensor(ggml_backend_buffer_t buffer, const struct ggml_tensor * tensor, void * data, size_t offset, size_t size) {
     b200_buffer_ctx * ctx = (b200_buffer_ctx *) buffer->context;
+    if (g_skip_logits_readback.load(std::memory_order_relaxed)) {      // the caller samples from the side output only
+        std::lock_guard<std::mutex> lk(g_logits_mu);
+        if (g_logits_ptrs.count(tensor->data)) return;
+    }
     cudaSetDevice(ctx->device);
     g_d2h_bytes += (int64_t) size;
     if (is_quant(tensor->type)) {
@@ -276,7 +286,7 @@ struct b200_backend_ctx {
     std::string  name;
     std::vector<cudaEvent_t> events;       // timing mode only
     std::atomic<int64_t> last_decode_ns{0};   // when this instance last submitted a decode-step graph
-    // quantised activation columns of the decode path (up to 32 columns of up to COLQ_MAX_K values)
+    // quantised activation columns of the decode path (up to COLQ_MAX_COLS columns of up to COLQ_MAX_K values)
     void *       colq = nullptr;
     std::vector<const float *> colq_ptrs;    // columns currently held in colq ...
     int64_t      colq_K = 0;
@@ -284,8 +294,16 @@ struct b200_backend_ctx {
     std::atomic<int64_t> served_ns{0};       // when a leader last enqueued a step for this instance (0: not in a batch)
     cudaEvent_t  sync_event = nullptr;       // blocking-sync event: waiting threads sleep instead of spinning on a core
     int64_t      item_seq = 0;
+    // side output of the last decoder graph: top-k / max / log-sum-exp of up to 8 logits rows (b200_topk_rows)
+    b200_topk_result * topk = nullptr;       // device, 8 entries
+    int          topk_rows = 0;              // rows valid after the last decoder graph of this instance
 };
 #define COLQ_MAX_K 8192
+#define COLQ_MAX_COLS 64
+static inline int8_t * colq_q(b200_backend_ctx * ctx) { return (int8_t *) ctx->colq; }
+static inline float *  colq_d(b200_backend_ctx * ctx) { return (float *) ((char *) ctx->colq + (size_t) COLQ_MAX_COLS * COLQ_MAX_K); }
+
+static thread_local b200_backend_ctx * tl_last_decode_ctx = nullptr;
 
 static void batcher_join(b200_backend_ctx * ctx);
 static void batcher_leave(b200_backend_ctx * ctx);
@@ -301,6 +319,8 @@ static void b200_backend_free(ggml_backend_t backend) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->colq) cudaFree(ctx->colq);
+    if (ctx->topk) cudaFree(ctx->topk);
+    if (tl_last_decode_ctx == ctx) tl_last_decode_ctx = nullptr;
     if (ctx->sync_event) cudaEventDestroy(ctx->sync_event);
     for (cudaEvent_t e : ctx->events) cudaEventDestroy(e);
     cudaStreamDestroy(ctx->stream);
@@ -360,9 +380,21 @@ static bool mma_weights_of(b200_backend_ctx * ctx, const struct ggml_tensor * w,
 static int gemm_quant(b200_backend_ctx * ctx, const struct ggml_tensor * w, const float * x, int64_t x_stride_bytes, int64_t N,
                       void * dst, int64_t ldd, const b200_epilogue * ep) {
     static const bool use_mma = getenv("GGML_B200_NO_MMA") == nullptr;
+    static const bool use_tc  = getenv("GGML_B200_NO_TC") == nullptr;
     void * st = (void *) ctx->stream;
     const int64_t K = w->ne[0], M = w->ne[1];
     const int64_t nb_total = (int64_t) (ggml_nbytes(w) / ggml_type_size(w->type));
+    if (use_tc) {
+        // tcgen05 product: reads the weight planes as they are (no repacked copy), activations as int8 + scales
+        const size_t q_bytes = (size_t) N * K, d_bytes = (size_t) N * (K / 32) * 4;
+        const size_t q_pad = (q_bytes + 255) & ~(size_t) 255;
+        if (!ensure_scratch(ctx, q_pad + d_bytes)) return (int) cudaErrorMemoryAllocation;
+        int8_t * xq = (int8_t *) ctx->scratch;
+        float *  xd = (float *) ((char *) ctx->scratch + q_pad);
+        int e = b200_quantize_q8_0(x, N, K, x_stride_bytes, xq, xd, st);
+        if (e) return e;
+        return b200_mul_mat_tc_ep((int) w->type, w->data, nb_total, M, K, xq, xd, N, dst, ldd, ep, st);
+    }
     mma_weights mw;
     if (use_mma && N >= 32 && K % 128 == 0 && mma_weights_of(ctx, w, nb_total, &mw)) {
         const size_t h_bytes = (size_t) N * (K / 32) * 64, d_bytes = (size_t) N * (K / 32) * 4;
@@ -637,8 +669,63 @@ static uint64_t graph_signature(struct ggml_cgraph * g) {
 }
 
 // Does graph g satisfy what the plan assumes (operators in place, supported, no aliasing hazard for fused items)?
+// A plan is found by a signature of operators, types and shapes only, so everything fusion relied on when the plan
+// was built is checked again on the candidate graph: the intermediates of a fused item have exactly one consumer and
+// are not graph outputs, shapes and strides of the operands are what the fused kernels take.
 static bool graph_fits_plan(const exec_plan & plan, struct ggml_cgraph * g) {
-    if (ggml_graph_n_nodes(g) != plan.n_nodes) return false;
+    const int n_nodes = ggml_graph_n_nodes(g);
+    if (n_nodes != plan.n_nodes) return false;
+    {   // intermediates that a fused launch never writes to memory
+        std::vector<const struct ggml_tensor *> inter;
+        for (const plan_item & it : plan.items) {
+            if (it.last == it.node) continue;
+            if (it.kind == PK_LAYER_NORM) {
+                inter.push_back(ggml_graph_node(g, it.node));
+                inter.push_back(ggml_graph_node(g, it.node + 1));
+            } else if (it.kind == PK_GEMV || it.kind == PK_GEMM) {
+                inter.push_back(ggml_graph_node(g, it.node));
+                for (int s = 0; s < it.n_steps; ++s) if (it.step_node[s] != it.last) inter.push_back(ggml_graph_node(g, it.step_node[s]));
+            }
+        }
+        if (!inter.empty()) {
+            std::unordered_map<const struct ggml_tensor *, int> uses;
+            uses.reserve(inter.size() * 2);
+            for (const struct ggml_tensor * t : inter) {
+                if (t->flags & GGML_TENSOR_FLAG_OUTPUT) return false;
+                uses[t] = 0;
+            }
+            // operands a fused epilogue adds (and what they are views of) must exist before the product runs
+            std::unordered_map<const struct ggml_tensor *, int> needed_before;
+            for (const plan_item & it : plan.items) {
+                if (it.kind != PK_GEMV && it.kind != PK_GEMM) continue;
+                for (int s = 0; s < it.n_steps; ++s) {
+                    if (it.step_kind[s] != B200_EP_ADD) continue;
+                    const struct ggml_tensor * o = ggml_graph_node(g, it.step_node[s])->src[it.step_src[s]];
+                    for (; o; o = o->view_src) {
+                        auto f = needed_before.find(o);
+                        if (f == needed_before.end() || f->second > it.node) needed_before[o] = it.node;
+                    }
+                }
+            }
+            for (int i = 0; i < n_nodes; ++i) {
+                const struct ggml_tensor * t = ggml_graph_node(g, i);
+                if (!needed_before.empty()) {
+                    auto f = needed_before.find(t);
+                    if (f != needed_before.end() && i >= f->second) return false;
+                }
+                for (int k = 0; k < GGML_MAX_SRC; ++k) {
+                    if (!t->src[k]) continue;
+                    auto u = uses.find(t->src[k]);
+                    if (u != uses.end()) u->second++;
+                }
+                if (t->view_src) {
+                    auto u = uses.find(t->view_src);
+                    if (u != uses.end()) u->second++;
+                }
+            }
+            for (const auto & u : uses) if (u.second != 1) return false;
+        }
+    }
     for (const plan_item & it : plan.items) {
         struct ggml_tensor * node = ggml_graph_node(g, it.node);
         if (!b200_op_supported(node)) return false;
@@ -647,6 +734,11 @@ static bool graph_fits_plan(const exec_plan & plan, struct ggml_cgraph * g) {
             struct ggml_tensor * mul = ggml_graph_node(g, it.node + 1), * out = ggml_graph_node(g, it.last);
             if (mul->op != GGML_OP_MUL || out->op != GGML_OP_ADD || mul->src[0] != node || out->src[0] != mul) return false;
             const struct ggml_tensor * x = node->src[0];
+            auto vec_ok = [&](const struct ggml_tensor * v) {
+                return v->type == GGML_TYPE_F32 && v->ne[0] == x->ne[0] && v->ne[1] == 1 && v->ne[2] == 1 && v->ne[3] == 1 && v->nb[0] == 4;
+            };
+            if (!vec_ok(mul->src[1]) || !vec_ok(out->src[1]) || x->type != GGML_TYPE_F32 || x->ne[2] != 1 || x->ne[3] != 1 || x->nb[0] != 4 ||
+                out->nb[0] != 4 || !ggml_are_same_shape(x, out)) return false;
             // rows are read and written by the same threads, so exact in-place is fine; a shifted overlap is not
             if (overlaps(out, x) && !(out->data == x->data && out->nb[1] == x->nb[1])) return false;
             if (!b200_op_supported(mul) || !b200_op_supported(out)) return false;
@@ -656,9 +748,12 @@ static bool graph_fits_plan(const exec_plan & plan, struct ggml_cgraph * g) {
             const struct ggml_tensor * cur = node;
             for (int s = 0; s < it.n_steps; ++s) {
                 struct ggml_tensor * t = ggml_graph_node(g, it.step_node[s]);
+                if (t->nb[0] != 4 || t->type != GGML_TYPE_F32 || !ggml_are_same_shape(t, node)) return false;
                 if (it.step_kind[s] == B200_EP_ADD) {
                     if (t->op != GGML_OP_ADD || t->src[1 - it.step_src[s]] != cur) return false;
                     const struct ggml_tensor * o = t->src[it.step_src[s]];
+                    if (o == cur || o->type != GGML_TYPE_F32 || o->nb[0] != 4 || o->ne[0] != node->ne[0] || o->ne[2] != 1 || o->ne[3] != 1 ||
+                        (o->ne[1] != 1 && o->ne[1] != node->ne[1])) return false;
                     // an added tensor may share memory with the result only element for element
                     if (overlaps(out, o) && !(o->data == out->data && o->nb[1] == out->nb[1])) return false;
                 } else if (it.step_kind[s] == B200_EP_SCALE) {
@@ -668,7 +763,8 @@ static bool graph_fits_plan(const exec_plan & plan, struct ggml_cgraph * g) {
                 }
                 cur = t;
             }
-            if (it.store_f16 && (out->op != GGML_OP_CPY || out->src[0] != cur || out->type != GGML_TYPE_F16)) return false;
+            if (it.store_f16 && (out->op != GGML_OP_CPY || out->src[0] != cur || out->type != GGML_TYPE_F16 || !ggml_is_contiguous(out) ||
+                                 !ggml_is_contiguous(cur) || ggml_nelements(out) != node->ne[0] * node->ne[1])) return false;
             // GEMV: every CTA reads the activations for the whole kernel, the result must not land on them
             // (the GEMM path reads a quantised copy made before the product starts)
             if (it.kind == PK_GEMV && it.last != it.node && overlaps(out, node->src[1])) return false;
@@ -759,10 +855,8 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
         // Rows of several states go to a product next (5..32 columns: the quantised-column path): the same kernel also
         // leaves them quantised in the column buffer, marked as written by this item so that the product reuses them.
         static const bool fuse_q = getenv("GGML_B200_NO_FUSION") == nullptr;
-        if (fuse_q && !launched_rows && n_rows > 4 && n_rows <= 32 && ne00 % 32 == 0 && ne00 <= COLQ_MAX_K) {
-            int8_t * xq = (int8_t *) ctx->colq;
-            float *  xd = (float *) ((char *) ctx->colq + (size_t) 32 * COLQ_MAX_K);
-            const int e = b200_layer_norm_rows_q(rows, n_rows, gamma, beta, ne00, eps, xq, xd, st);
+        if (fuse_q && !launched_rows && n_rows > 4 && n_rows <= COLQ_MAX_COLS && ne00 % 32 == 0 && ne00 <= COLQ_MAX_K) {
+            const int e = b200_layer_norm_rows_q(rows, n_rows, gamma, beta, ne00, eps, colq_q(ctx), colq_d(ctx), st);
             ctx->colq_ptrs.resize(n_rows);
             for (int i = 0; i < n_rows; ++i) ctx->colq_ptrs[i] = rows[i].y;
             ctx->colq_K = ne00;
@@ -783,11 +877,15 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
             ep.kind[s] = it.step_kind[s];
             if (it.step_kind[s] == B200_EP_SCALE) memcpy(&ep.scalar[s], ggml_graph_node(gs[0], it.step_node[s])->op_params, sizeof(float));
         }
-        b200_gemv_col cols[32];
-        const float * xs[32];
+        b200_gemv_col cols[COLQ_MAX_COLS];
+        const float * xs[COLQ_MAX_COLS];
         int n_cols = 0;
-        int8_t * xq = (int8_t *) ctx->colq;
-        float *  xd = (float *) ((char *) ctx->colq + (size_t) 32 * COLQ_MAX_K);
+        int8_t * xq = colq_q(ctx);
+        float *  xd = colq_d(ctx);
+        // products of this many columns or more go to the tcgen05 kernel (one launch for up to 64 columns, time nearly
+        // independent of the column count); fewer columns stay with the FMA-pipe kernels that stream the weights once
+        static const int tc_min_cols = getenv("GGML_B200_TC_MIN_COLS") ? atoi(getenv("GGML_B200_TC_MIN_COLS")) : 24;
+        static const bool use_tc = getenv("GGML_B200_NO_TC") == nullptr;
         auto flush = [&]() -> int {
             if (!n_cols) return 0;
             int e = 0;
@@ -799,17 +897,22 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
                 const bool reuse = ctx->colq_seq + 1 == ctx->item_seq && ctx->colq_K == K && (int) ctx->colq_ptrs.size() == n_cols &&
                                    memcmp(ctx->colq_ptrs.data(), xs, sizeof(xs[0]) * n_cols) == 0;
                 if (!reuse) {
-                    e = b200_quantize_cols(xs, n_cols, K, xq, xd, st);
+                    for (int c0 = 0; c0 < n_cols && !e; c0 += 32)
+                        e = b200_quantize_cols(xs + c0, n_cols - c0 < 32 ? n_cols - c0 : 32, K, xq + (size_t) c0 * K, xd + (size_t) c0 * (K / 32), st);
                     if (e) return e;
                     ctx->colq_ptrs.assign(xs, xs + n_cols);
                     ctx->colq_K = K;
                 }
                 ctx->colq_seq = ctx->item_seq;
-                // shared memory holds the quantised columns next to the weight rows: fewer columns per launch for long rows
-                const int cap = K > 2560 ? 16 : 32;
-                for (int c0 = 0; c0 < n_cols && !e; c0 += cap)
-                    e = b200_mul_mat_cols_q((int) w->type, w->data, nb_total, M, K, xq + (size_t) c0 * K, xd + (size_t) c0 * (K / 32), cols + c0,
-                                            n_cols - c0 < cap ? n_cols - c0 : cap, &ep, st);
+                if (use_tc && n_cols >= tc_min_cols) {
+                    e = b200_mul_mat_tc_cols((int) w->type, w->data, nb_total, M, K, xq, xd, cols, n_cols, &ep, st);
+                } else {
+                    // shared memory holds the quantised columns next to the weight rows: fewer columns per launch for long rows
+                    const int cap = K > 2560 ? 16 : 32;
+                    for (int c0 = 0; c0 < n_cols && !e; c0 += cap)
+                        e = b200_mul_mat_cols_q((int) w->type, w->data, nb_total, M, K, xq + (size_t) c0 * K, xd + (size_t) c0 * (K / 32), cols + c0,
+                                                n_cols - c0 < cap ? n_cols - c0 : cap, &ep, st);
+                }
             } else {
                 for (int c0 = 0; c0 < n_cols && !e; c0 += 8)
                     e = b200_mul_mat_vec_q_cols((int) w->type, w->data, nb_total, M, K, cols + c0, n_cols - c0 < 8 ? n_cols - c0 : 8, &ep, st);
@@ -833,7 +936,7 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
             const struct ggml_tensor * x = mm->src[1];
             const int64_t out_stride = it.store_f16 ? mm->ne[0] * 2 : (int64_t) out->nb[1];
             for (int64_t c = 0; c < x->ne[1]; ++c) {
-                if (n_cols == 32) { const int e = flush(); if (e) return e; ++n_flushes; ctx->colq_seq = -2; }
+                if (n_cols == COLQ_MAX_COLS) { const int e = flush(); if (e) return e; ++n_flushes; ctx->colq_seq = -2; }
                 b200_gemv_col & col = cols[n_cols];
                 memset(&col, 0, sizeof(col));
                 col.x = (const float *) ((const char *) x->data + c * x->nb[1]);
@@ -882,29 +985,32 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
         const struct ggml_tensor * q0 = n0->src[0], * k0 = n0->src[1], * v0 = n0->src[2];
         float scale;
         memcpy(&scale, (const float *) n0->op_params + 0, sizeof(float));
-        b200_fa_row rows[32];
+        b200_fa_row rows[COLQ_MAX_COLS];
         int n_rows = 0;
         static const bool fuse_q = getenv("GGML_B200_NO_FUSION") == nullptr;
         int n_launches = 0;
         bool last = false;
         auto flush = [&]() -> int {
             if (!n_rows) return 0;
-            int e;
-            // A single launch that covers all rows, followed by the output projection (5..32 columns: the quantised-column
-            // path): the kernel also leaves the rows quantised in the column buffer, marked as written by this item.
+            int e = 0;
+            // One flush that covers all rows, followed by the output projection (5..64 columns: the quantised-column path):
+            // the kernel also leaves the rows quantised in the column buffer, marked as written by this item.
             const int64_t kk = q0->ne[2] * 64;
-            if (fuse_q && last && n_launches == 0 && n_rows > 4 && kk <= COLQ_MAX_K && q0->ne[0] == 64) {
-                int8_t * xq = (int8_t *) ctx->colq;
-                float *  xd = (float *) ((char *) ctx->colq + (size_t) 32 * COLQ_MAX_K);
-                e = b200_flash_attn_decode_rows_q(rows, n_rows, q0->ne[2], (int64_t) q0->nb[2], (int64_t) k0->nb[1], (int64_t) k0->nb[2],
-                                                  (int64_t) v0->nb[1], (int64_t) v0->nb[2], scale, xq, xd, st);
+            const bool with_q = fuse_q && last && n_launches == 0 && n_rows > 4 && kk <= COLQ_MAX_K && q0->ne[0] == 64;
+            for (int r0 = 0; r0 < n_rows && !e; r0 += 32) {
+                const int n = n_rows - r0 < 32 ? n_rows - r0 : 32;
+                if (with_q)
+                    e = b200_flash_attn_decode_rows_q(rows + r0, n, q0->ne[2], (int64_t) q0->nb[2], (int64_t) k0->nb[1], (int64_t) k0->nb[2],
+                                                      (int64_t) v0->nb[1], (int64_t) v0->nb[2], scale, colq_q(ctx) + (size_t) r0 * kk, colq_d(ctx) + (size_t) r0 * (kk / 32), st);
+                else
+                    e = b200_flash_attn_decode_rows(rows + r0, n, q0->ne[2], (int64_t) q0->nb[2], (int64_t) k0->nb[1], (int64_t) k0->nb[2],
+                                                    (int64_t) v0->nb[1], (int64_t) v0->nb[2], scale, st);
+            }
+            if (with_q && !e) {
                 ctx->colq_ptrs.resize(n_rows);
                 for (int i = 0; i < n_rows; ++i) ctx->colq_ptrs[i] = rows[i].dst;
                 ctx->colq_K = kk;
                 ctx->colq_seq = ctx->item_seq;
-            } else {
-                e = b200_flash_attn_decode_rows(rows, n_rows, q0->ne[2], (int64_t) q0->nb[2], (int64_t) k0->nb[1], (int64_t) k0->nb[2],
-                                                (int64_t) v0->nb[1], (int64_t) v0->nb[2], scale, st);
             }
             ++n_launches;
             n_rows = 0;
@@ -928,7 +1034,7 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
                 continue;
             }
             for (int64_t r = 0; r < q->ne[1]; ++r) {
-                if (n_rows == 32) { const int e = flush(); if (e) return e; }
+                if (n_rows == COLQ_MAX_COLS) { const int e = flush(); if (e) return e; }
                 rows[n_rows].q    = (const float *) ((const char *) q->data + r * q->nb[1]);
                 rows[n_rows].k    = k->data;
                 rows[n_rows].v    = v->data;
@@ -995,8 +1101,13 @@ static int run_gemv_group(b200_backend_ctx * ctx, const plan_item * its, int n_i
         if (i == 0) n_cols = nc; else if (nc != n_cols) return -1;
     }
     if (n_cols <= 4) return -1;
-    int8_t * xq = (int8_t *) ctx->colq;
-    float *  xd = (float *) ((char *) ctx->colq + (size_t) 32 * COLQ_MAX_K);
+    {   // many columns: each product is one tcgen05 launch of its own (run_item)
+        static const int tc_min_cols = getenv("GGML_B200_TC_MIN_COLS") ? atoi(getenv("GGML_B200_TC_MIN_COLS")) : 24;
+        static const bool use_tc = getenv("GGML_B200_NO_TC") == nullptr;
+        if (use_tc && n_cols >= tc_min_cols) return -1;
+    }
+    int8_t * xq = colq_q(ctx);
+    float *  xd = colq_d(ctx);
     const bool reuse = ctx->colq_seq + 1 == ctx->item_seq && ctx->colq_K == K && (int) ctx->colq_ptrs.size() == n_cols &&
                        memcmp(ctx->colq_ptrs.data(), xs, sizeof(xs[0]) * n_cols) == 0;
     if (!reuse) {
@@ -1012,6 +1123,42 @@ static int run_gemv_group(b200_backend_ctx * ctx, const plan_item * its, int n_i
 
 static bool is_noop(enum ggml_op op) {
     return op == GGML_OP_NONE || op == GGML_OP_RESHAPE || op == GGML_OP_VIEW || op == GGML_OP_PERMUTE || op == GGML_OP_TRANSPOSE;
+}
+
+// The logits product is the last node of a decoder graph (src/whisper.cpp:2830, 2953).  With the side output switched
+// on, every logits row of every graph of the group gets its top-k / max / log-sum-exp written into the device buffer of
+// the backend instance the graph belongs to (owners[g]), by one launch on the stream that ran the plan.
+static int logits_side_output(b200_backend_ctx * ctx, struct ggml_cgraph * const * gs, b200_backend_ctx * const * owners, int n_g) {
+    const int k = g_topk_k.load(std::memory_order_relaxed);
+    const float * rows[64];
+    b200_topk_result * outs[64];
+    int n_rows = 0;
+    int64_t n_vocab = 0;
+    for (int g = 0; g < n_g; ++g) {
+        struct ggml_tensor * t = ggml_graph_node(gs[g], -1);
+        owners[g]->topk_rows = 0;
+        if (t->op != GGML_OP_MUL_MAT || t->type != GGML_TYPE_F32 || t->ne[0] < 1024 || t->ne[1] > 8 || t->ne[2] != 1 || t->ne[3] != 1 || t->nb[0] != 4) continue;
+        {
+            std::lock_guard<std::mutex> lk(g_logits_mu);
+            if (g_logits_ptrs.size() > 4096) g_logits_ptrs.clear();
+            g_logits_ptrs[t->data] = 1;
+        }
+        if (k <= 0 || !owners[g]->topk) continue;
+        if (n_vocab == 0) n_vocab = t->ne[0];
+        if (t->ne[0] != n_vocab) continue;
+        for (int64_t c = 0; c < t->ne[1]; ++c) {
+            if (n_rows == 64) {
+                const int e = b200_topk_rows(rows, outs, n_rows, n_vocab, k, (void *) ctx->stream);
+                if (e) return e;
+                n_rows = 0;
+            }
+            rows[n_rows] = (const float *) ((const char *) t->data + c * t->nb[1]);
+            outs[n_rows] = owners[g]->topk + c;
+            ++n_rows;
+        }
+        owners[g]->topk_rows = (int) t->ne[1];
+    }
+    return n_rows ? b200_topk_rows(rows, outs, n_rows, n_vocab, k, (void *) ctx->stream) : 0;
 }
 
 static int run_plan(b200_backend_ctx * ctx, const exec_plan & plan, struct ggml_cgraph * const * gs, int n_g, bool timing,
@@ -1158,8 +1305,10 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
         ++n_compute;
     }
 
+    const bool decode_graph = is_decode_graph(cgraph);
+    if (decode_graph) tl_last_decode_ctx = ctx;      // b200_last_topk answers for the state this thread stepped last
     // ---- batched path -------------------------------------------------------------------------
-    if (batching && fuse && B.alive > 1 && is_decode_graph(cgraph)) {
+    if (batching && fuse && B.alive > 1 && decode_graph) {
         batch_req req = { ctx, cgraph, graph_signature(cgraph), 0, nullptr, 0 };
         const int64_t t_arrive = now_ns();
         ctx->last_decode_ns = t_arrive;
@@ -1255,6 +1404,12 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
                 std::vector<int>    bt_class;
                 std::vector<double> bt_work;
                 rc = run_plan(ctx, plan_copy, gs.data(), (int) gs.size(), timing, &bt_class, &bt_work, &n_ev);
+                if (rc == 0 && (g_topk_k.load() > 0 || g_skip_logits_readback.load())) {
+                    std::vector<b200_backend_ctx *> owners;
+                    owners.push_back(ctx);
+                    for (batch_req * r : served) owners.push_back(r->ctx);
+                    rc = logits_side_output(ctx, gs.data(), owners.data(), (int) gs.size());
+                }
                 g_ns_lead_launch += now_ns() - t_l0;
                 if (rc == 0 && timing && !bt_class.empty() && cudaStreamSynchronize(ctx->stream) == cudaSuccess) {
                     std::lock_guard<std::mutex> tl(g_timing_mu);
@@ -1318,7 +1473,11 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
     std::vector<double> t_work;
     size_t n_ev = 0;
     struct ggml_cgraph * one[1] = { cgraph };
-    const int e = run_plan(ctx, plan, one, 1, timing, &t_class, &t_work, &n_ev);
+    int e = run_plan(ctx, plan, one, 1, timing, &t_class, &t_work, &n_ev);
+    if (e == 0 && decode_graph && (g_topk_k.load() > 0 || g_skip_logits_readback.load())) {
+        b200_backend_ctx * owner[1] = { ctx };
+        e = logits_side_output(ctx, one, owner, 1);
+    }
     if (e != 0) return finish_status(e);
     g_nodes_computed += n_compute;
     g_graphs_computed += 1;
@@ -1387,10 +1546,11 @@ static ggml_backend_t b200_dev_init_backend(ggml_backend_dev_t dev, const char *
     ctx->device = dctx->device;
     ctx->name   = dctx->name;
     if (!cuda_ok(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking), "cudaStreamCreate")) { delete ctx; return nullptr; }
-    if (!cuda_ok(cudaMalloc(&ctx->colq, (size_t) 32 * COLQ_MAX_K + (size_t) 32 * (COLQ_MAX_K / 32) * 4), "cudaMalloc(colq)")) {
+    if (!cuda_ok(cudaMalloc(&ctx->colq, (size_t) COLQ_MAX_COLS * COLQ_MAX_K + (size_t) COLQ_MAX_COLS * (COLQ_MAX_K / 32) * 4), "cudaMalloc(colq)")) {
         cudaStreamDestroy(ctx->stream); delete ctx; return nullptr;
     }
     if (cudaEventCreateWithFlags(&ctx->sync_event, cudaEventBlockingSync | cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); ctx->sync_event = nullptr; }
+    if (cudaMalloc((void **) &ctx->topk, 8 * sizeof(b200_topk_result)) != cudaSuccess) { cudaGetLastError(); ctx->topk = nullptr; }
     batcher_join(ctx);
     return new ggml_backend{ b200_guid(), b200_backend_iface, dev, ctx };
 }
@@ -1513,8 +1673,28 @@ static struct ggml_backend_feature * b200_get_features(ggml_backend_reg_t) {
     return features;
 }
 
+extern "C" {
+GGML_BACKEND_API void b200_logits_side_output(int top_k, int skip_readback) {
+    g_topk_k = top_k < 0 ? 0 : (top_k > B200_TOPK_MAX ? B200_TOPK_MAX : top_k);
+    g_skip_logits_readback = (skip_readback != 0 && top_k > 0) ? 1 : 0;
+}
+GGML_BACKEND_API int b200_last_topk(int row, b200_topk_result * out) {
+    b200_backend_ctx * ctx = tl_last_decode_ctx;
+    if (!ctx || !out || !ctx->topk || row < 0 || row >= ctx->topk_rows) return B200_ERR_ARG;
+    if (cudaSetDevice(ctx->device) != cudaSuccess) return (int) cudaGetLastError();
+    // the side output was enqueued on the stream that ran the graph; this instance's stream is ordered behind it
+    cudaError_t e = cudaMemcpyAsync(out, ctx->topk + row, sizeof(*out), cudaMemcpyDeviceToHost, ctx->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e != cudaSuccess) { cudaGetLastError(); return (int) e; }
+    g_d2h_bytes += (int64_t) sizeof(*out);
+    return 0;
+}
+}
+
 static void * b200_reg_get_proc_address(ggml_backend_reg_t, const char * name) {
     if (strcmp(name, "ggml_backend_get_features") == 0) return (void *) b200_get_features;
+    if (strcmp(name, "b200_logits_side_output") == 0) return (void *) b200_logits_side_output;
+    if (strcmp(name, "b200_last_topk") == 0)          return (void *) b200_last_topk;
     if (strcmp(name, "b200_stat_nodes") == 0)  return (void *) b200_stat_nodes;
     if (strcmp(name, "b200_stat_graphs") == 0) return (void *) b200_stat_graphs;
     if (strcmp(name, "b200_stat_h2d") == 0)    return (void *) b200_stat_h2d;

@@ -69,8 +69,10 @@ __device__ __forceinline__ float expf_glibc(float x, const uint64_t * tab) {
 // query tells each key the running maximum it meets, exp() runs in parallel, then the 64-wide F16 accumulators
 // (two dims per lane, FA_R independent chains) are updated key by key.  HAS_SKIP = a mask is present or the key count
 // is not a multiple of 32; without it the per-key "skipped" handling is compiled out.
+// RELAXED (measurement switch GGML_B200_RELAXED=1, off by default): what a tensor-core attention would do instead - the
+// softmax weights rounded to F16 once, the V accumulator kept in f32 - to measure how far that moves the model outputs.
 #define FA_R 4
-template <bool S_FMA, bool HAS_SKIP>
+template <bool S_FMA, bool HAS_SKIP, bool RELAXED>
 __global__ void __launch_bounds__(128, 5)
 k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
                  const char * __restrict__ k, int64_t nbk1, int64_t nbk2,
@@ -208,8 +210,11 @@ k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
                         float vx = vf.x, vy = vf.y;
                         if (HAS_SKIP && __float_as_uint(vs) == 0x80000000u) { vx = 0.0f; vy = 0.0f; }    // skipped key: exact no-op
                         S[r] = __fadd_rn(S[r], vs);          // ms == 1: fma(S, 1, vs) == S + vs
-                        const float2 t = __half22float2(__floats2half2_rn(__fmaf_rn(vx, vs, a0[r]), __fmaf_rn(vy, vs, a1[r])));
-                        a0[r] = t.x; a1[r] = t.y;
+                        if (RELAXED) { const float p = round_f16(vs); a0[r] = __fmaf_rn(vx, p, a0[r]); a1[r] = __fmaf_rn(vy, p, a1[r]); }
+                        else {
+                            const float2 t = __half22float2(__floats2half2_rn(__fmaf_rn(vx, vs, a0[r]), __fmaf_rn(vy, vs, a1[r])));
+                            a0[r] = t.x; a1[r] = t.y;
+                        }
                     }
                 }
                 return;
@@ -228,15 +233,21 @@ k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
                     if (HAS_SKIP && __float_as_uint(vs) == 0x80000000u) { vx = 0.0f; vy = 0.0f; }
                     if ((evt_any >> r) & 1u) {
                         if (ms != 1.0f) {
-                            const float2 t = __half22float2(__floats2half2_rn(__fmul_rn(a0[r], ms), __fmul_rn(a1[r], ms)));
-                            a0[r] = t.x; a1[r] = t.y;
+                            if (RELAXED) { a0[r] = __fmul_rn(a0[r], ms); a1[r] = __fmul_rn(a1[r], ms); }
+                            else {
+                                const float2 t = __half22float2(__floats2half2_rn(__fmul_rn(a0[r], ms), __fmul_rn(a1[r], ms)));
+                                a0[r] = t.x; a1[r] = t.y;
+                            }
                         }
                         S[r] = S_FMA ? __fmaf_rn(S[r], ms, vs) : __fadd_rn(__fmul_rn(S[r], ms), vs);
                     } else {
                         S[r] = __fadd_rn(S[r], vs);
                     }
-                    const float2 t = __half22float2(__floats2half2_rn(__fmaf_rn(vx, vs, a0[r]), __fmaf_rn(vy, vs, a1[r])));
-                    a0[r] = t.x; a1[r] = t.y;
+                    if (RELAXED) { const float p = round_f16(vs); a0[r] = __fmaf_rn(vx, p, a0[r]); a1[r] = __fmaf_rn(vy, p, a1[r]); }
+                    else {
+                        const float2 t = __half22float2(__floats2half2_rn(__fmaf_rn(vx, vs, a0[r]), __fmaf_rn(vy, vs, a1[r])));
+                        a0[r] = t.x; a1[r] = t.y;
+                    }
                 }
             }
         };
@@ -900,10 +911,12 @@ extern "C" int b200_flash_attn_ext(const float * q, int64_t nbq1, int64_t nbq2,
     }
     dim3 grid((unsigned) ((n_q + 4 * FA_R - 1) / (4 * FA_R)), (unsigned) n_head);
     const bool has_skip = mask != nullptr || (n_kv % 32) != 0;
-#define FA_LAUNCH(SF, HS) k_flash_attn_ext<SF, HS><<<grid, 128, 0, as_stream(stream)>>>((const char *) q, nbq1, nbq2, (const char *) k, nbk1, nbk2, \
+    static const bool relaxed = getenv("GGML_B200_RELAXED") != nullptr && atoi(getenv("GGML_B200_RELAXED")) != 0;
+#define FA_LAUNCH(SF, HS, RX) k_flash_attn_ext<SF, HS, RX><<<grid, 128, 0, as_stream(stream)>>>((const char *) q, nbq1, nbq2, (const char *) k, nbk1, nbk2, \
             (const char *) v, nbv1, nbv2, (const char *) mask, nbm1, dst, n_q, n_kv, n_head, scale)
-    if (g_fa_s_fma) { if (has_skip) FA_LAUNCH(true, true); else FA_LAUNCH(true, false); }
-    else            { if (has_skip) FA_LAUNCH(false, true); else FA_LAUNCH(false, false); }
+    if (relaxed)         { if (has_skip) FA_LAUNCH(true, true, true); else FA_LAUNCH(true, false, true); }
+    else if (g_fa_s_fma) { if (has_skip) FA_LAUNCH(true, true, false); else FA_LAUNCH(true, false, false); }
+    else                 { if (has_skip) FA_LAUNCH(false, true, false); else FA_LAUNCH(false, false, false); }
 #undef FA_LAUNCH
     B200_RETURN_LAST();
 }

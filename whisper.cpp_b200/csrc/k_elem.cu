@@ -366,3 +366,81 @@ extern "C" int b200_concat(const float * a, const int64_t * nea, const int64_t *
     k_concat<<<(unsigned) ((n + 255) / 256), 256, 0, as_stream(stream)>>>((const char *) a, da, (const char *) b, db, (char *) dst, dd, dim, n);
     B200_RETURN_LAST();
 }
+
+// ---- top-k of logits rows ------------------------------------------------------------------------
+// The host sampler of whisper.cpp reads every row of logits back and scans it (whisper_process_logits /
+// whisper_sample_token, src/whisper.cpp:5015-5430; greedy = first index of the maximum).  This kernel leaves, per
+// row, the k largest values with their indices (ties: lower index first, as a forward scan with `>` finds them), the
+// maximum and log(sum(exp(x - max))) + max, so that a caller that only needs those can skip the 200 KB row.
+// One CTA per row; k passes, each a block-wide arg-max over the values not yet taken (the row stays in L2).
+#define TOPK_THREADS 512
+struct TopkRows { const float * row[64]; b200_topk_result * out[64]; };
+
+__device__ __forceinline__ bool topk_better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
+__global__ void __launch_bounds__(TOPK_THREADS)
+k_topk_rows(TopkRows rows, int n, int k) {
+    chain_release();
+    chain_wait();
+    __shared__ float s_v[TOPK_THREADS / 32];
+    __shared__ int   s_i[TOPK_THREADS / 32];
+    __shared__ double s_d[TOPK_THREADS / 32];
+    __shared__ int   taken[B200_TOPK_MAX];
+    __shared__ float best_v;
+    const float * x = rows.row[blockIdx.x];
+    b200_topk_result * out = rows.out[blockIdx.x];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (int r = 0; r < k; ++r) {
+        float bv = -INFINITY;
+        int   bi = 0x7fffffff;
+        for (int i = tid; i < n; i += TOPK_THREADS) {
+            const float v = x[i];
+            bool skip = false;
+            for (int t = 0; t < r; ++t) skip |= (taken[t] == i);
+            if (!skip && (topk_better(v, i, bv, bi) || bi == 0x7fffffff)) { bv = v; bi = i; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int   oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi != 0x7fffffff && (bi == 0x7fffffff || topk_better(ov, oi, bv, bi))) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) { s_v[warp] = bv; s_i[warp] = bi; }
+        __syncthreads();
+        if (tid == 0) {
+            for (int w = 1; w < TOPK_THREADS / 32; ++w)
+                if (s_i[w] != 0x7fffffff && (bi == 0x7fffffff || topk_better(s_v[w], s_i[w], bv, bi))) { bv = s_v[w]; bi = s_i[w]; }
+            taken[r] = bi;
+            out->ids[r] = bi == 0x7fffffff ? -1 : bi;
+            out->vals[r] = bv;
+            if (r == 0) { best_v = bv; out->max = bv; }
+        }
+        __syncthreads();
+    }
+    // log-sum-exp around the maximum, accumulated in double
+    const float mx = best_v;
+    double s = 0.0;
+    for (int i = tid; i < n; i += TOPK_THREADS) s += exp((double) x[i] - (double) mx);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) s_d[warp] = s;
+    __syncthreads();
+    if (tid == 0) {
+        for (int w = 1; w < TOPK_THREADS / 32; ++w) s += s_d[w];
+        out->logsumexp = (float) (log(s) + (double) mx);
+        out->n = n; out->k = k;
+    }
+}
+
+extern "C" int b200_topk_rows(const float * const * rows, b200_topk_result * const * out, int n_rows, int64_t n, int k, void * stream) {
+    if (n_rows <= 0) return 0;
+    if (n_rows > 64 || n <= 0 || n > 0x7ffffff0 || k < 1 || k > B200_TOPK_MAX || !rows || !out) return B200_ERR_ARG;
+    TopkRows r;
+    for (int i = 0; i < n_rows; ++i) {
+        if (!rows[i] || !out[i]) return B200_ERR_ARG;
+        r.row[i] = rows[i]; r.out[i] = out[i];
+    }
+    const cudaError_t e = launch_chained(k_topk_rows, dim3((unsigned) n_rows), dim3(TOPK_THREADS), 0, as_stream(stream), r, (int) n, k);
+    if (e != cudaSuccess) return (int) e;
+    B200_RETURN_LAST();
+}
