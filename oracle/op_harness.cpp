@@ -210,4 +210,45 @@ int64_t oph_run(const char * dev_name, int op, const int64_t * p, const float * 
     return written;
 }
 
+
+// Error paths of a backend device (no abort, an error value instead):
+//  oph_try_alloc: 1 if the device's buffer type hands out a buffer of `size` bytes (freed again), 0 if it returns NULL.
+int oph_try_alloc(const char * dev_name, int64_t size) {
+    ggml_backend_dev_t dev = ggml_backend_dev_by_name(dev_name);
+    if (!dev) return -1;
+    ggml_backend_buffer_t buf = ggml_backend_buft_alloc_buffer(ggml_backend_dev_buffer_type(dev), (size_t) size);
+    if (!buf) return 0;
+    ggml_backend_buffer_free(buf);
+    return 1;
+}
+
+//  oph_unsupported_status: ggml_status of graph_compute for a graph that holds an operator the device does not support
+//  (ggml_sqr), handed to the backend directly, past the scheduler that would never send it there.  -1/-2: set-up failed,
+//  -3: the device claims to support the operator.
+int oph_unsupported_status(const char * dev_name) {
+    ggml_backend_t backend = init_backend(dev_name, 1);
+    if (!backend) return -1;
+    struct ggml_init_params ip = { ggml_tensor_overhead() * 8 + ggml_graph_overhead(), nullptr, true };
+    ggml_context * ctx = ggml_init(ip);
+    ggml_tensor * a = ggml_new_tensor_1d(ctx, GGML_TYPE_F32, 64);
+    ggml_tensor * r = ggml_sqr(ctx, a);
+    int rc;
+    if (ggml_backend_dev_supports_op(ggml_backend_get_device(backend), r)) {
+        rc = -3;
+    } else {
+        ggml_backend_buffer_t buf = ggml_backend_alloc_ctx_tensors(ctx, backend);
+        if (!buf) {
+            rc = -2;
+        } else {
+            ggml_cgraph * g = ggml_new_graph(ctx);
+            ggml_build_forward_expand(g, r);
+            rc = (int) ggml_backend_graph_compute(backend, g);
+            ggml_backend_buffer_free(buf);
+        }
+    }
+    ggml_free(ctx);
+    ggml_backend_free(backend);
+    return rc;
+}
+
 }

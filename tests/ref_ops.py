@@ -35,6 +35,8 @@ def lib():
         _lib.oph_dequantize.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64]
         _lib.oph_cpu_from_float.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64]
         _lib.oph_load_backend.argtypes = [C.c_char_p]
+        _lib.oph_try_alloc.argtypes = [C.c_char_p, C.c_int64]
+        _lib.oph_unsupported_status.argtypes = [C.c_char_p]
     return _lib
 
 

@@ -109,3 +109,19 @@ def test_static_scratch_entry_point_rejects_bad_arguments_without_a_device(pkg):
     assert call(nb=i64(64)) == 10001                       # weight tensor smaller than M x K
     assert call(N=i64(1 << 60)) == 10003                   # absurd N: too large, and no overflow on the way
     assert call(K=i64(48)) == 10001
+
+
+@pytest.mark.skipif(not R.have_ref(), reason="reference build (oracle/_ref) missing")
+def test_truncated_model_file_fails_cleanly(pkg, tmp_path):
+    """A model file cut off in the middle of its tensors makes whisper_init_* return NULL (the loader's own checks,
+    src/whisper.cpp:1874-1960); the harness turns that into an exception, nothing crashes."""
+    good = tmp_path / "tiny.bin"
+    pkg.synth.write_model(str(good), "tiny", "q5_0", seed=0)
+    data = good.read_bytes()
+    bad = tmp_path / "cut.bin"
+    bad.write_bytes(data[: len(data) // 2])
+    with pytest.raises(RuntimeError):
+        pkg.Whisper(str(bad), use_gpu=False)
+    bad.write_bytes(data[: len(data) * 3 // 4 + 5])          # cut inside a tensor's data
+    with pytest.raises(RuntimeError):
+        pkg.Whisper(str(bad), use_gpu=False)

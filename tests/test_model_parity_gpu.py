@@ -370,3 +370,20 @@ def test_logits_side_output_equals_host_scan(pkg, model_dir):
     finally:
         H.logits_side_output(0, probe=True)
         gpu.close()
+
+
+def test_tcgen05_product_at_model_level(pkg, model_dir):
+    """The tcgen05 / tensor-memory form of the many-column product is opt-in (GGML_B200_TC=1, read once per process): with it
+    a whole tiny model - encoder, cross K/V and prompt products all go through it - is still bit-identical to the reference
+    CPU backend.  Runs tests/relaxed_drift.py in a process of its own and reads its exact-arithmetic leg."""
+    import json
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, GGML_B200_TC="1", B200_MODEL_DIR=model_dir)
+    r = subprocess.run([sys.executable, os.path.join(here, "relaxed_drift.py"), "tiny", "q5_0", "8"], env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    res = json.loads([ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1])
+    exact = res["plugin_exact"]
+    assert "error" not in exact, exact
+    assert exact["encoder_rel_l2"] == 0.0 and exact["logits_max_rel"] == 0.0 and exact["first_free_running_divergence"] is None, exact

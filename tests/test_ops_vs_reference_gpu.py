@@ -197,3 +197,16 @@ def test_nonflash_pv(n_q, n_kv, H):
     p = np.abs(rnd(29, H, n_q, n_kv))
     a, b = both("KQV_NOFA", [n_q, n_kv, H, n_ctx], inputs=[v, p], out_shape=(H, n_q, 64))
     assert_bits(a, b, "non-flash PV")
+
+
+def test_error_paths_return_values_instead_of_aborting():
+    """An allocation the device cannot satisfy comes back as a NULL buffer, and a graph with an operator the plugin does
+    not implement comes back as a failed status (the scheduler never sends one; here it is handed over directly) - the
+    process keeps running in both cases, and ordinary work still succeeds afterwards."""
+    assert R.load_plugin() > 0
+    L = R.lib()
+    assert L.oph_try_alloc(b"B200_0", 1 << 20) == 1
+    assert L.oph_try_alloc(b"B200_0", 1 << 46) == 0          # 64 TiB: cudaMalloc fails, alloc_buffer returns NULL
+    st = L.oph_unsupported_status(b"B200_0")
+    assert st not in (0, -1, -2, -3), f"graph_compute returned {st} for an unsupported operator"
+    assert L.oph_try_alloc(b"B200_0", 1 << 20) == 1          # the device is still usable

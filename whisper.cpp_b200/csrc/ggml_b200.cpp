@@ -35,6 +35,16 @@ static bool cuda_ok(cudaError_t e, const char * what) {
 
 static bool is_quant(enum ggml_type t) { return t == GGML_TYPE_Q5_0 || t == GGML_TYPE_Q8_0; }
 
+// The buffer interface has no way to report a failed copy (set_tensor / get_tensor return void).  A failure is logged,
+// remembered, and the next graph_compute on that device returns GGML_STATUS_FAILED instead of computing on bad data;
+// the process is never aborted for it.
+static std::atomic<int> g_sticky_error[16];
+static void note_buffer_error(int device, const char * what) {
+    fprintf(stderr, "ggml-b200: %s failed on device %d; the next graph_compute on it reports GGML_STATUS_FAILED\n", what, device);
+    if (device >= 0 && device < 16) g_sticky_error[device] = 1;
+}
+extern "C" int b200_stat_sticky_error(int device) { return device >= 0 && device < 16 ? g_sticky_error[device].load() : 0; }
+
 // ---------------------------------------------------------------------------------------------
 // statistics (exposed through get_proc_address for tests and the benchmark)
 // ---------------------------------------------------------------------------------------------
@@ -167,13 +177,13 @@ static void b200_buffer_set_tensor(ggml_backend_buffer_t buffer, struct ggml_ten
         } else {
             ok = ok && cuda_ok(cudaMemcpyAsync(base + 32 * nb_total + 2 * first, d.data(), d.size(), cudaMemcpyHostToDevice, st), "set_tensor d");
         }
-        cuda_ok(cudaStreamSynchronize(st), "set_tensor sync");
-        GGML_ASSERT(ok);
+        ok = cuda_ok(cudaStreamSynchronize(st), "set_tensor sync") && ok;
+        if (!ok) note_buffer_error(ctx->device, "set_tensor");
         return;
     }
     bool ok = cuda_ok(cudaMemcpyAsync((char *) tensor->data + offset, data, size, cudaMemcpyHostToDevice, cudaStreamPerThread), "set_tensor");
     ok = ok && cuda_ok(cudaStreamSynchronize(cudaStreamPerThread), "set_tensor sync");
-    GGML_ASSERT(ok);
+    if (!ok) note_buffer_error(ctx->device, "set_tensor");
 }
 
 static void b200_buffer_get_tensor(ggml_backend_buffer_t buffer, const struct ggml_tensor * tensor, void * data, size_t offset, size_t size) {
@@ -202,7 +212,7 @@ static void b200_buffer_get_tensor(ggml_backend_buffer_t buffer, const struct gg
             ok = ok && cuda_ok(cudaMemcpyAsync(d.data(), base + 32 * nb_total + 2 * first, d.size(), cudaMemcpyDeviceToHost, st), "get_tensor d");
         }
         ok = ok && cuda_ok(cudaStreamSynchronize(st), "get_tensor sync");
-        GGML_ASSERT(ok);
+        if (!ok) { note_buffer_error(ctx->device, "get_tensor"); memset(data, 0, size); return; }
         uint8_t * dst = (uint8_t *) data;
         for (int64_t i = 0; i < count; ++i) {
             uint8_t * b = dst + bs * i;
@@ -218,7 +228,7 @@ static void b200_buffer_get_tensor(ggml_backend_buffer_t buffer, const struct gg
     }
     bool ok = cuda_ok(cudaMemcpyAsync(data, (const char *) tensor->data + offset, size, cudaMemcpyDeviceToHost, cudaStreamPerThread), "get_tensor");
     ok = ok && cuda_ok(cudaStreamSynchronize(cudaStreamPerThread), "get_tensor sync");
-    GGML_ASSERT(ok);
+    if (!ok) { note_buffer_error(ctx->device, "get_tensor"); memset(data, 0, size); }
 }
 
 static void b200_buffer_clear(ggml_backend_buffer_t buffer, uint8_t value) {
@@ -380,7 +390,9 @@ static bool mma_weights_of(b200_backend_ctx * ctx, const struct ggml_tensor * w,
 static int gemm_quant(b200_backend_ctx * ctx, const struct ggml_tensor * w, const float * x, int64_t x_stride_bytes, int64_t N,
                       void * dst, int64_t ldd, const b200_epilogue * ep) {
     static const bool use_mma = getenv("GGML_B200_NO_MMA") == nullptr;
-    static const bool use_tc  = getenv("GGML_B200_NO_TC") == nullptr;
+    // the tcgen05 / tensor-memory product gives the same bits but measures slower than the mma.sync form (every
+    // 32-block needs its own accumulator hand-off through tensor memory): opt-in
+    static const bool use_tc  = getenv("GGML_B200_TC") != nullptr && atoi(getenv("GGML_B200_TC")) != 0;
     void * st = (void *) ctx->stream;
     const int64_t K = w->ne[0], M = w->ne[1];
     const int64_t nb_total = (int64_t) (ggml_nbytes(w) / ggml_type_size(w->type));
@@ -884,8 +896,8 @@ static int run_item(b200_backend_ctx * ctx, const plan_item & it, struct ggml_cg
         float *  xd = colq_d(ctx);
         // products of this many columns or more go to the tcgen05 kernel (one launch for up to 64 columns, time nearly
         // independent of the column count); fewer columns stay with the FMA-pipe kernels that stream the weights once
-        static const int tc_min_cols = getenv("GGML_B200_TC_MIN_COLS") ? atoi(getenv("GGML_B200_TC_MIN_COLS")) : 24;
-        static const bool use_tc = getenv("GGML_B200_NO_TC") == nullptr;
+        static const int tc_min_cols = getenv("GGML_B200_TC_MIN_COLS") ? atoi(getenv("GGML_B200_TC_MIN_COLS")) : 48;
+        static const bool use_tc = getenv("GGML_B200_TC") != nullptr && atoi(getenv("GGML_B200_TC")) != 0;
         auto flush = [&]() -> int {
             if (!n_cols) return 0;
             int e = 0;
@@ -1102,8 +1114,8 @@ static int run_gemv_group(b200_backend_ctx * ctx, const plan_item * its, int n_i
     }
     if (n_cols <= 4) return -1;
     {   // many columns: each product is one tcgen05 launch of its own (run_item)
-        static const int tc_min_cols = getenv("GGML_B200_TC_MIN_COLS") ? atoi(getenv("GGML_B200_TC_MIN_COLS")) : 24;
-        static const bool use_tc = getenv("GGML_B200_NO_TC") == nullptr;
+        static const int tc_min_cols = getenv("GGML_B200_TC_MIN_COLS") ? atoi(getenv("GGML_B200_TC_MIN_COLS")) : 48;
+        static const bool use_tc = getenv("GGML_B200_TC") != nullptr && atoi(getenv("GGML_B200_TC")) != 0;
         if (use_tc && n_cols >= tc_min_cols) return -1;
     }
     int8_t * xq = colq_q(ctx);
@@ -1285,6 +1297,10 @@ static enum ggml_status finish_status(int e) {
 static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struct ggml_cgraph * cgraph) {
     b200_backend_ctx * ctx = (b200_backend_ctx *) backend->context;
     if (cudaSetDevice(ctx->device) != cudaSuccess) return GGML_STATUS_FAILED;
+    if (ctx->device < 16 && g_sticky_error[ctx->device].load(std::memory_order_relaxed)) {
+        fprintf(stderr, "ggml-b200: an earlier tensor copy on device %d failed: refusing to compute on its data\n", ctx->device);
+        return GGML_STATUS_FAILED;
+    }
     const int64_t t_enter = now_ns();
     static const bool fuse     = getenv("GGML_B200_NO_FUSION") == nullptr;
     static const bool batching = getenv("GGML_B200_NO_BATCHING") == nullptr;
@@ -1551,6 +1567,9 @@ static ggml_backend_t b200_dev_init_backend(ggml_backend_dev_t dev, const char *
     }
     if (cudaEventCreateWithFlags(&ctx->sync_event, cudaEventBlockingSync | cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); ctx->sync_event = nullptr; }
     if (cudaMalloc((void **) &ctx->topk, 8 * sizeof(b200_topk_result)) != cudaSuccess) { cudaGetLastError(); ctx->topk = nullptr; }
+    // activation scratch of the many-column products, sized here for Whisper's largest product (1500 columns of 5120
+    // values) so that graph_compute does not allocate on its usual path; it still grows on demand for larger graphs
+    ensure_scratch(ctx, (size_t) 1536 * 5120 + (size_t) 1536 * (5120 / 32) * 4);
     batcher_join(ctx);
     return new ggml_backend{ b200_guid(), b200_backend_iface, dev, ctx };
 }

@@ -22,13 +22,20 @@
 //               tiles of a stage in the canonical no-swizzle K-major layout (8-row x 16-byte core matrices), plus
 //               the block's scales; the zero part of B is written once at start and never touched again;
 //   warps 4-11  epilogue (see above), final hsum_float_8 order, fused ADD / SCALE / GELU / F16-store steps;
-//   warp  12    one thread issues the two K = 16 MMAs of a block, tcgen05.commit frees the stage and
-//               publishes the tensor-memory buffer (warps 13-15 only give their registers away).
+//   warp  12    one thread issues the two K = 16 MMAs of a block; one tcgen05.commit per block publishes the
+//               tensor-memory buffer, and the epilogue, having seen it, hands the operand stage back to the
+//               converters (warps 13-15 only give their registers away).
 // Registers: the kernel starts with 128 per thread (the whole register file); setmaxnreg moves them between the
 // warpgroups - converters keep 80, the MMA warpgroup 40, the epilogue warps grow to 192.  A warpgroup can only grow
 // by what the others of the same CTA have released: 128*80 + 256*192 + 128*40 = 64512 <= 512*128.
-// All hand-offs are mbarriers; every wait is bounded (one second), records a code in the status word and makes
-// all roles leave through the common exit that frees tensor memory.
+// All hand-offs are mbarriers; every wait is bounded (about one second; the clock is read only after thousands of failed
+// polls), records a code in the status word and makes all roles leave through the common exit that frees tensor memory.
+//
+// Measured (1280 x 1280 x 1500): 134 us, against 87 us for the mma.sync form (k_mma.cu) and 139 us for dp4a.  A
+// block-step costs about 1600 cycles here although its two MMAs take 256: every 32-block needs its own accumulator
+// hand-off (commit -> mbarrier -> tcgen05.ld -> mbarrier), a chain of about a thousand cycles, and tensor memory holds
+// only two blocks of a 128 x 32 tile.  Smaller tiles with four buffers were measured too (slower: the cost is per
+// hand-off, not per column).  The plugin therefore uses this kernel only on request (GGML_B200_TC=1).
 #include "b200_common.cuh"
 #include <string.h>
 #include <stdlib.h>
@@ -70,23 +77,42 @@ __device__ __forceinline__ f32x2 tc_fma2(f32x2 a, f32x2 b, f32x2 c) { f32x2 r; a
 
 __device__ __forceinline__ unsigned long long tc_now_ns() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 
-// Bounded mbarrier wait: false after one second or when another role has already given up.
-__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int * abort_flag, int * status, int code) {
+
+__device__ long long g_tc_prof[6][128];      // timing experiment: per-step clock stamps of CTA 0 (first 128 steps)
+extern "C" int b200_tc_prof_read(long long * out) { return (int) cudaMemcpyFromSymbol(out, g_tc_prof, sizeof(g_tc_prof)); }
+
+__device__ __forceinline__ bool tc_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded mbarrier wait: false after about one second or when another role has already given up.  The clock is only
+// looked at after many failed polls: reading it costs a few hundred cycles, which the ordinary hand-off (a barrier that
+// is ready or becomes ready within microseconds) must not pay.
+__device__ __forceinline__ bool tc_wait_slow(uint32_t bar, uint32_t parity, volatile int * abort_flag, int * status, int code) {
     unsigned long long t0 = 0;
-    const long long c0 = clock64();
     for (uint32_t i = 0;; ++i) {
-        uint32_t ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.b32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-        if (ok) return true;
-        if ((i & 63) == 63) {
+        if (tc_try(bar, parity)) return true;
+        if ((i & 255) == 255) {
             if (*abort_flag) return false;
             const unsigned long long t = tc_now_ns();
             if (t0 == 0) t0 = t;
-            // one second by the global timer; the cycle counter (about four seconds) backs it up
-            else if (t - t0 > 1000000000ull || clock64() - c0 > 8000000000ll) { *abort_flag = 1; atomicCAS(status, 0, code); return false; }
+            else if (t - t0 > 1000000000ull || i > (1u << 28)) { *abort_flag = 1; atomicCAS(status, 0, code); return false; }
         }
     }
+}
+__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile int * abort_flag, int * status, int code) {
+#pragma unroll 1
+    for (int i = 0; i < 2048; ++i) if (tc_try(bar, parity)) return true;
+    return tc_wait_slow(bar, parity, abort_flag, status, code);
+}
+// The same for a whole warp: one lane polls (32 lanes polling the same barrier word only slow its arrivals down), the
+// warp-level sync publishes what that lane acquired to the others.
+__device__ __forceinline__ bool tc_wait_warp(uint32_t bar, uint32_t parity, volatile int * abort_flag, int * status, int code) {
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = tc_wait(bar, parity, abort_flag, status, code) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 __device__ __forceinline__ void tc_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
@@ -125,7 +151,7 @@ __device__ __forceinline__ uint64_t tc_desc(uint32_t smem_addr, uint32_t lbo, ui
 template <int TYPE, bool COLS>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 k_mul_mat_tc(QPlanes w, int64_t M, int nbk, const int8_t * __restrict__ xq, const float * __restrict__ xd, int64_t N,
-             void * __restrict__ dst, int64_t ldd, TcEp ep, const __grid_constant__ TcCols cols, int * status, int relaxed, uint32_t lbo, uint32_t sbo) {
+             void * __restrict__ dst, int64_t ldd, TcEp ep, const __grid_constant__ TcCols cols, int * status, int relaxed, uint32_t lbo, uint32_t sbo, int dbg) {
     extern __shared__ __align__(1024) unsigned char tc_smem[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t smem_u = (uint32_t) __cvta_generic_to_shared(tc_smem);
@@ -159,6 +185,7 @@ k_mul_mat_tc(QPlanes w, int64_t M, int nbk, const int8_t * __restrict__ xq, cons
 
     const int tiles_m = (int) ((M + TC_BM - 1) / TC_BM), tiles_n = (int) ((N + TC_BN - 1) / TC_BN);
     const int n_tiles = tiles_m * tiles_n;
+    if ((dbg & 64) && blockIdx.x == 0 && tid == 128) g_tc_prof[0][0] = clock64();       // timing experiment: cycles of CTA 0
 
     if (warp < 4) {
         // ================= converters =================
@@ -194,7 +221,7 @@ k_mul_mat_tc(QPlanes w, int64_t M, int nbk, const int8_t * __restrict__ xq, cons
                 if (b + 1 < nbk) fetch(b + 1);
                 const int st = step % TC_NST;
                 const uint32_t it = step / TC_NST;
-                if (!tc_wait(bar_empty + st * 8, (it & 1) ^ 1, abort_flag, status, 1)) goto done;
+                if (!tc_wait_warp(bar_empty + st * 8, (it & 1) ^ 1, abort_flag, status, 1)) goto done;
                 unsigned char * sA = tc_smem + (size_t) st * TC_STAGE_BYTES;
                 uint32_t h[16];                                  // h[2e/2]: elements 2i, 2i+1 as f16x2
                 if (TYPE == B200_TYPE_Q5_0) {
@@ -254,7 +281,8 @@ k_mul_mat_tc(QPlanes w, int64_t M, int nbk, const int8_t * __restrict__ xq, cons
                     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                                  :: "r"(d_tmem), "l"(da + (256 >> 4)), "l"(db + (256 >> 4)), "r"(idesc), "r"(1) : "memory");
-                    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar_empty + st * 8) : "memory");
+                    // one commit per block: its arrival tells the epilogue that the lane sums are in tensor memory AND that the
+                    // operand stage has been read; the epilogue passes the second fact on to the converters
                     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar_tfull + buf * 8) : "memory");
                 }
             }
@@ -277,8 +305,9 @@ k_mul_mat_tc(QPlanes w, int64_t M, int nbk, const int8_t * __restrict__ xq, cons
                 for (int p = 0; p < 4; ++p) acc[c][p] = 0ull;
             for (int b = 0; b < nbk; ++b, ++step) {
                 const int buf = step & 1;
-                if (!tc_wait(bar_tfull + buf * 8, (step >> 1) & 1, abort_flag, status, 4)) goto done;
+                if (!tc_wait_warp(bar_tfull + buf * 8, (step >> 1) & 1, abort_flag, status, 4)) goto done;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (warp == 4 && lane == 0) tc_arrive(bar_empty + (step % TC_NST) * 8);      // the MMAs of this block have read their stage
                 const int slot = step % TC_SLOTS;
                 const float dw = dWs[slot * 128 + row];
                 const float * dxs = dXs + slot * 32 + g * 16;
@@ -360,6 +389,7 @@ k_mul_mat_tc(QPlanes w, int64_t M, int nbk, const int8_t * __restrict__ xq, cons
         }
     }
 done:
+    if ((dbg & 64) && blockIdx.x == 0 && tid == 128) g_tc_prof[0][1] = clock64();
     __syncwarp();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -425,10 +455,11 @@ static int tc_launch(int wtype, const void * w_planes, int64_t nb_total, int64_t
     static const uint32_t lbo = getenv("B200_TC_LBO") ? (uint32_t) atoi(getenv("B200_TC_LBO")) : 128u;
     static const uint32_t sbo = getenv("B200_TC_SBO") ? (uint32_t) atoi(getenv("B200_TC_SBO")) : 512u;
     const int nbk = (int) (K / 32);
+    static const int dbg = getenv("B200_TC_DBG") ? atoi(getenv("B200_TC_DBG")) : 0;      // timing experiments: 1 = no conversion, 2 = no epilogue
     cudaStream_t st = as_stream(stream);
     static const TcCols no_cols = {};
     const TcCols & ct = cols ? *cols : no_cols;
-#define TC_GO(T, C) k_mul_mat_tc<T, C><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(w, M, nbk, xq, xd, N, dst, dst_stride, e, ct, status, relaxed, lbo, sbo)
+#define TC_GO(T, C) k_mul_mat_tc<T, C><<<grid, TC_THREADS, TC_SMEM_BYTES, st>>>(w, M, nbk, xq, xd, N, dst, dst_stride, e, ct, status, relaxed, lbo, sbo, dbg)
     if (wtype == B200_TYPE_Q5_0) { if (cols) TC_GO(B200_TYPE_Q5_0, true); else TC_GO(B200_TYPE_Q5_0, false); }
     else                         { if (cols) TC_GO(B200_TYPE_Q8_0, true); else TC_GO(B200_TYPE_Q8_0, false); }
 #undef TC_GO

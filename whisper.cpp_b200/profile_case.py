@@ -11,6 +11,7 @@ Each case runs the kernel five times and prints the CUDA-event time of the last 
 import ctypes as C
 import os
 import sys
+import time
 
 import torch
 
@@ -21,6 +22,12 @@ i64, vp = C.c_int64, C.c_void_p
 
 
 def timed(fn, name):
+    if os.environ.get("B200_PROFILE_WARM", "1") != "0":      # bring the clocks up first (skipped under a profiler)
+        w = torch.empty(1 << 26, device="cuda")
+        t0 = time.perf_counter()
+        while time.perf_counter() - t0 < 0.6:
+            w.add_(1.0)
+            torch.cuda.synchronize()
     for _ in range(2):
         fn()
     torch.cuda.synchronize()
