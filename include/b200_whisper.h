@@ -46,6 +46,13 @@ int b200_blocks_to_planes(int type, const void * blocks, void * planes, int64_t 
                           int64_t nb_first, int64_t nb_count);   /* replaces nothing: layout helper */
 int b200_planes_to_blocks(int type, const void * planes, void * blocks, int64_t nb_total,
                           int64_t nb_first, int64_t nb_count);
+/* The same conversions on the device: `blocks_dev` holds nb_count raw ggml blocks (as read from a model file,
+ * src/whisper.cpp:1874-1960, or produced by the quantize tool), `planes_dev` is the whole tensor's plane storage.
+ * The plugin's set_tensor / get_tensor use them: one upload of the file's bytes plus one launch per weight tensor. */
+int b200_blocks_to_planes_device(int type, const void * blocks_dev, void * planes_dev, int64_t nb_total, int64_t nb_first,
+                                 int64_t nb_count, void * stream);
+int b200_planes_to_blocks_device(int type, const void * planes_dev, void * blocks_dev, int64_t nb_total, int64_t nb_first,
+                                 int64_t nb_count, void * stream);
 
 /* dequantize_row_q5_0 / dequantize_row_q8_0 (ggml/src/ggml-quants.c:296-320, 349-362) on planes. */
 int b200_dequantize(int type, const void * planes, int64_t nb_total, int64_t nb_first, int64_t nb_count,

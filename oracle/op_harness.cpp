@@ -223,22 +223,22 @@ int oph_try_alloc(const char * dev_name, int64_t size) {
 }
 
 //  oph_unsupported_status: ggml_status of graph_compute for a graph that holds an operator the device does not support
-//  (ggml_sqr), handed to the backend directly, past the scheduler that would never send it there.  -1/-2: set-up failed,
-//  -3: the device claims to support the operator.
+//  (ggml_sqr), handed to the backend directly, past the scheduler that would never send it there (GGML_STATUS_FAILED is -1,
+//  GGML_STATUS_ALLOC_FAILED -2, GGML_STATUS_SUCCESS 0).  -11/-12: set-up failed, -13: the device claims to support the operator.
 int oph_unsupported_status(const char * dev_name) {
     ggml_backend_t backend = init_backend(dev_name, 1);
-    if (!backend) return -1;
+    if (!backend) return -11;
     struct ggml_init_params ip = { ggml_tensor_overhead() * 8 + ggml_graph_overhead(), nullptr, true };
     ggml_context * ctx = ggml_init(ip);
     ggml_tensor * a = ggml_new_tensor_1d(ctx, GGML_TYPE_F32, 64);
     ggml_tensor * r = ggml_sqr(ctx, a);
     int rc;
     if (ggml_backend_dev_supports_op(ggml_backend_get_device(backend), r)) {
-        rc = -3;
+        rc = -13;
     } else {
         ggml_backend_buffer_t buf = ggml_backend_alloc_ctx_tensors(ctx, backend);
         if (!buf) {
-            rc = -2;
+            rc = -12;
         } else {
             ggml_cgraph * g = ggml_new_graph(ctx);
             ggml_build_forward_expand(g, r);

@@ -472,3 +472,24 @@ def test_topk_rows(K, n, k, n_rows):
         assert abs(r.logsumexp - lse) <= 1e-5 * max(1.0, abs(lse))
     assert K.b200_topk_rows(rows, outs, n_rows, i64(n), 9, None) != 0       # k beyond the maximum
     assert K.b200_topk_rows(rows, outs, 65, i64(n), 1, None) != 0           # too many rows
+
+
+@pytest.mark.parametrize("wtype,bs", [(6, 22), (8, 34)])
+def test_blocks_planes_on_the_device(K, wtype, bs):
+    """Raw ggml blocks -> planes -> raw blocks on the device equals the host conversion, whole tensors and partial ranges."""
+    nb = 3001
+    blocks = np.random.default_rng(bs).integers(0, 256, (nb, bs), dtype=np.uint8)
+    want = np.zeros(nb * bs, np.uint8)
+    assert K.b200_blocks_to_planes(wtype, blocks.ctypes.data_as(vp), want.ctypes.data_as(vp), i64(nb), i64(0), i64(nb)) == 0
+    d_blocks, d_planes = dev(blocks), torch.zeros(nb * bs, dtype=torch.uint8, device="cuda")
+    sync_ok(K.b200_blocks_to_planes_device(wtype, ptr(d_blocks), ptr(d_planes), i64(nb), i64(0), i64(nb), None))
+    assert np.array_equal(d_planes.cpu().numpy(), want)
+    # a partial range (blocks 100..699) lands where the host puts it and leaves the rest alone
+    part, want_p = torch.zeros(nb * bs, dtype=torch.uint8, device="cuda"), np.zeros(nb * bs, np.uint8)
+    assert K.b200_blocks_to_planes(wtype, blocks[100:700].ctypes.data_as(vp), want_p.ctypes.data_as(vp), i64(nb), i64(100), i64(600)) == 0
+    sync_ok(K.b200_blocks_to_planes_device(wtype, ptr(dev(blocks[100:700])), ptr(part), i64(nb), i64(100), i64(600), None))
+    assert np.array_equal(part.cpu().numpy(), want_p)
+    back = torch.zeros((nb, bs), dtype=torch.uint8, device="cuda")
+    sync_ok(K.b200_planes_to_blocks_device(wtype, ptr(d_planes), ptr(back), i64(nb), i64(0), i64(nb), None))
+    assert np.array_equal(back.cpu().numpy(), blocks)
+    assert K.b200_blocks_to_planes_device(wtype, ptr(d_blocks), ptr(d_planes), i64(nb), i64(3000), i64(2), None) != 0

@@ -142,47 +142,48 @@ static void b200_buffer_memset_tensor(ggml_backend_buffer_t buffer, struct ggml_
     cuda_ok(cudaStreamSynchronize(cudaStreamPerThread), "memset_tensor sync");
 }
 
-// Block-quantised tensors live in device memory as planes (see b200_whisper.h); set/get translate.
+// Block-quantised tensors live in device memory as planes (see b200_whisper.h); set/get translate on the device: the raw
+// block bytes cross the bus once, in one copy, into a staging buffer, and one launch scatters them into the planes
+// (get_tensor: the reverse).  The staging buffer is per device, grows on demand and is shared under a lock - weights are
+// written once, at model load, by one thread at a time.
+struct staging_buf { std::mutex mu; void * p = nullptr; size_t size = 0; };
+static staging_buf g_staging[B200_MAX_DEVICES];
+
+static void * staging_reserve(staging_buf & sb, size_t size) {
+    if (sb.size >= size) return sb.p;
+    if (sb.p) { cudaFree(sb.p); sb.p = nullptr; sb.size = 0; }
+    const size_t want = (size + ((size_t) 1 << 22) - 1) & ~(((size_t) 1 << 22) - 1);
+    if (cudaMalloc(&sb.p, want) != cudaSuccess) { cudaGetLastError(); sb.p = nullptr; return nullptr; }
+    sb.size = want;
+    return sb.p;
+}
+
 static void b200_buffer_set_tensor(ggml_backend_buffer_t buffer, struct ggml_tensor * tensor, const void * data, size_t offset, size_t size) {
     b200_buffer_ctx * ctx = (b200_buffer_ctx *) buffer->context;
     cudaSetDevice(ctx->device);
     g_h2d_bytes += (int64_t) size;
+    cudaStream_t st = cudaStreamPerThread;
     if (is_quant(tensor->type)) {
         mma_cache_drop_range(tensor->data, 1);
         const size_t  bs = ggml_type_size(tensor->type);
         const int64_t nb_total = (int64_t) (ggml_nbytes(tensor) / bs);
-        GGML_ASSERT(tensor->view_src == nullptr && "ggml-b200: views of block-quantised tensors are not supported");
-        GGML_ASSERT(offset % bs == 0 && size % bs == 0);
+        if (tensor->view_src != nullptr || offset % bs != 0 || size % bs != 0) {
+            note_buffer_error(ctx->device, "set_tensor on a view or a partial block of a block-quantised tensor");
+            return;
+        }
         const int64_t first = (int64_t) (offset / bs), count = (int64_t) (size / bs);
-        // repack into a host image of the touched plane ranges, then copy each range
-        const size_t qsz = tensor->type == GGML_TYPE_Q5_0 ? 16 : 32;
-        std::vector<uint8_t> qs(count * qsz), qh(tensor->type == GGML_TYPE_Q5_0 ? count * 4 : 0), d(count * 2);
-        const uint8_t * src = (const uint8_t *) data;
-        for (int64_t i = 0; i < count; ++i) {
-            const uint8_t * b = src + bs * i;
-            memcpy(&d[2 * i], b, 2);
-            if (tensor->type == GGML_TYPE_Q5_0) {
-                memcpy(&qh[4 * i], b + 2, 4);
-                memcpy(&qs[16 * i], b + 6, 16);
-            } else {
-                memcpy(&qs[32 * i], b + 2, 32);
-            }
-        }
-        char * base = (char *) tensor->data;
-        cudaStream_t st = cudaStreamPerThread;
-        bool ok = cuda_ok(cudaMemcpyAsync(base + qsz * first, qs.data(), qs.size(), cudaMemcpyHostToDevice, st), "set_tensor qs");
-        if (tensor->type == GGML_TYPE_Q5_0) {
-            ok = ok && cuda_ok(cudaMemcpyAsync(base + 16 * nb_total + 4 * first, qh.data(), qh.size(), cudaMemcpyHostToDevice, st), "set_tensor qh");
-            ok = ok && cuda_ok(cudaMemcpyAsync(base + 20 * nb_total + 2 * first, d.data(), d.size(), cudaMemcpyHostToDevice, st), "set_tensor d");
-        } else {
-            ok = ok && cuda_ok(cudaMemcpyAsync(base + 32 * nb_total + 2 * first, d.data(), d.size(), cudaMemcpyHostToDevice, st), "set_tensor d");
-        }
+        staging_buf & sb = g_staging[ctx->device];
+        std::lock_guard<std::mutex> lk(sb.mu);
+        void * stage = staging_reserve(sb, size);
+        bool ok = stage != nullptr;
+        ok = ok && cuda_ok(cudaMemcpyAsync(stage, data, size, cudaMemcpyHostToDevice, st), "set_tensor upload");
+        ok = ok && b200_blocks_to_planes_device((int) tensor->type, stage, tensor->data, nb_total, first, count, (void *) st) == 0;
         ok = cuda_ok(cudaStreamSynchronize(st), "set_tensor sync") && ok;
         if (!ok) note_buffer_error(ctx->device, "set_tensor");
         return;
     }
-    bool ok = cuda_ok(cudaMemcpyAsync((char *) tensor->data + offset, data, size, cudaMemcpyHostToDevice, cudaStreamPerThread), "set_tensor");
-    ok = ok && cuda_ok(cudaStreamSynchronize(cudaStreamPerThread), "set_tensor sync");
+    bool ok = cuda_ok(cudaMemcpyAsync((char *) tensor->data + offset, data, size, cudaMemcpyHostToDevice, st), "set_tensor");
+    ok = ok && cuda_ok(cudaStreamSynchronize(st), "set_tensor sync");
     if (!ok) note_buffer_error(ctx->device, "set_tensor");
 }
 
@@ -194,40 +195,28 @@ static void b200_buffer_get_tensor(ggml_backend_buffer_t buffer, const struct gg
     }
     cudaSetDevice(ctx->device);
     g_d2h_bytes += (int64_t) size;
+    cudaStream_t st = cudaStreamPerThread;
     if (is_quant(tensor->type)) {
         const size_t  bs = ggml_type_size(tensor->type);
         const int64_t nb_total = (int64_t) (ggml_nbytes(tensor) / bs);
-        GGML_ASSERT(tensor->view_src == nullptr);
-        GGML_ASSERT(offset % bs == 0 && size % bs == 0);
+        if (tensor->view_src != nullptr || offset % bs != 0 || size % bs != 0) {
+            note_buffer_error(ctx->device, "get_tensor on a view or a partial block of a block-quantised tensor");
+            memset(data, 0, size);
+            return;
+        }
         const int64_t first = (int64_t) (offset / bs), count = (int64_t) (size / bs);
-        const size_t qsz = tensor->type == GGML_TYPE_Q5_0 ? 16 : 32;
-        std::vector<uint8_t> qs(count * qsz), qh(tensor->type == GGML_TYPE_Q5_0 ? count * 4 : 0), d(count * 2);
-        const char * base = (const char *) tensor->data;
-        cudaStream_t st = cudaStreamPerThread;
-        bool ok = cuda_ok(cudaMemcpyAsync(qs.data(), base + qsz * first, qs.size(), cudaMemcpyDeviceToHost, st), "get_tensor qs");
-        if (tensor->type == GGML_TYPE_Q5_0) {
-            ok = ok && cuda_ok(cudaMemcpyAsync(qh.data(), base + 16 * nb_total + 4 * first, qh.size(), cudaMemcpyDeviceToHost, st), "get_tensor qh");
-            ok = ok && cuda_ok(cudaMemcpyAsync(d.data(), base + 20 * nb_total + 2 * first, d.size(), cudaMemcpyDeviceToHost, st), "get_tensor d");
-        } else {
-            ok = ok && cuda_ok(cudaMemcpyAsync(d.data(), base + 32 * nb_total + 2 * first, d.size(), cudaMemcpyDeviceToHost, st), "get_tensor d");
-        }
-        ok = ok && cuda_ok(cudaStreamSynchronize(st), "get_tensor sync");
-        if (!ok) { note_buffer_error(ctx->device, "get_tensor"); memset(data, 0, size); return; }
-        uint8_t * dst = (uint8_t *) data;
-        for (int64_t i = 0; i < count; ++i) {
-            uint8_t * b = dst + bs * i;
-            memcpy(b, &d[2 * i], 2);
-            if (tensor->type == GGML_TYPE_Q5_0) {
-                memcpy(b + 2, &qh[4 * i], 4);
-                memcpy(b + 6, &qs[16 * i], 16);
-            } else {
-                memcpy(b + 2, &qs[32 * i], 32);
-            }
-        }
+        staging_buf & sb = g_staging[ctx->device];
+        std::lock_guard<std::mutex> lk(sb.mu);
+        void * stage = staging_reserve(sb, size);
+        bool ok = stage != nullptr;
+        ok = ok && b200_planes_to_blocks_device((int) tensor->type, tensor->data, stage, nb_total, first, count, (void *) st) == 0;
+        ok = ok && cuda_ok(cudaMemcpyAsync(data, stage, size, cudaMemcpyDeviceToHost, st), "get_tensor download");
+        ok = cuda_ok(cudaStreamSynchronize(st), "get_tensor sync") && ok;
+        if (!ok) { note_buffer_error(ctx->device, "get_tensor"); memset(data, 0, size); }
         return;
     }
-    bool ok = cuda_ok(cudaMemcpyAsync(data, (const char *) tensor->data + offset, size, cudaMemcpyDeviceToHost, cudaStreamPerThread), "get_tensor");
-    ok = ok && cuda_ok(cudaStreamSynchronize(cudaStreamPerThread), "get_tensor sync");
+    bool ok = cuda_ok(cudaMemcpyAsync(data, (const char *) tensor->data + offset, size, cudaMemcpyDeviceToHost, st), "get_tensor");
+    ok = ok && cuda_ok(cudaStreamSynchronize(st), "get_tensor sync");
     if (!ok) { note_buffer_error(ctx->device, "get_tensor"); memset(data, 0, size); }
 }
 

@@ -5,11 +5,12 @@
 // Also the 1-D im2col that feeds the conv stem.
 #include "b200_common.cuh"
 
-template <bool X_F16>
+// A warp owns TM x TN outputs (lane = running sum k % 32): 4 x 4 for small products, 8 x 8 where both extents are large
+// (the conv stem: 3000 x 1280 and 1500 x 1280 outputs), which halves the loads per FMA.
+template <bool X_F16, int TM, int TN>
 __global__ void __launch_bounds__(128)
 k_mul_mat_f16(const char * __restrict__ a, Dims4 da, const char * __restrict__ b, Dims4 db,
               char * __restrict__ dst, int64_t nbd1, int64_t nbd2, int64_t nbd3) {
-    constexpr int TM = 4, TN = 4;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t M = da.ne[1], N = db.ne[1], K = da.ne[0];
     const int64_t m0 = ((int64_t) blockIdx.x * 2 + (warp & 1)) * TM;
@@ -94,11 +95,13 @@ extern "C" int b200_mul_mat_f16(const void * src0, const int64_t * ne0, const in
     const int64_t M = da.ne[1], N = db.ne[1], batch = db.ne[2] * db.ne[3];
     if (M <= 0 || N <= 0 || batch <= 0) return 0;
     if (batch > 65535 || (N + 7) / 8 > 65535) return B200_ERR_ARG;
-    dim3 grid((unsigned) ((M + 7) / 8), (unsigned) ((N + 7) / 8), (unsigned) batch);
-    if (src1_type == B200_TYPE_F16)
-        k_mul_mat_f16<true><<<grid, 128, 0, as_stream(stream)>>>((const char *) src0, da, (const char *) src1, db, (char *) dst, nbd[1], nbd[2], nbd[3]);
-    else
-        k_mul_mat_f16<false><<<grid, 128, 0, as_stream(stream)>>>((const char *) src0, da, (const char *) src1, db, (char *) dst, nbd[1], nbd[2], nbd[3]);
+    const bool big = M >= 256 && N >= 256;
+    const int t = big ? 8 : 4;
+    dim3 grid((unsigned) ((M + 2 * t - 1) / (2 * t)), (unsigned) ((N + 2 * t - 1) / (2 * t)), (unsigned) batch);
+#define B200_F16_GO(XF, T) k_mul_mat_f16<XF, T, T><<<grid, 128, 0, as_stream(stream)>>>((const char *) src0, da, (const char *) src1, db, (char *) dst, nbd[1], nbd[2], nbd[3])
+    if (src1_type == B200_TYPE_F16) { if (big) B200_F16_GO(true, 8); else B200_F16_GO(true, 4); }
+    else                            { if (big) B200_F16_GO(false, 8); else B200_F16_GO(false, 4); }
+#undef B200_F16_GO
     B200_RETURN_LAST();
 }
 

@@ -77,6 +77,53 @@ extern "C" int b200_planes_to_blocks(int type, const void * planes, void * block
 }
 
 // ------------------------------------------------------------------------------------------------
+// device: ggml blocks (raw bytes as a model file holds them, 22 / 34 bytes each, unaligned) <-> planes.  One thread
+// moves two bytes of a block, so the reads of a warp cover consecutive bytes of the block stream and the writes into
+// each plane are contiguous runs; this is how the plugin stores a weight tensor in one upload plus one launch.
+// ------------------------------------------------------------------------------------------------
+template <bool TO_PLANES>
+__global__ void k_blocks_planes(int type, uint8_t * __restrict__ blocks, uint8_t * __restrict__ planes, int64_t nb_total, int64_t nb_first, int64_t nb_count) {
+    const int bs2 = type == B200_TYPE_Q5_0 ? 11 : 17;                   // byte pairs per block
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;  // pair index in the block stream
+    if (i >= nb_count * bs2) return;
+    const int64_t blk = i / bs2;
+    const int     off = (int) (i - blk * bs2) * 2;                      // byte offset inside the block (even)
+    const int64_t o = nb_first + blk;
+    uint8_t * b = blocks + blk * (2 * bs2) + off;
+    uint8_t * pl;
+    if (type == B200_TYPE_Q5_0) {       // {f16 d; u8 qh[4]; u8 qs[16]}
+        if (off < 2)      pl = planes + 20 * nb_total + 2 * o;
+        else if (off < 6) pl = planes + 16 * nb_total + 4 * o + (off - 2);
+        else              pl = planes + 16 * o + (off - 6);
+    } else {                            // {f16 d; i8 qs[32]}
+        if (off < 2) pl = planes + 32 * nb_total + 2 * o;
+        else         pl = planes + 32 * o + (off - 2);
+    }
+    if (TO_PLANES) { pl[0] = b[0]; pl[1] = b[1]; }
+    else           { b[0] = pl[0]; b[1] = pl[1]; }
+}
+
+extern "C" int b200_blocks_to_planes_device(int type, const void * blocks_dev, void * planes_dev, int64_t nb_total, int64_t nb_first,
+                                            int64_t nb_count, void * stream) {
+    if (type != B200_TYPE_Q5_0 && type != B200_TYPE_Q8_0) return B200_ERR_ARG;
+    if (nb_first < 0 || nb_count < 0 || nb_first + nb_count > nb_total || !blocks_dev || !planes_dev) return B200_ERR_ARG;
+    if (nb_count == 0) return 0;
+    const int64_t n = nb_count * (type == B200_TYPE_Q5_0 ? 11 : 17);
+    k_blocks_planes<true><<<(unsigned) ((n + 255) / 256), 256, 0, as_stream(stream)>>>(type, (uint8_t *) blocks_dev, (uint8_t *) planes_dev, nb_total, nb_first, nb_count);
+    B200_RETURN_LAST();
+}
+
+extern "C" int b200_planes_to_blocks_device(int type, const void * planes_dev, void * blocks_dev, int64_t nb_total, int64_t nb_first,
+                                            int64_t nb_count, void * stream) {
+    if (type != B200_TYPE_Q5_0 && type != B200_TYPE_Q8_0) return B200_ERR_ARG;
+    if (nb_first < 0 || nb_count < 0 || nb_first + nb_count > nb_total || !blocks_dev || !planes_dev) return B200_ERR_ARG;
+    if (nb_count == 0) return 0;
+    const int64_t n = nb_count * (type == B200_TYPE_Q5_0 ? 11 : 17);
+    k_blocks_planes<false><<<(unsigned) ((n + 255) / 256), 256, 0, as_stream(stream)>>>(type, (uint8_t *) blocks_dev, (uint8_t *) planes_dev, nb_total, nb_first, nb_count);
+    B200_RETURN_LAST();
+}
+
+// ------------------------------------------------------------------------------------------------
 // dequantise (one thread per element)
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ float dequant_elem(int type, const QPlanes & p, int64_t blk, int e) {

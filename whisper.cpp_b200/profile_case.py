@@ -5,6 +5,7 @@
     python whisper.cpp_b200/profile_case.py tc_cols [M K N]   # the same kernel in its per-column (decode) form, default 64 columns
     python whisper.cpp_b200/profile_case.py fa_enc            # encoder attention 1500 x 1536 x 20 heads
     python whisper.cpp_b200/profile_case.py topk              # top-k side output of 64 logits rows
+    python whisper.cpp_b200/profile_case.py conv              # the two F16 products of the large-v3 conv stem
 
 Each case runs the kernel five times and prints the CUDA-event time of the last three launches.
 """
@@ -76,6 +77,15 @@ def main():
         rows = (vp * rows_n)(*[x[i].data_ptr() for i in range(rows_n)])
         outs = (vp * rows_n)(*[out[i].data_ptr() for i in range(rows_n)])
         timed(lambda: K.b200_topk_rows(rows, outs, rows_n, i64(n), 5, None), "topk_rows 64 x 51866, k = 5")
+    elif case == "conv":
+        def arr4(v):
+            return (C.c_int64 * 4)(*v)
+        for (M, N, Kd) in ((3000, 1280, 384), (1500, 1280, 3840)):
+            a, b = torch.randn((M, Kd), device="cuda").half(), torch.randn((N, Kd), device="cuda").half()
+            o = torch.zeros((N, M), device="cuda")
+            timed(lambda: K.b200_mul_mat_f16(ptr(a), arr4([Kd, M, 1, 1]), arr4([2, Kd * 2, Kd * M * 2, Kd * M * 2]), ptr(b), 1, arr4([Kd, N, 1, 1]),
+                                             arr4([2, Kd * 2, Kd * N * 2, Kd * N * 2]), ptr(o), arr4([4, M * 4, M * N * 4, M * N * 4]), None),
+                  f"mul_mat_f16 {M} x {N} x {Kd} ({2 * M * N * Kd / 1e9:.1f} GFLOP)")
     else:
         raise SystemExit(__doc__)
 
