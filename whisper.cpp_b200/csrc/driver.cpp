@@ -203,7 +203,8 @@ static void decode_phase_meet() {
     std::unique_lock<std::mutex> lk(g_phase_mu);
     if (!g_phase_hook || g_phase_parties <= 0) return;
     if (++g_phase_arrived >= g_phase_parties) { g_phase_hook(1); g_phase_cv.notify_all(); }
-    else g_phase_cv.wait(lk, [&] { return g_phase_arrived >= g_phase_parties || !g_phase_hook; });
+    // bounded: a state that failed before the meeting point must not leave the others waiting for ever
+    else g_phase_cv.wait_for(lk, std::chrono::seconds(120), [&] { return g_phase_arrived >= g_phase_parties || !g_phase_hook; });
 }
 
 // Optional: sample from the plugin's logits side output (get_proc_address "b200_last_topk", include/b200_whisper.h)

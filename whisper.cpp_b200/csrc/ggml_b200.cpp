@@ -1224,12 +1224,20 @@ static int run_plan(b200_backend_ctx * ctx, const exec_plan & plan, struct ggml_
 // bits it would get alone.  The wait is bounded (no thread ever waits on the GPU here, only on a host condition
 // variable with a timeout).
 // ---------------------------------------------------------------------------------------------
+// An event a leader records after a merged step; it goes back to the free list only when every follower that was served
+// by that step has made its own stream wait on it, so a follower that is descheduled for a long time can never find the
+// event re-recorded by a later batch.
+struct batch_event {
+    cudaEvent_t      ev = nullptr;
+    std::atomic<int> refs{0};
+};
+
 struct batch_req {
     b200_backend_ctx *   ctx;
     struct ggml_cgraph * g;
     uint64_t             sig;
     int                  state;     // 0 waiting, 1 done (stream must wait on ev), 2 run it yourself, 3 failed
-    cudaEvent_t          ev;
+    batch_event *        ev;
     int                  fits;      // checked against the cached plan by the submitting thread: 1 yes, -1 no, 0 not checked
 };
 
@@ -1238,8 +1246,7 @@ struct device_batcher {
     std::condition_variable cv;
     std::vector<batch_req *> pending;
     bool                    leader_active = false;
-    std::vector<cudaEvent_t> events;       // round-robin pool
-    size_t                  next_event = 0;
+    std::vector<batch_event *> free_events;   // events nobody waits on (guarded by mu)
     std::unordered_map<uint64_t, std::shared_ptr<const exec_plan>> plans;      // by signature, fused
     int                     alive = 0;                  // backend instances on this device
     double                  step_ns_ema = 0;            // typical time from "step enqueued" to "next step arrives"
@@ -1340,7 +1347,12 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
             B.cv.wait(lk, [&] { return req.state != 0; });
             lk.unlock();
             if (req.state == 1) {
-                if (!cuda_ok(cudaStreamWaitEvent(ctx->stream, req.ev, 0), "cudaStreamWaitEvent")) return GGML_STATUS_FAILED;
+                const bool waited = cuda_ok(cudaStreamWaitEvent(ctx->stream, req.ev->ev, 0), "cudaStreamWaitEvent");
+                if (req.ev->refs.fetch_sub(1) == 1) {            // last follower of that step: the event may be reused
+                    std::lock_guard<std::mutex> lk2(B.mu);
+                    B.free_events.push_back(req.ev);
+                }
+                if (!waited) return GGML_STATUS_FAILED;
                 g_nodes_computed += n_compute;
                 g_graphs_computed += 1;
                 g_host_ns_compute += now_ns() - t_enter;
@@ -1372,9 +1384,12 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
             std::vector<batch_req *> mine;
             mine.swap(B.pending);                                 // everything that is waiting now (may exceed max_group by a few)
             B.leader_active = false;                              // later arrivals elect their own leader
-            cudaEvent_t ev = nullptr;
-            if (B.events.size() < 64) { cudaEvent_t e; cudaEventCreateWithFlags(&e, cudaEventDisableTiming); B.events.push_back(e); }
-            ev = B.events[B.next_event++ % B.events.size()];
+            batch_event * ev = nullptr;
+            if (!B.free_events.empty()) { ev = B.free_events.back(); B.free_events.pop_back(); }
+            else {
+                ev = new batch_event;
+                if (cudaEventCreateWithFlags(&ev->ev, cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); delete ev; ev = nullptr; }
+            }
             // plan of the leader's structure (cached by signature)
             std::shared_ptr<const exec_plan> plan_sp;
             {
@@ -1426,13 +1441,20 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
                         g_tc_count[bt_class[k]] += 1;
                     }
                 }
-                if (rc == 0 && !served.empty()) rc = cudaEventRecord(ev, ctx->stream) == cudaSuccess ? 0 : (int) cudaGetLastError();
+                if (rc == 0 && !served.empty()) {
+                    if (!ev) rc = (int) cudaErrorMemoryAllocation;
+                    else {
+                        ev->refs = (int) served.size();
+                        rc = cudaEventRecord(ev->ev, ctx->stream) == cudaSuccess ? 0 : (int) cudaGetLastError();
+                    }
+                }
                 g_batched_graphs += (int64_t) gs.size();
                 g_batches += 1;
             } else {
                 rc = -1;                                          // leader's own graph does not fit: everybody runs alone
             }
             lk.lock();
+            if (ev && (rc != 0 || served.empty())) B.free_events.push_back(ev);      // nobody is going to wait on it
             const int64_t t_done = now_ns();
             if (rc == 0) ctx->served_ns = t_done;
             for (batch_req * r : mine) {

@@ -372,55 +372,82 @@ extern "C" int b200_concat(const float * a, const int64_t * nea, const int64_t *
 // whisper_sample_token, src/whisper.cpp:5015-5430; greedy = first index of the maximum).  This kernel leaves, per
 // row, the k largest values with their indices (ties: lower index first, as a forward scan with `>` finds them), the
 // maximum and log(sum(exp(x - max))) + max, so that a caller that only needs those can skip the 200 KB row.
-// One CTA per row; k passes, each a block-wide arg-max over the values not yet taken (the row stays in L2).
 #define TOPK_THREADS 512
 struct TopkRows { const float * row[64]; b200_topk_result * out[64]; };
 
 __device__ __forceinline__ bool topk_better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
 
+// One CTA per row, ONE pass over the row: every thread keeps the k best of its own elements (sorted, ties towards the
+// lower index - a thread meets its indices in ascending order) and a running (max, sum of exp) pair; then k rounds of a
+// block-wide arg-max over the threads' current heads pick the global winners, and the (max, sum) pairs are merged.
 __global__ void __launch_bounds__(TOPK_THREADS)
 k_topk_rows(TopkRows rows, int n, int k) {
     chain_release();
     chain_wait();
-    __shared__ float s_v[TOPK_THREADS / 32];
-    __shared__ int   s_i[TOPK_THREADS / 32];
+    __shared__ float  s_v[TOPK_THREADS / 32];
+    __shared__ int    s_i[TOPK_THREADS / 32];
+    __shared__ int    s_t[TOPK_THREADS / 32];
     __shared__ double s_d[TOPK_THREADS / 32];
-    __shared__ int   taken[B200_TOPK_MAX];
-    __shared__ float best_v;
+    __shared__ float  s_m[TOPK_THREADS / 32];
+    __shared__ int    win_t;
+    __shared__ float  row_max;
     const float * x = rows.row[blockIdx.x];
     b200_topk_result * out = rows.out[blockIdx.x];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    for (int r = 0; r < k; ++r) {
-        float bv = -INFINITY;
-        int   bi = 0x7fffffff;
-        for (int i = tid; i < n; i += TOPK_THREADS) {
-            const float v = x[i];
-            bool skip = false;
-            for (int t = 0; t < r; ++t) skip |= (taken[t] == i);
-            if (!skip && (topk_better(v, i, bv, bi) || bi == 0x7fffffff)) { bv = v; bi = i; }
+    float bv[B200_TOPK_MAX];
+    int   bi[B200_TOPK_MAX];
+#pragma unroll
+    for (int j = 0; j < B200_TOPK_MAX; ++j) { bv[j] = -INFINITY; bi[j] = 0x7fffffff; }
+    float  m = -INFINITY;      // running maximum of this thread's elements
+    double se = 0.0;           // sum of exp(x - m) over them
+    for (int i = tid; i < n; i += TOPK_THREADS) {
+        const float v = x[i];
+        if (v > m) { se = se * (double) __expf(m - v) + 1.0; m = v; }
+        else if (v == v) se += (double) __expf(v - m);
+        // insertion into the sorted list (strictly greater moves ahead; an equal value with a higher index stays behind)
+        if (bi[k - 1] == 0x7fffffff || v > bv[k - 1]) {
+            float cv = v; int ci = i;
+#pragma unroll
+            for (int j = 0; j < B200_TOPK_MAX; ++j) {
+                if (j < k && (bi[j] == 0x7fffffff || cv > bv[j])) {
+                    const float tv = bv[j]; const int ti = bi[j];
+                    bv[j] = cv; bi[j] = ci; cv = tv; ci = ti;
+                }
+            }
         }
+    }
+    // k rounds: the best head of all threads wins, its owner moves on to its next candidate
+    int head = 0;
+    for (int r = 0; r < k; ++r) {
+        float cv = -INFINITY; int ci = 0x7fffffff;
+#pragma unroll
+        for (int j = 0; j < B200_TOPK_MAX; ++j) if (j == head) { cv = bv[j]; ci = bi[j]; }
+        if (head >= k) ci = 0x7fffffff;
+        int ct = tid;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int   oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (oi != 0x7fffffff && (bi == 0x7fffffff || topk_better(ov, oi, bv, bi))) { bv = ov; bi = oi; }
+            const float ov = __shfl_xor_sync(0xffffffffu, cv, o);
+            const int   oi = __shfl_xor_sync(0xffffffffu, ci, o);
+            const int   ot = __shfl_xor_sync(0xffffffffu, ct, o);
+            if (oi != 0x7fffffff && (ci == 0x7fffffff || topk_better(ov, oi, cv, ci))) { cv = ov; ci = oi; ct = ot; }
         }
-        if (lane == 0) { s_v[warp] = bv; s_i[warp] = bi; }
+        if (lane == 0) { s_v[warp] = cv; s_i[warp] = ci; s_t[warp] = ct; }
         __syncthreads();
         if (tid == 0) {
             for (int w = 1; w < TOPK_THREADS / 32; ++w)
-                if (s_i[w] != 0x7fffffff && (bi == 0x7fffffff || topk_better(s_v[w], s_i[w], bv, bi))) { bv = s_v[w]; bi = s_i[w]; }
-            taken[r] = bi;
-            out->ids[r] = bi == 0x7fffffff ? -1 : bi;
-            out->vals[r] = bv;
-            if (r == 0) { best_v = bv; out->max = bv; }
+                if (s_i[w] != 0x7fffffff && (ci == 0x7fffffff || topk_better(s_v[w], s_i[w], cv, ci))) { cv = s_v[w]; ci = s_i[w]; ct = s_t[w]; }
+            out->ids[r] = ci == 0x7fffffff ? -1 : ci;
+            out->vals[r] = cv;
+            if (r == 0) { row_max = cv; out->max = cv; }
+            win_t = ci == 0x7fffffff ? -1 : ct;
         }
         __syncthreads();
+        if (tid == win_t) ++head;
     }
-    // log-sum-exp around the maximum, accumulated in double
-    const float mx = best_v;
-    double s = 0.0;
-    for (int i = tid; i < n; i += TOPK_THREADS) s += exp((double) x[i] - (double) mx);
+    // log-sum-exp: merge the (max, sum) pairs around the row maximum
+    const float mx = row_max;
+    double s = se * (double) __expf(m - mx);
+    if (m == -INFINITY) s = 0.0;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     if (lane == 0) s_d[warp] = s;
@@ -430,6 +457,7 @@ k_topk_rows(TopkRows rows, int n, int k) {
         out->logsumexp = (float) (log(s) + (double) mx);
         out->n = n; out->k = k;
     }
+    (void) s_m;
 }
 
 extern "C" int b200_topk_rows(const float * const * rows, b200_topk_result * const * out, int n_rows, int64_t n, int k, void * stream) {

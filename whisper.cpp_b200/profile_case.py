@@ -3,6 +3,7 @@
 
     python whisper.cpp_b200/profile_case.py tc [M K N]        # tcgen05 quantised product, default 1280 x 1280 x 1500
     python whisper.cpp_b200/profile_case.py tc_cols [M K N]   # the same kernel in its per-column (decode) form, default 64 columns
+    python whisper.cpp_b200/profile_case.py mma [M K N]       # mma.sync quantised product (packed operands), default 1280 x 1280 x 1500
     python whisper.cpp_b200/profile_case.py fa_enc            # encoder attention 1500 x 1536 x 20 heads
     python whisper.cpp_b200/profile_case.py topk              # top-k side output of 64 logits rows
     python whisper.cpp_b200/profile_case.py conv              # the two F16 products of the large-v3 conv stem
@@ -63,6 +64,17 @@ def main():
             timed(lambda: K.b200_mul_mat_tc_cols(6, ptr(p), i64(nb), i64(M), i64(Kd), ptr(xq), ptr(xd), cols, N, C.byref(ep), None),
                   f"mul_mat_tc_cols {M} x {Kd} x {N} columns")
         assert K.b200_mul_mat_tc_status() == 0
+    elif case == "mma":
+        M, Kd, N = dims if len(dims) == 3 else (1280, 1280, 1500)
+        nb = M * Kd // 32
+        p = q5_planes(nb)
+        x, out = torch.randn((N, Kd), device="cuda"), torch.zeros((N, M), device="cuda")
+        wh, wd = torch.empty((nb, 16), dtype=torch.int32, device="cuda"), torch.empty(nb, device="cuda")
+        xh, xdh = torch.empty((N * Kd // 32, 16), dtype=torch.int32, device="cuda"), torch.empty(N * Kd // 32, device="cuda")
+        assert K.b200_mma_pack_weights(6, ptr(p), i64(nb), ptr(wh), ptr(wd), None) == 0
+        assert K.b200_mma_quantize(ptr(x), i64(N), i64(Kd), i64(Kd * 4), ptr(xh), ptr(xdh), None) == 0
+        timed(lambda: K.b200_mul_mat_mma_ep(ptr(wh), ptr(wd), i64(M), i64(Kd), ptr(xh), ptr(xdh), i64(N), ptr(out), i64(M), None, None),
+              f"mul_mat_mma {M} x {Kd} x {N}")
     elif case == "fa_enc":
         H, n_q, n_kv = 20, 1500, 1536
         q = torch.randn((n_q, H * 64), device="cuda")
