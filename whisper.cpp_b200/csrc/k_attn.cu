@@ -71,15 +71,27 @@ __device__ __forceinline__ float expf_glibc(float x, const uint64_t * tab) {
 // is not a multiple of 32; without it the per-key "skipped" handling is compiled out.
 // RELAXED (measurement switch GGML_B200_RELAXED=1, off by default): what a tensor-core attention would do instead - the
 // softmax weights rounded to F16 once, the V accumulator kept in f32 - to measure how far that moves the model outputs.
+// MIXED: the key/query products use the mixed-precision FMA of sm_100 (two f16 factors, f32 addend and result: the
+// same value as converting both factors first, the products of two f16 numbers being exact in f32), which drops the
+// f16 -> f32 conversions of the keys and halves the shared-memory reads of the queries.
 #define FA_R 4
-template <bool S_FMA, bool HAS_SKIP, bool RELAXED>
+__device__ __forceinline__ void fma_f16x2_f32(float & a0, float & a1, uint32_t kw, uint32_t qw) {
+    asm("{\n\t.reg .b16 kl, kh, ql, qh;\n\t"
+        "mov.b32 {kl, kh}, %2;\n\t"
+        "mov.b32 {ql, qh}, %3;\n\t"
+        "fma.rn.f32.f16 %0, kl, ql, %0;\n\t"
+        "fma.rn.f32.f16 %1, kh, qh, %1;\n\t}"
+        : "+f"(a0), "+f"(a1) : "r"(kw), "r"(qw));
+}
+template <bool S_FMA, bool HAS_SKIP, bool RELAXED, bool MIXED>
 __global__ void __launch_bounds__(128, 5)
 k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
                  const char * __restrict__ k, int64_t nbk1, int64_t nbk2,
                  const char * __restrict__ v, int64_t nbv1, int64_t nbv2,
                  const char * __restrict__ mask, int64_t nbm1,
                  float * __restrict__ dst, int64_t n_q, int64_t n_kv, int64_t n_head, float scale) {
-    __shared__ __align__(16) float Qs[4][FA_R][64];
+    __shared__ __align__(16) float Qs[4][MIXED ? 1 : FA_R][64];
+    __shared__ __align__(16) __half Qh[4][MIXED ? FA_R : 1][64];
     __shared__ __align__(16) float MS[4][FA_R][32];
     __shared__ __align__(16) float VS[4][FA_R][32];
     __shared__ uint64_t s_exp_tab[32];
@@ -94,8 +106,13 @@ k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
     for (int r = 0; r < FA_R; ++r) {
         const int64_t iq = min(row0 + r, n_q - 1);             // rows past the end repeat the last one and are not stored
         const float * qp = (const float *) (q + iq * nbq1 + h * nbq2);
-        Qs[warp][r][lane]      = round_f16(qp[lane]);
-        Qs[warp][r][lane + 32] = round_f16(qp[lane + 32]);
+        if (MIXED) {
+            Qh[warp][r][lane]      = __float2half_rn(qp[lane]);
+            Qh[warp][r][lane + 32] = __float2half_rn(qp[lane + 32]);
+        } else {
+            Qs[warp][r][lane]      = round_f16(qp[lane]);
+            Qs[warp][r][lane + 32] = round_f16(qp[lane + 32]);
+        }
     }
     __syncwarp();
 
@@ -131,11 +148,24 @@ k_flash_attn_ext(const char * __restrict__ q, int64_t nbq1, int64_t nbq2,
             float s = -INFINITY;
             if (!skip) {
                 float acc[32];
+                if (MIXED) {
+#pragma unroll
+                    for (int p = 0; p < 32; ++p) acc[p] = 0.0f;
+                }
 #pragma unroll
                 for (int step = 0; step < 2; ++step) {
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const uint4 kv = kreg[step * 4 + c];
+                        if (MIXED) {
+                            const uint4 qv = *(const uint4 *) &Qh[warp][r][step * 32 + c * 8];
+                            float * a = &acc[c * 8];
+                            fma_f16x2_f32(a[0], a[1], kv.x, qv.x);
+                            fma_f16x2_f32(a[2], a[3], kv.y, qv.y);
+                            fma_f16x2_f32(a[4], a[5], kv.z, qv.z);
+                            fma_f16x2_f32(a[6], a[7], kv.w, qv.w);
+                            continue;
+                        }
                         const float4 qa = *(const float4 *) &Qs[warp][r][step * 32 + c * 8];
                         const float4 qb = *(const float4 *) &Qs[warp][r][step * 32 + c * 8 + 4];
                         const float2 k0 = __half22float2(*(const __half2 *) &kv.x);
@@ -912,7 +942,10 @@ extern "C" int b200_flash_attn_ext(const float * q, int64_t nbq1, int64_t nbq2,
     dim3 grid((unsigned) ((n_q + 4 * FA_R - 1) / (4 * FA_R)), (unsigned) n_head);
     const bool has_skip = mask != nullptr || (n_kv % 32) != 0;
     static const bool relaxed = getenv("GGML_B200_RELAXED") != nullptr && atoi(getenv("GGML_B200_RELAXED")) != 0;
-#define FA_LAUNCH(SF, HS, RX) k_flash_attn_ext<SF, HS, RX><<<grid, 128, 0, as_stream(stream)>>>((const char *) q, nbq1, nbq2, (const char *) k, nbk1, nbk2, \
+    static const bool mixed = getenv("B200_FA_MIXED") == nullptr || atoi(getenv("B200_FA_MIXED")) != 0;
+#define FA_LAUNCH(SF, HS, RX) if (mixed) k_flash_attn_ext<SF, HS, RX, true><<<grid, 128, 0, as_stream(stream)>>>((const char *) q, nbq1, nbq2, (const char *) k, nbk1, nbk2, \
+            (const char *) v, nbv1, nbv2, (const char *) mask, nbm1, dst, n_q, n_kv, n_head, scale); \
+        else k_flash_attn_ext<SF, HS, RX, false><<<grid, 128, 0, as_stream(stream)>>>((const char *) q, nbq1, nbq2, (const char *) k, nbk1, nbk2, \
             (const char *) v, nbv1, nbv2, (const char *) mask, nbm1, dst, n_q, n_kv, n_head, scale)
     if (relaxed)         { if (has_skip) FA_LAUNCH(true, true, true); else FA_LAUNCH(true, false, true); }
     else if (g_fa_s_fma) { if (has_skip) FA_LAUNCH(true, true, false); else FA_LAUNCH(true, false, false); }

@@ -400,19 +400,39 @@ k_topk_rows(TopkRows rows, int n, int k) {
     for (int j = 0; j < B200_TOPK_MAX; ++j) { bv[j] = -INFINITY; bi[j] = 0x7fffffff; }
     float  m = -INFINITY;      // running maximum of this thread's elements
     double se = 0.0;           // sum of exp(x - m) over them
-    for (int i = tid; i < n; i += TOPK_THREADS) {
-        const float v = x[i];
-        if (v > m) { se = se * (double) __expf(m - v) + 1.0; m = v; }
-        else if (v == v) se += (double) __expf(v - m);
-        // insertion into the sorted list (strictly greater moves ahead; an equal value with a higher index stays behind)
-        if (bi[k - 1] == 0x7fffffff || v > bv[k - 1]) {
-            float cv = v; int ci = i;
+    float thr = -INFINITY;     // value of the k-th entry of the list once the list is full
+    bool  thr_set = false;
+    // eight loads in flight per thread (the pass is bound by load latency, not by bandwidth); the running sum takes every
+    // element, the sorted list only the few that beat its last entry, in ascending index order
+    for (int i = tid; i < n; i += 8 * TOPK_THREADS) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = (i + u * TOPK_THREADS < n) ? x[i + u * TOPK_THREADS] : 0.0f;
+        unsigned cand = 0;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (i + u * TOPK_THREADS < n) {
+                if (v[u] > m) { se = se * (double) __expf(m - v[u]) + 1.0; m = v[u]; }
+                else if (v[u] == v[u]) se += (double) __expf(v[u] - m);
+                if (!thr_set || v[u] > thr) cand |= 1u << u;
+            }
+        }
+        while (cand) {
+            const int u = __ffs(cand) - 1;
+            cand &= cand - 1;
+            float cv = v[0];
+#pragma unroll
+            for (int t = 1; t < 8; ++t) if (u == t) cv = v[t];
+            int ci = i + u * TOPK_THREADS;
+            if (thr_set && !(cv > thr)) continue;              // an earlier candidate of this round raised the bar
+            // insertion into the sorted list (strictly greater moves ahead; an equal value with a higher index stays behind)
 #pragma unroll
             for (int j = 0; j < B200_TOPK_MAX; ++j) {
                 if (j < k && (bi[j] == 0x7fffffff || cv > bv[j])) {
                     const float tv = bv[j]; const int ti = bi[j];
                     bv[j] = cv; bi[j] = ci; cv = tv; ci = ti;
                 }
+                if (j == k - 1) { thr = bv[j]; thr_set = bi[j] != 0x7fffffff; }      // the list's last entry, without a dynamic index
             }
         }
     }

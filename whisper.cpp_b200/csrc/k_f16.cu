@@ -5,6 +5,13 @@
 // Also the 1-D im2col that feeds the conv stem.
 #include "b200_common.cuh"
 
+// d = a * b + c with two f16 factors (bit patterns), f32 addend and result: the mixed-precision FMA of sm_100.  The
+// product of two f16 numbers is exact in f32, so this is fmaf(float(a), float(b), c) without the two conversions.
+__device__ __forceinline__ float fma_f16_f32(unsigned short a, unsigned short b, float c) {
+    asm("fma.rn.f32.f16 %0, %1, %2, %0;" : "+f"(c) : "h"(a), "h"(b));
+    return c;
+}
+
 // A warp owns TM x TN outputs (lane = running sum k % 32): 4 x 4 for small products, 8 x 8 where both extents are large
 // (the conv stem: 3000 x 1280 and 1500 x 1280 outputs), which halves the loads per FMA.
 template <bool X_F16, int TM, int TN>
@@ -29,26 +36,26 @@ k_mul_mat_f16(const char * __restrict__ a, Dims4 da, const char * __restrict__ b
 
     const int64_t np = K & ~(int64_t) 31;
     for (int64_t k0 = 0; k0 < np; k0 += 32) {
-        float av[TM], bv[TN];
+        unsigned short av[TM], bv[TN];
 #pragma unroll
         for (int i = 0; i < TM; ++i) {
             const int64_t m = m0 + i;
-            av[i] = (m < M) ? __half2float(*(const __half *) (ap + m * da.nb[1] + (k0 + lane) * 2)) : 0.0f;
+            av[i] = (m < M) ? *(const unsigned short *) (ap + m * da.nb[1] + (k0 + lane) * 2) : (unsigned short) 0;
         }
 #pragma unroll
         for (int j = 0; j < TN; ++j) {
             const int64_t n = n0 + j;
             if (n < N) {
-                if (X_F16) bv[j] = __half2float(*(const __half *) (bp + n * db.nb[1] + (k0 + lane) * 2));
-                else       bv[j] = round_f16(*(const float *) (bp + n * db.nb[1] + (k0 + lane) * 4));
+                if (X_F16) bv[j] = *(const unsigned short *) (bp + n * db.nb[1] + (k0 + lane) * 2);
+                else       bv[j] = __half_as_ushort(__float2half_rn(*(const float *) (bp + n * db.nb[1] + (k0 + lane) * 4)));
             } else {
-                bv[j] = 0.0f;
+                bv[j] = 0;
             }
         }
 #pragma unroll
         for (int i = 0; i < TM; ++i)
 #pragma unroll
-            for (int j = 0; j < TN; ++j) acc[i][j] = __fmaf_rn(av[i], bv[j], acc[i][j]);
+            for (int j = 0; j < TN; ++j) acc[i][j] = fma_f16_f32(av[i], bv[j], acc[i][j]);
     }
 
 #pragma unroll
