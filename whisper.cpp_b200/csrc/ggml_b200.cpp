@@ -1362,10 +1362,13 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
             // state 2: structure or aliasing did not fit the group's plan - run alone below
         } else {
             B.leader_active = true;
-            // how many states are decoding right now?  those that sent a decode graph within the last 20 ms
+            // how many states are decoding right now?  those that sent a decode graph within the last 20 ms, or within three
+            // turns where a turn takes longer than that (per-operator timing switched on, a device shared with encoders)
             int expected = 0;
             const int64_t now = now_ns();
-            for (b200_backend_ctx * c : B.members) if (now - c->last_decode_ns < 20 * 1000 * 1000) ++expected;
+            int64_t recent_ns = 20 * 1000 * 1000;
+            if (3.0 * B.step_ns_ema > (double) recent_ns) recent_ns = (int64_t) (3.0 * B.step_ns_ema);
+            for (b200_backend_ctx * c : B.members) if (now - c->last_decode_ns < recent_ns) ++expected;
             if (expected > max_group) expected = max_group;     // larger populations run as several groups whose steps overlap on the device
             // States that were served by an earlier batch come back one turn later.  Waiting for them merges the groups:
             // while they are away the device is busy with their step anyway, so the wait costs nothing when the device
@@ -1374,7 +1377,8 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
             if (B.step_ns_ema > 0) {
                 const int64_t turn_us = (int64_t) (1.25 * B.step_ns_ema / 1000.0);
                 if (turn_us > wait_us) wait_us = turn_us;
-                if (wait_us > 20000) wait_us = 20000;
+                const int64_t cap_us = timing ? 500000 : 20000;      // with per-operator timing a turn takes tens of milliseconds
+                if (wait_us > cap_us) wait_us = cap_us;
             }
             const auto deadline = std::chrono::steady_clock::now() + std::chrono::microseconds(wait_us);
             const int64_t t_w0 = now_ns();
