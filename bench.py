@@ -56,13 +56,13 @@ TOTAL_CLIPS = 64
 # replayed exactly, which keeps the attention kernels and the float chain of the products off the MMA accumulators.
 LIMITER = {
     "flash_attn_ext":    "F16 accumulation chain and 32-way score sums replayed exactly: instruction issue, tensor pipe unused by design",
-    "mul_mat_q":         "tcgen05 lane sums (fresh tensor-memory accumulator per 32-block), float chain of 8 FMAs per block and output on the FMA pipe",
+    "mul_mat_q":         "mma.sync lane sums (zero-expanded f16 operands), float chain of 8 FMAs per block and output on the FMA pipe",
     "mul_mat_vec_q":     "launch and load latency of small dependent launches, not bandwidth",
     "flash_attn_decode": "sequential F16 chain over the keys of each (row, head)",
 }
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of one representative launch of each class, from an ncu capture
 TRAFFIC_NCU = {
-    "mul_mat_vec_q":     {"bytes": 1.175e6, "launch": "1280 x 1280 Q5_0 weights x 16 columns (algorithmic 1.23e6: columns and output stay in L2)"},
+    "mul_mat_vec_q":     {"bytes": 1.177e6, "launch": "1280 x 1280 Q5_0 weights x 12 columns, the group size of the run (algorithmic 1.205e6: columns and output stay in L2)"},
     "flash_attn_decode": {"bytes": 251.9e6, "launch": "32 rows x 20 heads x 1536 keys (algorithmic 251.7e6)"},
     "flash_attn_ext":    {"bytes": 15.6e6,  "launch": "1500 x 1536 keys x 20 heads (Q + K/V once; K/V re-reads hit L2)"},
 }
@@ -445,7 +445,9 @@ def main():
                        "clips_total": clips_rank * world, "clips_per_gpu": clips_rank, "states_per_gpu": n_states, "flash_attn": True,
                        "sampling": "greedy from the plugin's top-k side output (b200_last_topk), logits read-back off" if side_output
                                    else "greedy from the logits rows read back to the host",
-                       "l2": "inputs larger than L2: 1.1 GB of weights are streamed per decode step per state"},
+                       "l2": "inputs larger than L2: 1.1 GB of weights are streamed per decode step per state",
+                       "timed_region": "value: encoder + decoder with the log-mels prepared beforehand; e2e: PCM on the host -> log-mel on the "
+                                       "device -> encoder -> decoder -> token ids on the host"},
             "e2e": {"value": e2e, "unit": "audio-s/s", "h2d_bytes_per_step": int(h2d_step), "d2h_bytes_per_step": int(d2h_step),
                     "ms_per_step": 1000.0 * sec_e / args.steps},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu_base,

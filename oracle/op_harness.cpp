@@ -61,7 +61,7 @@ static ggml_backend_t init_backend(const char * dev_name, int threads) {
 
 // op ids
 enum { OP_MUL_MAT = 1, OP_MUL_MAT_CONV, OP_FLASH_ATTN, OP_NORM, OP_ADD, OP_MUL, OP_SCALE, OP_GELU, OP_CPY_F16, OP_CONT_T,
-       OP_GET_ROWS, OP_IM2COL, OP_SOFT_MAX, OP_CONCAT, OP_KQ_NOFA, OP_KQV_NOFA, OP_CPY_F16_T, OP_ROUNDTRIP };
+       OP_GET_ROWS, OP_IM2COL, OP_SOFT_MAX, OP_CONCAT, OP_KQ_NOFA, OP_KQV_NOFA, OP_CPY_F16_T, OP_ROUNDTRIP, OP_MM_TWICE };
 
 // p: integer parameters, f: float parameters, in: input buffers (host), out: result buffer (host).
 // Returns number of bytes written to out, or a negative error.
@@ -168,6 +168,16 @@ int64_t oph_run(const char * dev_name, int op, const int64_t * p, const float * 
             src[1] = ggml_new_tensor_3d(ctx, GGML_TYPE_F32, n_kv, n_q, H);
             ggml_tensor * V = ggml_view_3d(ctx, src[0], n_kv, 64, H, n_ctx * ggml_element_size(src[0]), n_ctx * ggml_element_size(src[0]) * 64, 0);
             res = ggml_mul_mat(ctx, V, src[1]);
+        } break;
+        case OP_MM_TWICE: {         // two products on the same activations, p: wtype, K, M, N, overwrite.  With overwrite the
+                                    // activations are scaled IN PLACE between the products (the second product must see the new values:
+                                    // a backend that keeps a converted copy of the activations has to notice the write)
+            src[0] = ggml_new_tensor_2d(ctx, (enum ggml_type) p[0], p[1], p[2]);
+            src[1] = ggml_new_tensor_2d(ctx, GGML_TYPE_F32, p[1], p[3]);
+            ggml_tensor * y1 = ggml_mul_mat(ctx, src[0], src[1]);
+            ggml_tensor * x2 = p[4] ? ggml_scale_inplace(ctx, src[1], 0.5f) : src[1];
+            ggml_tensor * y2 = ggml_mul_mat(ctx, src[0], x2);
+            res = ggml_add(ctx, y1, ggml_scale(ctx, y2, 3.0f));
         } break;
         case OP_ROUNDTRIP: {        // set_tensor then get_tensor of a weight tensor; p: type, ne0, ne1
             src[0] = ggml_new_tensor_2d(ctx, (enum ggml_type) p[0], p[1], p[2]);

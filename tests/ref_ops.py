@@ -12,7 +12,7 @@ REF = os.path.join(ROOT, "oracle", "_ref")
 PLUGIN = os.path.join(ROOT, "whisper.cpp_b200", "libggml-b200.so")
 
 OPS = dict(MUL_MAT=1, MUL_MAT_CONV=2, FLASH_ATTN=3, NORM=4, ADD=5, MUL=6, SCALE=7, GELU=8, CPY_F16=9, CONT_T=10,
-           GET_ROWS=11, IM2COL=12, SOFT_MAX=13, CONCAT=14, KQ_NOFA=15, KQV_NOFA=16, CPY_F16_T=17, ROUNDTRIP=18)
+           GET_ROWS=11, IM2COL=12, SOFT_MAX=13, CONCAT=14, KQ_NOFA=15, KQV_NOFA=16, CPY_F16_T=17, ROUNDTRIP=18, MM_TWICE=19)
 F32, F16, Q5_0, Q8_0 = 0, 1, 6, 8
 BLOCK = {Q5_0: 22, Q8_0: 34}
 

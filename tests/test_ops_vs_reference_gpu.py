@@ -56,6 +56,17 @@ def test_mul_mat_quant(wtype, K, M, N):
     assert_bits(a, b, f"mul_mat type {wtype} K{K} M{M} N{N}")
 
 
+@pytest.mark.parametrize("overwrite", [0, 1])
+@pytest.mark.parametrize("wtype,K,M,N", [(R.Q5_0, 1280, 256, 64), (R.Q8_0, 384, 100, 40), (R.Q5_0, 512, 96, 12)])
+def test_two_products_on_the_same_activations(wtype, K, M, N, overwrite):
+    """The plugin quantises activations once for products that follow each other on the same source - and again when a node
+    in between wrote into that memory (here: an in-place scale)."""
+    w = R.quantize(wtype, rnd(12, M, K, scale=0.02))
+    x = rnd(13, N, K)
+    a, b = both("MM_TWICE", [wtype, K, M, N, overwrite], inputs=[w, x], out_shape=(N, M))
+    assert_bits(a, b, f"two products, overwrite {overwrite}")
+
+
 @pytest.mark.parametrize("K,M,N", [(384, 384, 1), (384, 1536, 3), (1536, 384, 40), (240, 300, 384), (384, 51865, 1), (100, 7, 5)])
 def test_mul_mat_f16_weights(K, M, N):
     w = rnd(4, M, K, scale=0.02).astype(np.float16)

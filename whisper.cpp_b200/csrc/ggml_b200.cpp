@@ -296,7 +296,21 @@ struct b200_backend_ctx {
     // side output of the last decoder graph: top-k / max / log-sum-exp of up to 8 logits rows (b200_topk_rows)
     b200_topk_result * topk = nullptr;       // device, 8 entries
     int          topk_rows = 0;              // rows valid after the last decoder graph of this instance
+    // what the scratch holds: the quantised form `qx_mode` of the activations at qx_data (N rows of K values, row stride
+    // in bytes).  Products that follow each other on the same activations (Q, K and V of a layer; the 64 cross-attention
+    // K/V products on the encoder output) quantise them once.  Cleared at the start of every graph and by every node
+    // whose output overlaps the range.
+    const void * qx_data = nullptr;
+    int64_t      qx_N = 0, qx_K = 0, qx_stride = 0;
+    int          qx_mode = 0;
 };
+static inline void qx_forget(b200_backend_ctx * ctx) { ctx->qx_data = nullptr; }
+static inline void qx_note_write(b200_backend_ctx * ctx, const struct ggml_tensor * t) {
+    if (!ctx->qx_data || !t || !t->data) return;
+    const char * a0 = (const char *) ctx->qx_data, * a1 = a0 + ctx->qx_N * ctx->qx_stride;
+    const char * b0 = (const char *) t->data,      * b1 = b0 + ggml_nbytes(t);
+    if (b0 < a1 && a0 < b1) ctx->qx_data = nullptr;
+}
 #define COLQ_MAX_K 8192
 #define COLQ_MAX_COLS 64
 static inline int8_t * colq_q(b200_backend_ctx * ctx) { return (int8_t *) ctx->colq; }
@@ -340,6 +354,7 @@ static void b200_backend_synchronize(ggml_backend_t backend) {
 
 static bool ensure_scratch(b200_backend_ctx * ctx, size_t size) {
     if (ctx->scratch_size >= size) return true;
+    qx_forget(ctx);
     if (ctx->scratch) {
         cudaStreamSynchronize(ctx->stream);
         cudaFree(ctx->scratch);
@@ -374,6 +389,14 @@ static bool mma_weights_of(b200_backend_ctx * ctx, const struct ggml_tensor * w,
     return true;
 }
 
+static inline bool qx_holds(const b200_backend_ctx * ctx, const void * x, int64_t N, int64_t K, int64_t stride, int mode) {
+    static const bool reuse = getenv("GGML_B200_NO_QX_REUSE") == nullptr;
+    return reuse && ctx->qx_data == x && ctx->qx_N == N && ctx->qx_K == K && ctx->qx_stride == stride && ctx->qx_mode == mode;
+}
+static inline void qx_set(b200_backend_ctx * ctx, const void * x, int64_t N, int64_t K, int64_t stride, int mode) {
+    ctx->qx_data = x; ctx->qx_N = N; ctx->qx_K = K; ctx->qx_stride = stride; ctx->qx_mode = mode;
+}
+
 // Quantised weights x f32 activations for more than 8 columns: activations are quantised into this backend's
 // scratch, then the tensor-pipe product (K a multiple of 128, 32 columns or more) or the dp4a product runs.
 static int gemm_quant(b200_backend_ctx * ctx, const struct ggml_tensor * w, const float * x, int64_t x_stride_bytes, int64_t N,
@@ -392,8 +415,11 @@ static int gemm_quant(b200_backend_ctx * ctx, const struct ggml_tensor * w, cons
         if (!ensure_scratch(ctx, q_pad + d_bytes)) return (int) cudaErrorMemoryAllocation;
         int8_t * xq = (int8_t *) ctx->scratch;
         float *  xd = (float *) ((char *) ctx->scratch + q_pad);
-        int e = b200_quantize_q8_0(x, N, K, x_stride_bytes, xq, xd, st);
-        if (e) return e;
+        if (!qx_holds(ctx, x, N, K, x_stride_bytes, 1)) {
+            int e = b200_quantize_q8_0(x, N, K, x_stride_bytes, xq, xd, st);
+            if (e) return e;
+            qx_set(ctx, x, N, K, x_stride_bytes, 1);
+        }
         return b200_mul_mat_tc_ep((int) w->type, w->data, nb_total, M, K, xq, xd, N, dst, ldd, ep, st);
     }
     mma_weights mw;
@@ -401,8 +427,11 @@ static int gemm_quant(b200_backend_ctx * ctx, const struct ggml_tensor * w, cons
         const size_t h_bytes = (size_t) N * (K / 32) * 64, d_bytes = (size_t) N * (K / 32) * 4;
         if (!ensure_scratch(ctx, h_bytes + d_bytes)) return (int) cudaErrorMemoryAllocation;
         float * xd = (float *) ((char *) ctx->scratch + h_bytes);
-        int e = b200_mma_quantize(x, N, K, x_stride_bytes, ctx->scratch, xd, st);
-        if (e) return e;
+        if (!qx_holds(ctx, x, N, K, x_stride_bytes, 2)) {
+            int e = b200_mma_quantize(x, N, K, x_stride_bytes, ctx->scratch, xd, st);
+            if (e) return e;
+            qx_set(ctx, x, N, K, x_stride_bytes, 2);
+        }
         return b200_mul_mat_mma_ep(mw.h, mw.d, M, K, ctx->scratch, xd, N, dst, ldd, ep, st);
     }
     const size_t q_bytes = (size_t) N * K, d_bytes = (size_t) N * (K / 32) * 4;
@@ -410,8 +439,11 @@ static int gemm_quant(b200_backend_ctx * ctx, const struct ggml_tensor * w, cons
     if (!ensure_scratch(ctx, q_pad + d_bytes)) return (int) cudaErrorMemoryAllocation;
     int8_t * xq = (int8_t *) ctx->scratch;
     float *  xd = (float *) ((char *) ctx->scratch + q_pad);
-    int e = b200_quantize_q8_0(x, N, K, x_stride_bytes, xq, xd, st);
-    if (e) return e;
+    if (!qx_holds(ctx, x, N, K, x_stride_bytes, 1)) {
+        int e = b200_quantize_q8_0(x, N, K, x_stride_bytes, xq, xd, st);
+        if (e) return e;
+        qx_set(ctx, x, N, K, x_stride_bytes, 1);
+    }
     return b200_mul_mat_q_ep((int) w->type, w->data, nb_total, M, K, xq, xd, N, dst, ldd, ep, st);
 }
 
@@ -1169,6 +1201,7 @@ static int run_plan(b200_backend_ctx * ctx, const exec_plan & plan, struct ggml_
         return ctx->events[(*n_ev)++];
     };
     ctx->colq_seq = -2;                      // activations of an earlier graph never carry over
+    qx_forget(ctx);
     static const bool group_gemv = getenv("GGML_B200_NO_FUSION") == nullptr && getenv("GGML_B200_NO_QKV_GROUP") == nullptr;
     for (size_t ii = 0; ii < plan.items.size(); ++ii) {
         const plan_item & it = plan.items[ii];
@@ -1182,6 +1215,7 @@ static int run_plan(b200_backend_ctx * ctx, const exec_plan & plan, struct ggml_
                    ggml_graph_node(gs[0], plan.items[ii + n_items].node)->src[1]->data == x0) ++n_items;
             if (n_items >= 2) {
                 const int e = run_gemv_group(ctx, &plan.items[ii], n_items, gs, n_g);
+                qx_forget(ctx);
                 if (e > 0) return e;
                 if (e == 0) {
                     ctx->item_seq += n_items - 1;
@@ -1205,6 +1239,8 @@ static int run_plan(b200_backend_ctx * ctx, const exec_plan & plan, struct ggml_
             if (*n_ev == 0) cudaEventRecord(next_event(), ctx->stream);      // one event per item boundary: item k runs between events k and k+1
         }
         const int e = run_item(ctx, it, gs, n_g);
+        if (n_g > 1) qx_forget(ctx);
+        else for (int nd = it.node; nd <= it.last; ++nd) qx_note_write(ctx, ggml_graph_node(gs[0], nd));      // an overwritten source is quantised again
         if (timing) cudaEventRecord(next_event(), ctx->stream);
         if (e != 0) {
             struct ggml_tensor * node = ggml_graph_node(gs[0], it.node);

@@ -399,7 +399,7 @@ k_topk_rows(TopkRows rows, int n, int k) {
 #pragma unroll
     for (int j = 0; j < B200_TOPK_MAX; ++j) { bv[j] = -INFINITY; bi[j] = 0x7fffffff; }
     float  m = -INFINITY;      // running maximum of this thread's elements
-    double se = 0.0;           // sum of exp(x - m) over them
+    float  se = 0.0f;          // sum of exp(x - m) over them (about a hundred terms per thread; the threads' sums are merged in double)
     float thr = -INFINITY;     // value of the k-th entry of the list once the list is full
     bool  thr_set = false;
     // eight loads in flight per thread (the pass is bound by load latency, not by bandwidth); the running sum takes every
@@ -412,8 +412,8 @@ k_topk_rows(TopkRows rows, int n, int k) {
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             if (i + u * TOPK_THREADS < n) {
-                if (v[u] > m) { se = se * (double) __expf(m - v[u]) + 1.0; m = v[u]; }
-                else if (v[u] == v[u]) se += (double) __expf(v[u] - m);
+                if (v[u] > m) { se = se * __expf(m - v[u]) + 1.0f; m = v[u]; }
+                else if (v[u] == v[u]) se += __expf(v[u] - m);
                 if (!thr_set || v[u] > thr) cand |= 1u << u;
             }
         }
@@ -466,7 +466,7 @@ k_topk_rows(TopkRows rows, int n, int k) {
     }
     // log-sum-exp: merge the (max, sum) pairs around the row maximum
     const float mx = row_max;
-    double s = se * (double) __expf(m - mx);
+    double s = (double) se * (double) __expf(m - mx);
     if (m == -INFINITY) s = 0.0;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
