@@ -328,9 +328,12 @@ def main():
         sampler.join()
         l1, h1, d1 = kl.b200_launch_count(), stat("b200_stat_h2d"), stat("b200_stat_d2h")
         t = torch.tensor([dt], device="cuda", dtype=torch.float64)
+        counts = torch.tensor([l1 - l0, h1 - h0, d1 - d0], device="cuda", dtype=torch.float64)      # whole-job sums
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()), l1 - l0, h1 - h0, d1 - d0, sampler.summary()
+            dist.all_reduce(counts, op=dist.ReduceOp.SUM)
+        n_l, n_h, n_d = (int(v) for v in counts.tolist())
+        return float(t.item()), n_l, n_h, n_d, sampler.summary()
 
     timed_tokens = []      # clip 0 of every timed step (both arms)
     sec_v, launches, _, _, clocks = run_steps("value")
@@ -343,8 +346,8 @@ def main():
     # the device mel front-end moves PCM in and the mel out, besides what crosses the plugin boundary
     mel_h2d = pcm.shape[1] * 4 + 400 * 4
     mel_d2h = w.n_mels * 6000 * 4
-    h2d_step = h2d / args.steps + clips_rank * mel_h2d
-    d2h_step = d2h / args.steps + clips_rank * mel_d2h
+    h2d_step = h2d / args.steps + clips_rank * world * mel_h2d
+    d2h_step = d2h / args.steps + clips_rank * world * mel_d2h
 
     # Roofline of the dominant kernel: per-operator CUDA events on the backend's own streams (b200_timing_*), two extra
     # passes inside this run.  Encoder-side classes are timed with ONE state on two clips (concurrent states would run
