@@ -3,6 +3,7 @@
 // ("CPU" = the reference's own CPU backend, "B200_0" = the plugin under test) and returns the result.
 // Compiled against the reference's ggml headers and linked to its unmodified libggml*.so
 // (oracle/Makefile), so the CPU side IS the reference implementation of each operator.
+#include <dlfcn.h>
 #include "ggml.h"
 #include "ggml-alloc.h"
 #include "ggml-backend.h"
@@ -220,6 +221,41 @@ int64_t oph_run(const char * dev_name, int op, const int64_t * p, const float * 
     return written;
 }
 
+
+// Plan reuse of the plugin: two graphs with the same operators, types and shapes in the same order.  In the first the
+// product feeds only the addition (a fusion candidate); in the second (variant 1) the last node reads the PRODUCT instead of
+// the sum, so the product has two consumers and must be written to memory.  Calls the plugin's test hook
+// b200_plan_probe(plan_graph, candidate) from the already loaded plugin library; no device work.
+// Returns the hook's value, or -10 (hook not found), -11 (set-up failed).
+int oph_plan_probe(const char * plugin_path, int variant) {
+    void * h = dlopen(plugin_path, RTLD_NOW | RTLD_LOCAL);
+    if (!h) return -10;
+    typedef int (*probe_fn)(ggml_cgraph *, ggml_cgraph *);
+    probe_fn probe = (probe_fn) dlsym(h, "b200_plan_probe");
+    if (!probe) return -10;
+    ggml_backend_t cpu = init_backend("CPU", 1);
+    if (!cpu) return -11;
+    struct ggml_init_params ip = { ggml_tensor_overhead() * 64 + 2 * ggml_graph_overhead(), nullptr, true };
+    ggml_context * ctx = ggml_init(ip);
+    ggml_cgraph * g[2];
+    for (int v = 0; v < 2; ++v) {
+        ggml_tensor * w = ggml_new_tensor_2d(ctx, GGML_TYPE_Q5_0, 256, 64);
+        ggml_tensor * x = ggml_new_tensor_2d(ctx, GGML_TYPE_F32, 256, 1);
+        ggml_tensor * b = ggml_new_tensor_1d(ctx, GGML_TYPE_F32, 64);
+        ggml_tensor * y = ggml_mul_mat(ctx, w, x);
+        ggml_tensor * z = ggml_add(ctx, y, b);
+        ggml_tensor * r = ggml_scale(ctx, (v == 1 && variant == 1) ? y : z, 2.0f);
+        g[v] = ggml_new_graph(ctx);
+        if (v == 1 && variant == 1) ggml_build_forward_expand(g[v], z);      // keep the node order: product, sum, scale
+        ggml_build_forward_expand(g[v], r);
+    }
+    ggml_backend_buffer_t buf = ggml_backend_alloc_ctx_tensors(ctx, cpu);
+    int rc = buf ? probe(g[0], g[1]) : -11;
+    if (buf) ggml_backend_buffer_free(buf);
+    ggml_free(ctx);
+    ggml_backend_free(cpu);
+    return rc;
+}
 
 // Error paths of a backend device (no abort, an error value instead):
 //  oph_try_alloc: 1 if the device's buffer type hands out a buffer of `size` bytes (freed again), 0 if it returns NULL.

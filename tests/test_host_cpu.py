@@ -125,3 +125,19 @@ def test_truncated_model_file_fails_cleanly(pkg, tmp_path):
     bad.write_bytes(data[: len(data) * 3 // 4 + 5])          # cut inside a tensor's data
     with pytest.raises(RuntimeError):
         pkg.Whisper(str(bad), use_gpu=False)
+
+
+@pytest.mark.skipif(not R.have_ref(), reason="reference build (oracle/_ref) missing")
+def test_cached_plan_is_refused_for_a_graph_with_other_consumers():
+    """Plans are cached by a signature of operators, types and shapes.  Two graphs with the same signature: in one the
+    product feeds only the bias addition (the plugin fuses them), in the other a later node reads the product itself, so
+    the product must reach memory.  The plugin has to refuse the cached fused plan for the second graph (no device work:
+    the plugin's test hook only builds and compares plans)."""
+    lib = R.lib()
+    lib.oph_plan_probe.argtypes = [C.c_char_p, C.c_int]
+    same = lib.oph_plan_probe(R.PLUGIN.encode(), 0)
+    other = lib.oph_plan_probe(R.PLUGIN.encode(), 1)
+    assert same >= 0 and other >= 0, (same, other)       # -1: signatures differ (the test graphs would be wrong), -10/-11: set-up
+    assert same & 2 and other & 2, "the product + bias pair is expected to be fused"
+    assert same & 1, "an identical graph must fit its own plan"
+    assert not (other & 1), "a graph whose product has a second consumer must not run on the fused plan"

@@ -1252,6 +1252,18 @@ static int run_plan(b200_backend_ctx * ctx, const exec_plan & plan, struct ggml_
     return 0;
 }
 
+// Test hook (no device work): builds the fused plan of `plan_graph` and says whether `candidate`, a graph with the same
+// signature, may run on it.  Returns -1 when the signatures differ, else bit 0 = fits, bit 1 = the plan fuses something.
+extern "C" int b200_plan_probe(struct ggml_cgraph * plan_graph, struct ggml_cgraph * candidate) {
+    if (!plan_graph || !candidate) return -2;
+    if (graph_signature(plan_graph) != graph_signature(candidate)) return -1;
+    exec_plan plan;
+    build_plan(plan_graph, plan, true);
+    int fused = 0;
+    for (const plan_item & it : plan.items) if (it.last != it.node) fused = 2;
+    return (graph_fits_plan(plan, candidate) ? 1 : 0) | fused;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Cross-state batching of decode steps.  Every whisper_state owns a backend instance and a host thread; their
 // single-token decode graphs arrive here independently.  Threads that arrive within a short window hand their
