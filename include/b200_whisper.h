@@ -292,7 +292,13 @@ void   b200_mel_destroy(void * plan);
  *       side output of logits row `row` of the last decoder graph computed on the CALLING thread (whisper_decode is
  *       synchronous, so that is the state the thread just stepped); waits for that graph, copies one result to the host.
  *       Returns 0, or B200_ERR_ARG when there is no such row.
- * No counterpart in the reference, which samples from the full row on the host. */
+ * No counterpart in the reference, which samples from the full row on the host.
+ *
+ * A plain exported symbol of the plugin for tests (no device work, needs no GPU):
+ *   int b200_plan_probe(struct ggml_cgraph * plan_graph, struct ggml_cgraph * candidate)
+ *       builds the fused execution plan of plan_graph and checks candidate against it the way a cached plan is checked
+ *       before reuse: -1 when the two graphs' signatures differ, else bit 0 = candidate may run on the plan, bit 1 = the
+ *       plan fuses at least one pair of nodes. */
 
 /* Library info: number of kernel launches issued so far by this process (all entry points). */
 int64_t b200_launch_count(void);
