@@ -641,7 +641,8 @@ k_flash_attn_decode_stream(FaRows rows, int max_kv, int8_t * __restrict__ xq, fl
     const float scale = rows.scale;
     chain_wait();                          // Q, and for self-attention the newest K/V rows, come from the kernels before this one
 
-    if (tid < 64) Qs[tid] = round_f16(*(const float *) (R.q + h * rows.nbq2 + tid * 4));
+    __half * Qh = (__half *) Qs;           // the query as f16: the scores use the mixed-precision FMA (f16 factors, f32 sum)
+    if (tid < 64) Qh[tid] = __float2half_rn(*(const float *) (R.q + h * rows.nbq2 + tid * 4));
     if (tid >= 96) s_exp_tab[tid - 96] = c_exp2f_tab[tid - 96];
     for (int g = tid; g < (max_kv + 7) / 8; g += FA_DEC_THREADS) evt[g] = 0;
 
@@ -691,30 +692,20 @@ k_flash_attn_decode_stream(FaRows rows, int max_kv, int8_t * __restrict__ xq, fl
             skip = (mv == -INFINITY);
             if (!skip) {
                 float acc[32];
+#pragma unroll
+                for (int pp = 0; pp < 32; ++pp) acc[pp] = 0.0f;
                 const char * krow = (const char *) (Ks + (size_t) (c % 3) * FA_DEC_CHUNK * 64) + j * 128;
 #pragma unroll
                 for (int step = 0; step < 2; ++step) {
 #pragma unroll
                     for (int cc = 0; cc < 4; ++cc) {
                         const uint4 kv = *(const uint4 *) (krow + (((step * 4 + cc) ^ (j & 7)) << 4));
-                        const float4 qa = *(const float4 *) &Qs[step * 32 + cc * 8];
-                        const float4 qb = *(const float4 *) &Qs[step * 32 + cc * 8 + 4];
-                        const float2 k0v = __half22float2(*(const __half2 *) &kv.x);
-                        const float2 k1v = __half22float2(*(const __half2 *) &kv.y);
-                        const float2 k2v = __half22float2(*(const __half2 *) &kv.z);
-                        const float2 k3v = __half22float2(*(const __half2 *) &kv.w);
+                        const uint4 qv = *(const uint4 *) (Qh + step * 32 + cc * 8);
                         float * a = &acc[cc * 8];
-                        if (step == 0) {
-                            a[0] = __fmaf_rn(k0v.x, qa.x, 0.0f); a[1] = __fmaf_rn(k0v.y, qa.y, 0.0f);
-                            a[2] = __fmaf_rn(k1v.x, qa.z, 0.0f); a[3] = __fmaf_rn(k1v.y, qa.w, 0.0f);
-                            a[4] = __fmaf_rn(k2v.x, qb.x, 0.0f); a[5] = __fmaf_rn(k2v.y, qb.y, 0.0f);
-                            a[6] = __fmaf_rn(k3v.x, qb.z, 0.0f); a[7] = __fmaf_rn(k3v.y, qb.w, 0.0f);
-                        } else {
-                            a[0] = __fmaf_rn(k0v.x, qa.x, a[0]); a[1] = __fmaf_rn(k0v.y, qa.y, a[1]);
-                            a[2] = __fmaf_rn(k1v.x, qa.z, a[2]); a[3] = __fmaf_rn(k1v.y, qa.w, a[3]);
-                            a[4] = __fmaf_rn(k2v.x, qb.x, a[4]); a[5] = __fmaf_rn(k2v.y, qb.y, a[5]);
-                            a[6] = __fmaf_rn(k3v.x, qb.z, a[6]); a[7] = __fmaf_rn(k3v.y, qb.w, a[7]);
-                        }
+                        fma_f16x2_f32(a[0], a[1], kv.x, qv.x);
+                        fma_f16x2_f32(a[2], a[3], kv.y, qv.y);
+                        fma_f16x2_f32(a[4], a[5], kv.z, qv.z);
+                        fma_f16x2_f32(a[6], a[7], kv.w, qv.w);
                     }
                 }
                 float y[8];
