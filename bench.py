@@ -24,6 +24,7 @@ import argparse
 import ctypes as C
 import json
 import os
+import resource
 import subprocess
 import sys
 import threading
@@ -313,6 +314,7 @@ def main():
                 barrier()
                 sampler.start()
                 l0, h0, d0 = kl.b200_launch_count(), stat("b200_stat_h2d"), stat("b200_stat_d2h")
+                ru0 = resource.getrusage(resource.RUSAGE_SELF)
                 t0 = time.perf_counter()
             # every call returns when the last state has synchronised its stream and read its last logits back: the host
             # clock brackets all device work of the step (the plugin's streams are not torch's, so torch events see nothing)
@@ -324,6 +326,8 @@ def main():
                 timed_tokens.append(toks[0].copy())
         barrier()
         dt = time.perf_counter() - t0
+        ru1 = resource.getrusage(resource.RUSAGE_SELF)
+        host_cpu[kind] = ((ru1.ru_utime - ru0.ru_utime) + (ru1.ru_stime - ru0.ru_stime)) / dt      # host cores busy in this rank
         sampler.stop_flag.set()
         sampler.join()
         l1, h1, d1 = kl.b200_launch_count(), stat("b200_stat_h2d"), stat("b200_stat_d2h")
@@ -335,6 +339,7 @@ def main():
         n_l, n_h, n_d = (int(v) for v in counts.tolist())
         return float(t.item()), n_l, n_h, n_d, sampler.summary()
 
+    host_cpu = {}
     timed_tokens = []      # clip 0 of every timed step (both arms)
     sec_v, launches, _, _, clocks = run_steps("value")
     if args.quick:
@@ -454,6 +459,8 @@ def main():
             "e2e": {"value": e2e, "unit": "audio-s/s", "h2d_bytes_per_step": int(h2d_step), "d2h_bytes_per_step": int(d2h_step),
                     "ms_per_step": 1000.0 * sec_e / args.steps},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu_base,
+            "host": {"cpus": os.cpu_count(), "cores_busy_value": round(host_cpu.get("value", 0.0), 2),
+                     "cores_busy_e2e": round(host_cpu.get("e2e", 0.0), 2), "threads": n_states},
             "parity_in_run": parity, "encoder_ms_per_30s": encoder_ms, "whisper_bench": wbench,
             "kernel_classes_per_clip": {k: {"launch_groups": round(v["launch_groups"], 1), "ms": round(v["ms"], 3), "timed": v["timed"]}
                                         for k, v in sorted(per_clip.items(), key=lambda kv: -kv[1]["ms"])},

@@ -158,6 +158,25 @@ static void * staging_reserve(staging_buf & sb, size_t size) {
     return sb.p;
 }
 
+// Waits for a stream without spinning on a core: with one host thread per whisper_state there are more threads than
+// cores, and a thread that spins in cudaStreamSynchronize takes its core away from the threads that are launching work.
+// One blocking-sync event per host thread (never destroyed: it lives as long as the thread's CUDA context use).
+static cudaError_t stream_wait_blocking(cudaStream_t st) {
+    static const bool spin = getenv("GGML_B200_SPIN_SYNC") != nullptr;
+    if (spin) return cudaStreamSynchronize(st);
+    thread_local cudaEvent_t ev[B200_MAX_DEVICES] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= B200_MAX_DEVICES) return cudaStreamSynchronize(st);
+    if (!ev[dev] && cudaEventCreateWithFlags(&ev[dev], cudaEventBlockingSync | cudaEventDisableTiming) != cudaSuccess) {
+        cudaGetLastError();
+        ev[dev] = nullptr;
+        return cudaStreamSynchronize(st);
+    }
+    cudaError_t e = cudaEventRecord(ev[dev], st);
+    if (e != cudaSuccess) return e;
+    return cudaEventSynchronize(ev[dev]);
+}
+
 static void b200_buffer_set_tensor(ggml_backend_buffer_t buffer, struct ggml_tensor * tensor, const void * data, size_t offset, size_t size) {
     b200_buffer_ctx * ctx = (b200_buffer_ctx *) buffer->context;
     cudaSetDevice(ctx->device);
@@ -178,12 +197,12 @@ static void b200_buffer_set_tensor(ggml_backend_buffer_t buffer, struct ggml_ten
         bool ok = stage != nullptr;
         ok = ok && cuda_ok(cudaMemcpyAsync(stage, data, size, cudaMemcpyHostToDevice, st), "set_tensor upload");
         ok = ok && b200_blocks_to_planes_device((int) tensor->type, stage, tensor->data, nb_total, first, count, (void *) st) == 0;
-        ok = cuda_ok(cudaStreamSynchronize(st), "set_tensor sync") && ok;
+        ok = cuda_ok(stream_wait_blocking(st), "set_tensor sync") && ok;
         if (!ok) note_buffer_error(ctx->device, "set_tensor");
         return;
     }
     bool ok = cuda_ok(cudaMemcpyAsync((char *) tensor->data + offset, data, size, cudaMemcpyHostToDevice, st), "set_tensor");
-    ok = ok && cuda_ok(cudaStreamSynchronize(st), "set_tensor sync");
+    ok = ok && cuda_ok(stream_wait_blocking(st), "set_tensor sync");
     if (!ok) note_buffer_error(ctx->device, "set_tensor");
 }
 
@@ -211,12 +230,12 @@ static void b200_buffer_get_tensor(ggml_backend_buffer_t buffer, const struct gg
         bool ok = stage != nullptr;
         ok = ok && b200_planes_to_blocks_device((int) tensor->type, tensor->data, stage, nb_total, first, count, (void *) st) == 0;
         ok = ok && cuda_ok(cudaMemcpyAsync(data, stage, size, cudaMemcpyDeviceToHost, st), "get_tensor download");
-        ok = cuda_ok(cudaStreamSynchronize(st), "get_tensor sync") && ok;
+        ok = cuda_ok(stream_wait_blocking(st), "get_tensor sync") && ok;
         if (!ok) { note_buffer_error(ctx->device, "get_tensor"); memset(data, 0, size); }
         return;
     }
     bool ok = cuda_ok(cudaMemcpyAsync(data, (const char *) tensor->data + offset, size, cudaMemcpyDeviceToHost, st), "get_tensor");
-    ok = ok && cuda_ok(cudaStreamSynchronize(st), "get_tensor sync");
+    ok = ok && cuda_ok(stream_wait_blocking(st), "get_tensor sync");
     if (!ok) { note_buffer_error(ctx->device, "get_tensor"); memset(data, 0, size); }
 }
 
@@ -1287,11 +1306,15 @@ struct batch_req {
     int                  state;     // 0 waiting, 1 done (stream must wait on ev), 2 run it yourself, 3 failed
     batch_event *        ev;
     int                  fits;      // checked against the cached plan by the submitting thread: 1 yes, -1 no, 0 not checked
+    // A follower sleeps on its OWN condition variable and only the leader that served it wakes it.  One shared variable
+    // with notify_all wakes every waiting thread on every arrival: with 64 states that is thousands of futile wake-ups
+    // per step, all queueing for the batcher's mutex in front of the leaders.
+    std::condition_variable * cv;
 };
 
 struct device_batcher {
     std::mutex              mu;
-    std::condition_variable cv;
+    std::condition_variable cv;                 // the current leader waits here for arrivals
     std::vector<batch_req *> pending;
     bool                    leader_active = false;
     std::vector<batch_event *> free_events;   // events nobody waits on (guarded by mu)
@@ -1369,7 +1392,8 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
     if (decode_graph) tl_last_decode_ctx = ctx;      // b200_last_topk answers for the state this thread stepped last
     // ---- batched path -------------------------------------------------------------------------
     if (batching && fuse && B.alive > 1 && decode_graph) {
-        batch_req req = { ctx, cgraph, graph_signature(cgraph), 0, nullptr, 0 };
+        std::condition_variable my_cv;
+        batch_req req = { ctx, cgraph, graph_signature(cgraph), 0, nullptr, 0, &my_cv };
         const int64_t t_arrive = now_ns();
         ctx->last_decode_ns = t_arrive;
         {   // every thread checks its own graph against the cached plan, in parallel with the others
@@ -1391,8 +1415,8 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
         }
         B.pending.push_back(&req);
         if (B.leader_active) {
-            B.cv.notify_all();                                   // the leader may be waiting for this arrival
-            B.cv.wait(lk, [&] { return req.state != 0; });
+            B.cv.notify_one();                                   // the leader (the only waiter on this variable) may be waiting for this arrival
+            my_cv.wait(lk, [&] { return req.state != 0; });
             lk.unlock();
             if (req.state == 1) {
                 const bool waited = cuda_ok(cudaStreamWaitEvent(ctx->stream, req.ev->ev, 0), "cudaStreamWaitEvent");
@@ -1515,9 +1539,9 @@ static enum ggml_status b200_backend_graph_compute(ggml_backend_t backend, struc
                 for (batch_req * s : served) if (s == r) was_served = true;
                 if (was_served) { r->ev = ev; r->state = rc == 0 ? 1 : 3; if (rc == 0) r->ctx->served_ns = t_done; }
                 else r->state = 2;
+                r->cv->notify_one();                              // under the lock: the request lives on its owner's stack until it sees its state
             }
             lk.unlock();
-            B.cv.notify_all();
             if (rc == 0) {
                 g_nodes_computed += n_compute;
                 g_graphs_computed += 1;
@@ -1766,7 +1790,7 @@ GGML_BACKEND_API int b200_last_topk(int row, b200_topk_result * out) {
     if (cudaSetDevice(ctx->device) != cudaSuccess) return (int) cudaGetLastError();
     // the side output was enqueued on the stream that ran the graph; this instance's stream is ordered behind it
     cudaError_t e = cudaMemcpyAsync(out, ctx->topk + row, sizeof(*out), cudaMemcpyDeviceToHost, ctx->stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess) e = stream_wait_blocking(ctx->stream);
     if (e != cudaSuccess) { cudaGetLastError(); return (int) e; }
     g_d2h_bytes += (int64_t) sizeof(*out);
     return 0;
