@@ -21,6 +21,7 @@
 #include <condition_variable>
 #include <memory>
 #include <mutex>
+#include <thread>
 #include <string>
 #include <unordered_map>
 #include <vector>
@@ -158,15 +159,19 @@ static void * staging_reserve(staging_buf & sb, size_t size) {
     return sb.p;
 }
 
-// Waits for a stream without spinning on a core: with one host thread per whisper_state there are more threads than
-// cores, and a thread that spins in cudaStreamSynchronize takes its core away from the threads that are launching work.
-// One blocking-sync event per host thread (never destroyed: it lives as long as the thread's CUDA context use).
+// Waits for a stream.  With one host thread per whisper_state there can be more threads than cores, and a thread that
+// spins in cudaStreamSynchronize then takes its core away from the threads that are launching work: in that case the
+// wait sleeps on a blocking-sync event (one per host thread and device, never destroyed).  With few states the spinning
+// wait is kept: waking a sleeping thread costs tens of microseconds, several times per decoder step.
+static int live_backends(int device);
 static cudaError_t stream_wait_blocking(cudaStream_t st) {
-    static const bool spin = getenv("GGML_B200_SPIN_SYNC") != nullptr;
-    if (spin) return cudaStreamSynchronize(st);
-    thread_local cudaEvent_t ev[B200_MAX_DEVICES] = {};
+    static const int force = getenv("GGML_B200_SPIN_SYNC") ? atoi(getenv("GGML_B200_SPIN_SYNC")) : -1;      // 1 spin, 0 sleep
+    static const int cores = (int) std::thread::hardware_concurrency();
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= B200_MAX_DEVICES) return cudaStreamSynchronize(st);
+    const bool spin = force >= 0 ? force != 0 : 2 * live_backends(dev) <= (cores > 0 ? cores : 8);
+    if (spin) return cudaStreamSynchronize(st);
+    thread_local cudaEvent_t ev[B200_MAX_DEVICES] = {};
     if (!ev[dev] && cudaEventCreateWithFlags(&ev[dev], cudaEventBlockingSync | cudaEventDisableTiming) != cudaSuccess) {
         cudaGetLastError();
         ev[dev] = nullptr;
@@ -1326,6 +1331,7 @@ struct device_batcher {
 };
 
 static device_batcher g_batchers[B200_MAX_DEVICES];
+static int live_backends(int device) { return g_batchers[device].alive; }      // read without the lock: a hint
 
 static void batcher_join(b200_backend_ctx * ctx) {
     device_batcher & B = g_batchers[ctx->device];
