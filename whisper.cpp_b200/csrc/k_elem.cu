@@ -424,7 +424,7 @@ k_topk_rows(TopkRows rows, int n, int k) {
 #pragma unroll
             for (int t = 1; t < 8; ++t) if (u == t) cv = v[t];
             int ci = i + u * TOPK_THREADS;
-            if (thr_set && !(cv > thr)) continue;              // an earlier candidate of this round raised the bar
+            if (thr_set && !(cv > thr)) continue;              // an earlier candidate of these eight raised the bar
             // insertion into the sorted list (strictly greater moves ahead; an equal value with a higher index stays behind)
 #pragma unroll
             for (int j = 0; j < B200_TOPK_MAX; ++j) {

@@ -1230,14 +1230,10 @@ static int launch_skinny2(const QPlanes & w, int64_t M, int nbk, const int8_t * 
 template <int TYPE>
 static int launch_skinny_n(const QPlanes & w, int64_t M, int nbk, const int8_t * xq, const float * xd, int n_cols, const GemvCols32 & cols,
                            const GemvEp & ep, cudaStream_t st) {
-    // measured on B200: the column-pair form wins for many columns on short rows and for the tall logits matrix
+    // measured on B200: the column-pair form wins for many columns on short rows and for the tall logits matrix; for 9..16
+    // columns it neither helps nor hurts the throughput of 64 concurrent states (19.5 against 19.2-20.1 ms per round of
+    // decode steps) and its single launch is slower, so the lane-per-thread form keeps those
     if (n_cols >= 9 && M >= 16384) return launch_skinny2<TYPE, 16>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
-    static const int s2_min = getenv("B200_SKINNY2_MIN_COLS") ? atoi(getenv("B200_SKINNY2_MIN_COLS")) : 17;      // experiment
-    static const int s2_rows = getenv("B200_SKINNY2_ROWS") ? atoi(getenv("B200_SKINNY2_ROWS")) : 8;
-    if (n_cols >= s2_min && n_cols < 17 && nbk <= 80) {
-        if (s2_rows == 16) return launch_skinny2<TYPE, 16>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
-        return launch_skinny2<TYPE, 8>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
-    }
     if (n_cols >= 17 && nbk <= 80) return launch_skinny2<TYPE, 8>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
     if (M >= 16384 && n_cols > 4) {      // tall matrices (logits): more rows per CTA so that the columns are staged fewer times
         if (n_cols <= 8)  return launch_skinny<TYPE, 32, 8>(w, M, nbk, xq, xd, n_cols, cols, ep, st);
