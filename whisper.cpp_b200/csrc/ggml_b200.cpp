@@ -166,7 +166,13 @@ static void * staging_reserve(staging_buf & sb, size_t size) {
 static int live_backends(int device);
 static cudaError_t stream_wait_blocking(cudaStream_t st) {
     static const int force = getenv("GGML_B200_SPIN_SYNC") ? atoi(getenv("GGML_B200_SPIN_SYNC")) : -1;      // 1 spin, 0 sleep
-    static const int cores = (int) std::thread::hardware_concurrency();
+    // cores this process can count on: the host's, shared with the other ranks of a one-process-per-GPU launch
+    static const int cores = [] {
+        int c = (int) std::thread::hardware_concurrency();
+        const char * lws = getenv("LOCAL_WORLD_SIZE");
+        const int ranks = lws ? atoi(lws) : 1;
+        return ranks > 1 ? c / ranks : c;
+    }();
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= B200_MAX_DEVICES) return cudaStreamSynchronize(st);
     const bool spin = force >= 0 ? force != 0 : 2 * live_backends(dev) <= (cores > 0 ? cores : 8);
