@@ -324,7 +324,10 @@ struct b200_backend_ctx {
     cudaEvent_t  sync_event = nullptr;       // blocking-sync event: waiting threads sleep instead of spinning on a core
     int64_t      item_seq = 0;
     // side output of the last decoder graph: top-k / max / log-sum-exp of up to 8 logits rows (b200_topk_rows)
-    b200_topk_result * topk = nullptr;       // device, 8 entries
+    b200_topk_result * topk = nullptr;       // 8 entries, as the kernels address them
+    b200_topk_result * topk_host = nullptr;  // the same entries as the host reads them, when they live in mapped pinned host memory:
+                                             // the kernel stores its few words per row straight into host memory and b200_last_topk
+                                             // needs no copy and no wait of its own after the step has been synchronised
     int          topk_rows = 0;              // rows valid after the last decoder graph of this instance
     // what the scratch holds: the quantised form `qx_mode` of the activations at qx_data (N rows of K values, row stride
     // in bytes).  Products that follow each other on the same activations (Q, K and V of a layer; the 64 cross-attention
@@ -362,7 +365,8 @@ static void b200_backend_free(ggml_backend_t backend) {
     cudaStreamSynchronize(ctx->stream);
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->colq) cudaFree(ctx->colq);
-    if (ctx->topk) cudaFree(ctx->topk);
+    if (ctx->topk_host) cudaFreeHost(ctx->topk_host);
+    else if (ctx->topk) cudaFree(ctx->topk);
     if (tl_last_decode_ctx == ctx) tl_last_decode_ctx = nullptr;
     if (ctx->sync_event) cudaEventDestroy(ctx->sync_event);
     for (cudaEvent_t e : ctx->events) cudaEventDestroy(e);
@@ -1665,7 +1669,20 @@ static ggml_backend_t b200_dev_init_backend(ggml_backend_dev_t dev, const char *
         cudaStreamDestroy(ctx->stream); delete ctx; return nullptr;
     }
     if (cudaEventCreateWithFlags(&ctx->sync_event, cudaEventBlockingSync | cudaEventDisableTiming) != cudaSuccess) { cudaGetLastError(); ctx->sync_event = nullptr; }
-    if (cudaMalloc((void **) &ctx->topk, 8 * sizeof(b200_topk_result)) != cudaSuccess) { cudaGetLastError(); ctx->topk = nullptr; }
+    {
+        static const bool zero_copy = getenv("GGML_B200_TOPK_DEVICE") == nullptr;
+        void * hp = nullptr, * dp = nullptr;
+        if (zero_copy && cudaHostAlloc(&hp, 8 * sizeof(b200_topk_result), cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess &&
+            cudaHostGetDevicePointer(&dp, hp, 0) == cudaSuccess) {
+            memset(hp, 0, 8 * sizeof(b200_topk_result));
+            ctx->topk_host = (b200_topk_result *) hp;
+            ctx->topk = (b200_topk_result *) dp;
+        } else {
+            cudaGetLastError();
+            if (hp) cudaFreeHost(hp);
+            if (cudaMalloc((void **) &ctx->topk, 8 * sizeof(b200_topk_result)) != cudaSuccess) { cudaGetLastError(); ctx->topk = nullptr; }
+        }
+    }
     // activation scratch of the many-column products, sized here for Whisper's largest product (1500 columns of 5120
     // values) so that graph_compute does not allocate on its usual path; it still grows on demand for larger graphs
     ensure_scratch(ctx, (size_t) 1536 * 5120 + (size_t) 1536 * (5120 / 32) * 4);
@@ -1801,8 +1818,15 @@ GGML_BACKEND_API int b200_last_topk(int row, b200_topk_result * out) {
     if (!ctx || !out || !ctx->topk || row < 0 || row >= ctx->topk_rows) return B200_ERR_ARG;
     if (cudaSetDevice(ctx->device) != cudaSuccess) return (int) cudaGetLastError();
     // the side output was enqueued on the stream that ran the graph; this instance's stream is ordered behind it
-    cudaError_t e = cudaMemcpyAsync(out, ctx->topk + row, sizeof(*out), cudaMemcpyDeviceToHost, ctx->stream);
-    if (e == cudaSuccess) e = stream_wait_blocking(ctx->stream);
+    cudaError_t e;
+    if (ctx->topk_host) {      // written by the kernel into host memory: visible once the stream is known to be idle
+        e = cudaStreamQuery(ctx->stream);
+        if (e == cudaErrorNotReady) { cudaGetLastError(); e = stream_wait_blocking(ctx->stream); }
+        if (e == cudaSuccess) memcpy(out, ctx->topk_host + row, sizeof(*out));
+    } else {
+        e = cudaMemcpyAsync(out, ctx->topk + row, sizeof(*out), cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = stream_wait_blocking(ctx->stream);
+    }
     if (e != cudaSuccess) { cudaGetLastError(); return (int) e; }
     g_d2h_bytes += (int64_t) sizeof(*out);
     return 0;
